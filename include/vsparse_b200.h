@@ -1,0 +1,209 @@
+/*
+ * vsparse_b200 — C ABI of the column-vector-sparse (CVSE) SpMM / SDDMM library for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain pointers and sizes.  Unless a function says "host", pointers are DEVICE
+ * pointers owned by the caller; the library allocates nothing, keeps no workspace between calls, enqueues
+ * its kernels on `stream` (a cudaStream_t passed as void*) and returns without synchronising.
+ *
+ * Return value of every function: 0 on success, a negative VS_ERR_* code when the arguments are rejected
+ * before anything is launched, or a positive cudaError_t if the CUDA runtime reported one.
+ *
+ * Naming follows the vectorSparse reference, whose operator headers these entry points replace:
+ *   SpMM   A[m x n] * B[n x k] = C[m x k]      reference argument `k` = dense width, `n` = columns of A
+ *   SDDMM  out = (lhs[m x k] * rhs[n x k]^T) sampled at the CVSE mask of an m x n matrix
+ * CVSE: m_vec vector-rows of `vec_length` (V) real rows each (m = m_vec*V); row_offsets[m_vec+1] and
+ * col_indices[nnz_vec] count column VECTORS; values[j*V+v] belongs to real row i*V+v, column col_indices[j];
+ * row_indices[m_vec] is the order in which vector-rows are scheduled (a load-balancing hint that never
+ * changes the result).
+ */
+#ifndef VSPARSE_B200_H
+#define VSPARSE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types */
+#define VS_F16 0
+#define VS_F32 1
+
+/* kernel families: the reference's wmma* entry points map to TENSOR, its cuda* entry points to CUDA_CORE */
+#define VS_PATH_TENSOR 0
+#define VS_PATH_CUDA_CORE 1
+
+/* validation errors (nothing was launched) */
+#define VS_OK 0
+#define VS_ERR_VEC_LENGTH (-1)   /* vec_length not in {1,2,4,8} (tensor path: {2,4,8}) */
+#define VS_ERR_DTYPE (-2)        /* unsupported (path, in_dtype, out_dtype) combination */
+#define VS_ERR_SHAPE (-3)        /* negative size, or a size the path cannot tile (see each function) */
+#define VS_ERR_NULL (-4)         /* a required pointer is null */
+#define VS_ERR_ALIGN (-5)        /* a pointer or stride is not 16-byte aligned */
+#define VS_ERR_STRUCTURE (-6)    /* host-side CVSE check failed: offsets not monotone, column out of range */
+#define VS_ERR_IO (-7)           /* file could not be opened or parsed */
+#define VS_ERR_ARG (-8)          /* any other rejected argument (unknown mode, batch < 1, ...) */
+#define VS_ERR_DEVICE (-9)       /* a kernel reported a bounded wait that ran out (see vs_device_status) */
+
+const char *vs_error_string(int code);
+
+/* Library / build identification: "vsparse_b200 <version> sm_100a". */
+const char *vs_version(void);
+
+/* ------------------------------------------------------------------------------------------------------
+ * SpMM.  Replaces spmm::wmmaSpmm (include/wmma_spmm.cuh:7-29, path = VS_PATH_TENSOR) and spmm::cudaSpmm
+ * (include/cuda_spmm.cuh:7-29, path = VS_PATH_CUDA_CORE).
+ *
+ *   C[(i*V+v)*k + l] = sum_{j in row i} values[j*V+v] * rhs[col_indices[j]*k + l],  every row of C written
+ *   (vector-rows without nonzeros produce zeros).
+ *
+ * (in_dtype, out_dtype): (F16,F16), (F16,F32) on both paths; (F32,F32) on VS_PATH_CUDA_CORE only (the
+ * reference's float wmmaSpmm prints "doesn't support" and computes nothing, src/wmma_spmm.cu:412-422; here it
+ * returns VS_ERR_DTYPE).  fp16 products are accumulated in fp32.
+ * vec_length: {2,4,8} on the tensor path, {1,2,4,8} on the CUDA-core path, else VS_ERR_VEC_LENGTH.
+ * k (dense width): tensor path needs k % 64 == 0 (as the reference, src/wmma_spmm.cu:327,396); CUDA-core path
+ * needs k % 8 == 0 for fp16 and k % 4 == 0 for fp32.  values, rhs, out must be 16-byte aligned.
+ * ---------------------------------------------------------------------------------------------------- */
+int vs_spmm(int path, int in_dtype, int out_dtype, int m_vec, int vec_length, int k, int n,
+            const int32_t *row_indices, const int32_t *row_offsets, const int32_t *col_indices,
+            const void *values, const void *rhs_matrix, void *output_matrix, void *stream);
+
+/* `batch` independent products that share one CVSE structure (row_indices/row_offsets/col_indices) and differ
+ * in values, rhs and output, found at element strides stride_values / stride_rhs / stride_out from the first
+ * (a stride of 0 shares that operand; stride_out must not be 0).  Strides must keep 16-byte alignment.
+ * One launch covers the whole batch.  The reference has no batched call; this is the batch x head form of its
+ * SpMM for fixed-mask sparse attention. */
+int vs_spmm_batched(int path, int in_dtype, int out_dtype, int m_vec, int vec_length, int k, int n,
+                    const int32_t *row_indices, const int32_t *row_offsets, const int32_t *col_indices,
+                    const void *values, const void *rhs_matrix, void *output_matrix, int batch,
+                    int64_t stride_values, int64_t stride_rhs, int64_t stride_out, void *stream);
+
+/* ------------------------------------------------------------------------------------------------------
+ * SDDMM.  Replaces sddmm::wmmaSddmm (include/wmma_sddmm.cuh:7-33, path = VS_PATH_TENSOR) and
+ * sddmm::cudaSddmm (include/cuda_sddmm.cuh:7-32, path = VS_PATH_CUDA_CORE; `algorithm` ignored).
+ *
+ *   out[j*V+v] = sum_l lhs[(i*V+v)*k + l] * rhs[col_indices[j]*k + l]   for row_offsets[i] <= j < row_offsets[i+1]
+ *
+ * Exactly nonzeros_vec*V outputs are written; the structure arrays are read-only.
+ * (in_dtype, out_dtype): (F16,F16), (F16,F32).  (F32,F32) is VS_ERR_DTYPE on both paths (the reference prints
+ * "doesn't support", src/cuda_sddmm.cu:1333-1344, src/wmma_sddmm.cu:3204-3215).
+ * k (contraction length): tensor path needs k % 64 == 0 (the reference's main loop, src/wmma_sddmm.cu:147);
+ * CUDA-core path needs k % 8 == 0.
+ * algorithm: 0..3 accepted on the tensor path and all computed by the same kernel — in the reference they are
+ * implementation variants of one function, and variant 3 returns deliberately wrong values
+ * (src/wmma_sddmm.cu:769-771); here it returns correct ones.  Other values: VS_ERR_ARG.
+ * ---------------------------------------------------------------------------------------------------- */
+int vs_sddmm(int path, int in_dtype, int out_dtype, int m_vec, int k, int n, int nonzeros_vec,
+             const int32_t *row_indices, const int32_t *row_offsets, const int32_t *col_indices,
+             const void *lhs_matrix, const void *rhs_matrix, void *output_values, int vec_length,
+             void *stream, int algorithm);
+
+/* Batched twin: shared structure; lhs, rhs, out at element strides (stride_out must not be 0). */
+int vs_sddmm_batched(int path, int in_dtype, int out_dtype, int m_vec, int k, int n, int nonzeros_vec,
+                     const int32_t *row_indices, const int32_t *row_offsets, const int32_t *col_indices,
+                     const void *lhs_matrix, const void *rhs_matrix, void *output_values, int vec_length,
+                     int batch, int64_t stride_lhs, int64_t stride_rhs, int64_t stride_out, void *stream,
+                     int algorithm);
+
+/* ------------------------------------------------------------------------------------------------------
+ * Masked row softmax over CVSE values, in place or out of place (probs may equal scores):
+ *   probs[j*V+v] = exp(scale*scores[j*V+v] - max) / sum,  max and sum over the entries j of vector-row i.
+ * fp32 arithmetic; dtype is VS_F16 or VS_F32 for both arrays.  No counterpart in the reference (its README
+ * points to an external repository for attention); it is the step between SDDMM and SpMM in fixed-mask
+ * sparse attention.
+ * ---------------------------------------------------------------------------------------------------- */
+int vs_softmax_cvse(int dtype, int m_vec, int vec_length, const int32_t *row_indices,
+                    const int32_t *row_offsets, const void *scores, void *probs, float scale, int batch,
+                    int64_t stride, void *stream);
+
+/* Fixed-mask sparse attention for `batch` (batch x head) problems sharing one mask:
+ *   O_b = softmax(scale * SDDMM(Q_b, K_b)) . V_b, fp16 in and out, head dimension d (d % 64 == 0).
+ * q [batch][m][d], kmat / vmat [batch][n][d], out [batch][m][d], all contiguous.
+ * `workspace` must hold batch * nonzeros_vec * V fp16 values (the probabilities); the caller owns it.
+ * Enqueues three kernels on `stream`. */
+int vs_attention_cvse(int path, int m_vec, int vec_length, int n, int d, int nonzeros_vec,
+                      const int32_t *row_indices, const int32_t *row_offsets, const int32_t *col_indices,
+                      const void *q, const void *kmat, const void *vmat, void *out, void *workspace,
+                      float scale, int batch, void *stream);
+
+/* ------------------------------------------------------------------------------------------------------
+ * Host-buffer convenience forms (every pointer is a HOST pointer).  They allocate device buffers, copy the
+ * operands in, run the operator, copy the result back and free the buffers, synchronising before returning:
+ * what the reference drivers do around their kernel call (spmm_benchmark.cpp:100-216,
+ * sddmm_benchmark.cpp:222-283).
+ * ---------------------------------------------------------------------------------------------------- */
+int vs_spmm_host(int path, int in_dtype, int out_dtype, int m_vec, int vec_length, int k, int n,
+                 const int32_t *row_indices, const int32_t *row_offsets, const int32_t *col_indices,
+                 const void *values, const void *rhs_matrix, void *output_matrix);
+
+int vs_sddmm_host(int path, int in_dtype, int out_dtype, int m_vec, int k, int n, int nonzeros_vec,
+                  const int32_t *row_indices, const int32_t *row_offsets, const int32_t *col_indices,
+                  const void *lhs_matrix, const void *rhs_matrix, void *output_values, int vec_length,
+                  int algorithm);
+
+/* ------------------------------------------------------------------------------------------------------
+ * Device status.  Kernels that wait on hardware barriers bound every wait; one that ran out records a code
+ * in a per-device status word instead of hanging.  Reads the word of the current device (synchronises the
+ * device), optionally clearing it.  0 = no kernel ever gave up.
+ * ---------------------------------------------------------------------------------------------------- */
+int vs_device_status(int clear, uint32_t *status);
+
+/* ------------------------------------------------------------------------------------------------------
+ * Tensor-core encoding self-test (diagnostic; no counterpart in the reference).  Copies `image_bytes` of a
+ * caller-built shared-memory image (device pointer) to the start of a 1024-byte aligned buffer, issues n_mma
+ * tcgen05.mma kind::f16 instructions with the given 64-bit (A, B) descriptor pairs — their start-address field
+ * relative to the image — accumulating into one tile, and copies the accumulator, pre-filled with `fill`, to
+ * out[lane * ncols + col] (128 lanes, ncols a multiple of 8, at most 64).  Lets the host confirm an operand
+ * layout convention against a plain matrix product before trusting a kernel built on it.
+ * ---------------------------------------------------------------------------------------------------- */
+int vs_selftest_mma(const void *image, int image_bytes, const uint64_t *descs, int n_mma, uint32_t idesc,
+                    int ncols, float fill, float *out, void *stream);
+
+/* ------------------------------------------------------------------------------------------------------
+ * CVSE builder, row swizzle and generators — HOST functions on HOST arrays.
+ * ---------------------------------------------------------------------------------------------------- */
+
+/* Checks a CVSE structure: row_offsets[0]==0, non-decreasing, row_offsets[m_vec]==nonzeros_vec, every
+ * column in [0, n).  Returns VS_OK or VS_ERR_STRUCTURE. */
+int vs_cvse_validate(int m_vec, int n, int nonzeros_vec, const int32_t *row_offsets,
+                     const int32_t *col_indices);
+
+/* mode 0: identity (IdentityRowSwizzle, include/bm_test_utils.h:196-198).
+ * mode 1: vector-rows by nonzero count, descending (SortedRowSwizzle, :200-215); ties by ascending index. */
+int vs_row_swizzle(int mode, int m_vec, const int32_t *row_offsets, int32_t *row_indices);
+
+/* .smtx pattern files (spmm_benchmark.cpp:21-54): line 1 "rows, cols, nnz"; line 2 rows+1 offsets; line 3 nnz
+ * column indices.  The header call returns the three sizes; the body call fills caller arrays of
+ * rows+1 and nnz ints. */
+int vs_smtx_read_header(const char *path, int *rows, int *cols, int *nnz);
+int vs_smtx_read(const char *path, int rows, int nnz, int32_t *row_offsets, int32_t *col_indices);
+int vs_smtx_write(const char *path, int rows, int cols, int nnz, const int32_t *row_offsets,
+                  const int32_t *col_indices);
+
+/* Dense 0/1 mask [m_vec x n] (one byte per vector slot) -> CVSE structure.  Pass col_indices == NULL to
+ * count only (row_offsets is still filled).  Returns nonzeros_vec or a negative error. */
+int vs_cvse_from_dense_mask(int m_vec, int n, const uint8_t *mask, int32_t *row_offsets,
+                            int32_t *col_indices);
+
+/* Seeded pattern generators; two-call protocol: col_indices == NULL fills row_offsets and returns nnz_vec,
+ * the second call (same arguments) fills col_indices too.  Columns ascend within a row.
+ *   kind 0 "fixed"  : every vector-row gets exactly round((1-sparsity)*n) columns, uniform without replacement
+ *   kind 1 "beta"   : row density = clip(2*(1-sparsity)*beta_i, 0, 1), beta_i ~ Beta(2,2); columns as above
+ *   kind 2 "uniform": exactly round(m_vec*n*(1-sparsity)) slots uniform over the whole m_vec x n grid
+ *                     (the recipe of MakeSparseMatrixRandomUniform, include/bm_test_utils.h:70-127)
+ *   kind 3 "band"   : attention mask: a band of `band` columns centred on the vector-row's diagonal position
+ *                     plus random columns on a stride-16 lattice until the row holds round((1-sparsity)*n)
+ */
+int vs_cvse_generate(int kind, uint64_t seed, int m_vec, int n, int vec_length, double sparsity, int band,
+                     int32_t *row_offsets, int32_t *col_indices);
+
+/* Seeded value generators (counter-based, identical on every platform).
+ *   dist 0: uniform(-1, 1)  (the law of MakeDenseMatrix, include/bm_test_utils.h:130-142)
+ *   dist 1: normal(0, sigma)
+ * dtype VS_F32 writes floats; VS_F16 writes the fp32 draw rounded to nearest-even fp16. */
+int vs_fill_random(int dtype, int dist, uint64_t seed, double sigma, int64_t count, void *out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VSPARSE_B200_H */

@@ -1,0 +1,222 @@
+"""ctypes front end of the CPU oracle (TEST INFRASTRUCTURE ONLY).
+
+Only the tests, the smoke entry and the benchmark's CPU-baseline legs import this module; the shipped
+package never does.  `lib()` is the plain-C restatement (oracle/vs_oracle.c); `ref()` is the reference's
+own host verification code compiled by `make -C oracle ref`, or None where that library is not present.
+
+All arrays are numpy; fp16 data travel as float16 arrays (their 16-bit patterns are passed through).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+_REF = None
+_REF_TRIED = False
+
+_I32P = C.POINTER(C.c_int)
+_F32P = C.POINTER(C.c_float)
+_F64P = C.POINTER(C.c_double)
+_U16P = C.POINTER(C.c_uint16)
+
+
+def build(ref: bool = False) -> None:
+    """Compile the oracle (and, with ref=True and a reference checkout present, the reference shim)."""
+    subprocess.run(["make", "-C", _HERE, "all"], check=True, capture_output=True)
+    if ref:
+        subprocess.run(["make", "-C", _HERE, "ref"], check=True, capture_output=True)
+
+
+def lib() -> C.CDLL:
+    global _LIB
+    if _LIB is None:
+        path = os.path.join(_HERE, "libvs_oracle.so")
+        src = os.path.join(_HERE, "vs_oracle.c")
+        if not os.path.exists(path) or os.path.getmtime(path) < os.path.getmtime(src):
+            build()
+        _LIB = C.CDLL(path)
+    return _LIB
+
+
+def ref():
+    """The compiled reference host code, or None if oracle/_ref/libvsref.so has not been built."""
+    global _REF, _REF_TRIED
+    if not _REF_TRIED:
+        _REF_TRIED = True
+        path = os.path.join(_HERE, "_ref", "libvsref.so")
+        if os.path.exists(path):
+            _REF = C.CDLL(path)
+    return _REF
+
+
+def num_threads() -> int:
+    return int(lib().vso_num_threads())
+
+
+def _i32(a):
+    a = np.ascontiguousarray(a, dtype=np.int32)
+    return a, a.ctypes.data_as(_I32P)
+
+
+def _f32(a):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    return a, a.ctypes.data_as(_F32P)
+
+
+def _h16(a):
+    a = np.ascontiguousarray(a, dtype=np.float16)
+    return a, a.ctypes.data_as(_U16P)
+
+
+def spmm(m_vec, V, N, row_offsets, col_indices, values, B, acc="f64", threads=1):
+    """C = A(CVSE) @ B.  acc='f32' is the reference loop (spmm_benchmark.cpp:66-86); 'f64' the parity reference.
+
+    float16 inputs with acc='f32' run the half-precision driver's loop (promotion per use)."""
+    ro, rop = _i32(row_offsets)
+    ci, cip = _i32(col_indices)
+    M = m_vec * V
+    if acc == "f64":
+        v, vp = _f32(np.asarray(values, dtype=np.float32))
+        b, bp = _f32(np.asarray(B, dtype=np.float32))
+        out = np.empty((M, N), dtype=np.float64)
+        lib().vso_spmm_f64(m_vec, V, N, rop, cip, vp, bp, out.ctypes.data_as(_F64P), threads)
+        return out
+    out = np.empty((M, N), dtype=np.float32)
+    if np.asarray(values).dtype == np.float16:
+        v, vp = _h16(values)
+        b, bp = _h16(B)
+        lib().vso_spmm_h16(m_vec, V, N, rop, cip, vp, bp, out.ctypes.data_as(_F32P), threads)
+    else:
+        v, vp = _f32(values)
+        b, bp = _f32(B)
+        lib().vso_spmm_f32(m_vec, V, N, rop, cip, vp, bp, out.ctypes.data_as(_F32P), threads)
+    return out
+
+
+def sddmm(m_vec, k, V, row_offsets, col_indices, lhs, rhs, acc="f64", threads=1):
+    """out[j*V+v] = <lhs[i*V+v], rhs[col[j]]>.  acc='f32' is Host_sddmm (bm_test_utils.h:171-193)."""
+    ro, rop = _i32(row_offsets)
+    ci, cip = _i32(col_indices)
+    nnz = int(ro[m_vec]) * V
+    if acc == "f64":
+        a, ap = _f32(np.asarray(lhs, dtype=np.float32))
+        b, bp = _f32(np.asarray(rhs, dtype=np.float32))
+        out = np.empty(nnz, dtype=np.float64)
+        lib().vso_sddmm_f64(m_vec, k, V, rop, cip, ap, bp, out.ctypes.data_as(_F64P), threads)
+        return out
+    out = np.empty(nnz, dtype=np.float32)
+    if np.asarray(lhs).dtype == np.float16:
+        a, ap = _h16(lhs)
+        b, bp = _h16(rhs)
+        lib().vso_sddmm_h16(m_vec, k, V, rop, cip, ap, bp, out.ctypes.data_as(_F32P), threads)
+    else:
+        a, ap = _f32(lhs)
+        b, bp = _f32(rhs)
+        lib().vso_sddmm_f32(m_vec, k, V, rop, cip, ap, bp, out.ctypes.data_as(_F32P), threads)
+    return out
+
+
+def row_swizzle(mode, m_vec, row_offsets):
+    """mode 0 identity, 1 sorted by row length descending (ties by index) — bm_test_utils.h:196-215."""
+    ro, rop = _i32(row_offsets)
+    out = np.empty(m_vec, dtype=np.int32)
+    rc = lib().vso_row_swizzle(int(mode), m_vec, rop, out.ctypes.data_as(_I32P))
+    if rc != 0:
+        raise ValueError(f"vso_row_swizzle failed: {rc}")
+    return out
+
+
+def softmax(m_vec, V, row_offsets, scores, scale):
+    ro, rop = _i32(row_offsets)
+    s, sp = _f32(np.asarray(scores, dtype=np.float32))
+    out = np.empty(s.shape, dtype=np.float64)
+    lib().vso_softmax_f64(m_vec, V, rop, sp, C.c_double(scale), out.ctypes.data_as(_F64P))
+    return out
+
+
+def attention(m_vec, V, d, dv, row_offsets, col_indices, Q, K, Vm, scale):
+    ro, rop = _i32(row_offsets)
+    ci, cip = _i32(col_indices)
+    q, qp = _f32(np.asarray(Q, dtype=np.float32))
+    k, kp = _f32(np.asarray(K, dtype=np.float32))
+    v, vp = _f32(np.asarray(Vm, dtype=np.float32))
+    out = np.empty((m_vec * V, dv), dtype=np.float64)
+    scratch = np.empty(2 * int(ro[m_vec]) * V, dtype=np.float64)
+    lib().vso_attention_f64(m_vec, V, d, dv, rop, cip, qp, kp, vp, C.c_double(scale),
+                            out.ctypes.data_as(_F64P), scratch.ctypes.data_as(_F64P))
+    return out
+
+
+def f32_to_h16(a):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    out = np.empty(a.shape, dtype=np.float16)
+    lib().vso_f32_to_h16(a.ctypes.data_as(_F32P), out.ctypes.data_as(_U16P), C.c_int64(a.size))
+    return out
+
+
+def h16_to_f32(a):
+    a = np.ascontiguousarray(a, dtype=np.float16)
+    out = np.empty(a.shape, dtype=np.float32)
+    lib().vso_h16_to_f32(a.ctypes.data_as(_U16P), out.ctypes.data_as(_F32P), C.c_int64(a.size))
+    return out
+
+
+# ---- the reference's own host code (present only where `make -C oracle ref` ran) ---------------------
+
+def ref_spmm(m_vec, V, N, row_offsets, col_indices, values, B):
+    r = ref()
+    ro, rop = _i32(row_offsets)
+    ci, cip = _i32(col_indices)
+    out = np.empty((m_vec * V, N), dtype=np.float32)
+    if np.asarray(values).dtype == np.float16:
+        v, vp = _h16(values)
+        b, bp = _h16(B)
+        r.ref_spmm_host_h16(m_vec, V, N, rop, cip, vp, bp, out.ctypes.data_as(_F32P))
+    else:
+        v, vp = _f32(values)
+        b, bp = _f32(B)
+        r.ref_spmm_host_f32(m_vec, V, N, rop, cip, vp, bp, out.ctypes.data_as(_F32P))
+    return out
+
+
+def ref_sddmm(m_vec, k, V, row_offsets, col_indices, lhs, rhs, out16=False):
+    r = ref()
+    ro, rop = _i32(row_offsets)
+    ci, cip = _i32(col_indices)
+    nnz = int(ro[m_vec]) * V
+    if np.asarray(lhs).dtype == np.float16:
+        a, ap = _h16(lhs)
+        b, bp = _h16(rhs)
+        if out16:
+            out = np.empty(nnz, dtype=np.float16)
+            r.ref_sddmm_host_h16_out16(m_vec, k, V, rop, cip, ap, bp, out.ctypes.data_as(_U16P))
+            return out
+        out = np.empty(nnz, dtype=np.float32)
+        r.ref_sddmm_host_h16(m_vec, k, V, rop, cip, ap, bp, out.ctypes.data_as(_F32P))
+        return out
+    a, ap = _f32(lhs)
+    b, bp = _f32(rhs)
+    out = np.empty(nnz, dtype=np.float32)
+    r.ref_sddmm_host_f32(m_vec, k, V, rop, cip, ap, bp, out.ctypes.data_as(_F32P))
+    return out
+
+
+def ref_row_swizzle(sorted_, m_vec, row_offsets):
+    ro, rop = _i32(row_offsets)
+    out = np.empty(m_vec, dtype=np.int32)
+    ref().ref_row_swizzle(int(bool(sorted_)), m_vec, rop, out.ctypes.data_as(_I32P))
+    return out
+
+
+def ref_make_dense(rows, cols, dtype=np.float32):
+    out = np.empty((rows, cols), dtype=dtype)
+    if dtype == np.float16:
+        ref().ref_make_dense_h16(rows, cols, out.ctypes.data_as(_U16P))
+    else:
+        ref().ref_make_dense_f32(rows, cols, out.ctypes.data_as(_F32P))
+    return out

@@ -1,0 +1,305 @@
+/*
+ * CPU oracle for column-vector-sparse (CVSE) SpMM / SDDMM / masked row softmax.
+ *
+ * TEST INFRASTRUCTURE ONLY.  Nothing in the shipped library links or calls this file; it is the
+ * checker that the tests, the smoke entry and the benchmark's CPU-baseline leg compare the CUDA
+ * kernels against.
+ *
+ * Every function restates, in plain C, a loop of the vectorSparse reference:
+ *   - vso_spmm_f32         : host SpMM loop, spmm_benchmark.cpp:66-86 (order i -> j -> v -> l, fp32 "+=")
+ *   - vso_sddmm_f32        : Host_sddmm, include/bm_test_utils.h:171-193 (fp32 accumulator per output)
+ *   - vso_row_swizzle      : IdentityRowSwizzle / SortedRowSwizzle, include/bm_test_utils.h:196-215
+ *   - *_f64 variants       : the same loops with a double accumulator (the parity reference for the
+ *                            stated tolerances rel-L2 <= 5e-3, max-abs <= 2e-2)
+ *   - vso_softmax_f64,
+ *     vso_attention_f64    : masked row softmax and SDDMM -> softmax -> SpMM.  The reference has no code
+ *                            for these (README.md:76 points to an external repository), so they are
+ *                            defined here and PARITY IS UNPINNED for them.
+ *
+ * Pinning: vso_sddmm_f32 and vso_row_swizzle are checked bit-for-bit against the reference's own
+ * Host_sddmm / SortedRowSwizzle compiled from the reference header, and vso_spmm_f32 against the
+ * reference driver's inline loop compiled in place (see oracle/Makefile, oracle/ref_shim.cpp);
+ * committed golden vectors hold their outputs.
+ *
+ * CVSE layout (spmm_benchmark.cpp:26-60,79-81): m_vec vector-rows of V real rows each;
+ * row_offsets[m_vec+1] counts nonzero column VECTORS; col_indices[nnz_vec]; values[j*V+v] is the
+ * element in real row i*V+v, column col_indices[j].
+ *
+ * fp16 data are passed as raw uint16 bit patterns ("h16") and promoted to float exactly, which is
+ * what `(float)half` does in the reference loops.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define VSO_API __attribute__((visibility("default")))
+
+/* ---- fp16 <-> fp32, exact, no hardware dependency ------------------------------------------------ */
+
+static inline float h16_to_f32(uint16_t h) {
+    uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    uint32_t exp = (h >> 10) & 0x1fu;
+    uint32_t man = h & 0x3ffu;
+    uint32_t bits;
+    if (exp == 0) {
+        if (man == 0) {
+            bits = sign;
+        } else { /* subnormal: renormalise */
+            int e = -1;
+            do { man <<= 1; ++e; } while (!(man & 0x400u));
+            man &= 0x3ffu;
+            bits = sign | ((uint32_t)(127 - 15 - e) << 23) | (man << 13);
+        }
+    } else if (exp == 31) {
+        bits = sign | 0x7f800000u | (man << 13);
+    } else {
+        bits = sign | ((exp + 127 - 15) << 23) | (man << 13);
+    }
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+/* round-to-nearest-even, the conversion `(half)float` performs */
+static inline uint16_t f32_to_h16(float f) {
+    uint32_t x;
+    memcpy(&x, &f, 4);
+    uint32_t sign = (x >> 16) & 0x8000u;
+    uint32_t ax = x & 0x7fffffffu;
+    if (ax >= 0x7f800000u) { /* inf / nan */
+        return (uint16_t)(sign | 0x7c00u | ((ax > 0x7f800000u) ? 0x200u : 0));
+    }
+    if (ax >= 0x477ff000u) { /* rounds to >= 65520 -> inf */
+        return (uint16_t)(sign | 0x7c00u);
+    }
+    if (ax < 0x33000001u) { /* < 2^-25 (or exactly 2^-25, ties to even 0) */
+        return (uint16_t)sign;
+    }
+    int32_t e = (int32_t)(ax >> 23) - 127;
+    uint32_t man = (ax & 0x7fffffu) | 0x800000u;
+    if (e < -14) { /* subnormal half */
+        int shift = -14 - e + 13; /* bits dropped */
+        uint32_t q = man >> shift;
+        uint32_t rem = man & ((1u << shift) - 1u);
+        uint32_t half = 1u << (shift - 1);
+        if (rem > half || (rem == half && (q & 1u))) ++q;
+        return (uint16_t)(sign | q);
+    }
+    uint32_t q = ((uint32_t)(e + 15) << 10) | ((man >> 13) & 0x3ffu);
+    uint32_t rem = man & 0x1fffu;
+    if (rem > 0x1000u || (rem == 0x1000u && (q & 1u))) ++q; /* carry may bump the exponent: fine */
+    return (uint16_t)(sign | q);
+}
+
+VSO_API void vso_h16_to_f32(const uint16_t *src, float *dst, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) dst[i] = h16_to_f32(src[i]);
+}
+
+VSO_API void vso_f32_to_h16(const float *src, uint16_t *dst, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) dst[i] = f32_to_h16(src[i]);
+}
+
+VSO_API int vso_num_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+/* ---- SpMM: C[M x N] = A(CVSE, M x K) * B[K x N]  (spmm_benchmark.cpp:66-86) ----------------------- */
+
+/* fp32 data, fp32 accumulate, sequential: the loop exactly as the reference driver runs it.
+ * threads <= 1 keeps the reference's single thread; threads > 1 splits vector-rows across OpenMP
+ * threads (rows are independent, so every output element still sees the same addition order). */
+VSO_API void vso_spmm_f32(int m_vec, int V, int N, const int *row_offsets, const int *col_indices,
+                          const float *values, const float *B, float *C, int threads) {
+    memset(C, 0, sizeof(float) * (size_t)m_vec * V * N);
+#pragma omp parallel for schedule(dynamic, 4) num_threads(threads > 1 ? threads : 1)
+    for (int i = 0; i < m_vec; ++i) {
+        for (int j = row_offsets[i]; j < row_offsets[i + 1]; ++j) {
+            int col = col_indices[j];
+            for (int v = 0; v < V; ++v) {
+                float a = values[(size_t)j * V + v];
+                float *c = C + ((size_t)i * V + v) * N;
+                const float *b = B + (size_t)col * N;
+                for (int l = 0; l < N; ++l) c[l] += a * b[l];
+            }
+        }
+    }
+}
+
+/* fp16 bit patterns in, promoted to float per use, fp32 accumulate (the mixed==1 driver). */
+VSO_API void vso_spmm_h16(int m_vec, int V, int N, const int *row_offsets, const int *col_indices,
+                          const uint16_t *values, const uint16_t *B, float *C, int threads) {
+    memset(C, 0, sizeof(float) * (size_t)m_vec * V * N);
+#pragma omp parallel for schedule(dynamic, 4) num_threads(threads > 1 ? threads : 1)
+    for (int i = 0; i < m_vec; ++i) {
+        for (int j = row_offsets[i]; j < row_offsets[i + 1]; ++j) {
+            int col = col_indices[j];
+            for (int v = 0; v < V; ++v) {
+                float a = h16_to_f32(values[(size_t)j * V + v]);
+                float *c = C + ((size_t)i * V + v) * N;
+                const uint16_t *b = B + (size_t)col * N;
+                for (int l = 0; l < N; ++l) c[l] += a * h16_to_f32(b[l]);
+            }
+        }
+    }
+}
+
+/* double accumulator: the parity reference. */
+VSO_API void vso_spmm_f64(int m_vec, int V, int N, const int *row_offsets, const int *col_indices,
+                          const float *values, const float *B, double *C, int threads) {
+    memset(C, 0, sizeof(double) * (size_t)m_vec * V * N);
+#pragma omp parallel for schedule(dynamic, 4) num_threads(threads > 1 ? threads : 1)
+    for (int i = 0; i < m_vec; ++i) {
+        for (int j = row_offsets[i]; j < row_offsets[i + 1]; ++j) {
+            int col = col_indices[j];
+            for (int v = 0; v < V; ++v) {
+                double a = (double)values[(size_t)j * V + v];
+                double *c = C + ((size_t)i * V + v) * N;
+                const float *b = B + (size_t)col * N;
+                for (int l = 0; l < N; ++l) c[l] += a * (double)b[l];
+            }
+        }
+    }
+}
+
+/* ---- SDDMM: out[j*V+v] = <lhs[i*V+v, :], rhs[col[j], :]>  (bm_test_utils.h:171-193) --------------- */
+
+VSO_API void vso_sddmm_f32(int m_vec, int k, int V, const int *row_offsets, const int *col_indices,
+                           const float *lhs, const float *rhs, float *out, int threads) {
+#pragma omp parallel for schedule(dynamic, 4) num_threads(threads > 1 ? threads : 1)
+    for (int i = 0; i < m_vec; ++i) {
+        for (int j = row_offsets[i]; j < row_offsets[i + 1]; ++j) {
+            for (int v = 0; v < V; ++v) {
+                float acc = 0.0f;
+                const float *a = lhs + ((size_t)i * V + v) * k;
+                const float *b = rhs + (size_t)col_indices[j] * k;
+                for (int l = 0; l < k; ++l) acc += a[l] * b[l];
+                out[(size_t)j * V + v] = acc;
+            }
+        }
+    }
+}
+
+VSO_API void vso_sddmm_h16(int m_vec, int k, int V, const int *row_offsets, const int *col_indices,
+                           const uint16_t *lhs, const uint16_t *rhs, float *out, int threads) {
+#pragma omp parallel for schedule(dynamic, 4) num_threads(threads > 1 ? threads : 1)
+    for (int i = 0; i < m_vec; ++i) {
+        for (int j = row_offsets[i]; j < row_offsets[i + 1]; ++j) {
+            for (int v = 0; v < V; ++v) {
+                float acc = 0.0f;
+                const uint16_t *a = lhs + ((size_t)i * V + v) * k;
+                const uint16_t *b = rhs + (size_t)col_indices[j] * k;
+                for (int l = 0; l < k; ++l) acc += h16_to_f32(a[l]) * h16_to_f32(b[l]);
+                out[(size_t)j * V + v] = acc;
+            }
+        }
+    }
+}
+
+VSO_API void vso_sddmm_f64(int m_vec, int k, int V, const int *row_offsets, const int *col_indices,
+                           const float *lhs, const float *rhs, double *out, int threads) {
+#pragma omp parallel for schedule(dynamic, 4) num_threads(threads > 1 ? threads : 1)
+    for (int i = 0; i < m_vec; ++i) {
+        for (int j = row_offsets[i]; j < row_offsets[i + 1]; ++j) {
+            for (int v = 0; v < V; ++v) {
+                double acc = 0.0;
+                const float *a = lhs + ((size_t)i * V + v) * k;
+                const float *b = rhs + (size_t)col_indices[j] * k;
+                for (int l = 0; l < k; ++l) acc += (double)a[l] * (double)b[l];
+                out[(size_t)j * V + v] = acc;
+            }
+        }
+    }
+}
+
+/* ---- row swizzle (bm_test_utils.h:196-215) ------------------------------------------------------- */
+
+typedef struct { int len; int idx; } vso_rowlen;
+
+static int cmp_rowlen_desc(const void *pa, const void *pb) {
+    const vso_rowlen *a = (const vso_rowlen *)pa, *b = (const vso_rowlen *)pb;
+    if (a->len != b->len) return (a->len > b->len) ? -1 : 1; /* longer rows first */
+    return (a->idx > b->idx) - (a->idx < b->idx);            /* ties by index: a stable order */
+}
+
+/* mode 0: identity; mode 1: argsort by row length, descending.  The reference sorts with an unstable
+ * std::sort, so its tie order is unspecified; ties are broken here by ascending row index. */
+VSO_API int vso_row_swizzle(int mode, int m_vec, const int *row_offsets, int *row_indices) {
+    if (mode == 0) {
+        for (int i = 0; i < m_vec; ++i) row_indices[i] = i;
+        return 0;
+    }
+    if (mode != 1) return -1;
+    vso_rowlen *tmp = (vso_rowlen *)malloc(sizeof(vso_rowlen) * (size_t)(m_vec > 0 ? m_vec : 1));
+    if (!tmp) return -2;
+    for (int i = 0; i < m_vec; ++i) {
+        tmp[i].len = row_offsets[i + 1] - row_offsets[i];
+        tmp[i].idx = i;
+    }
+    qsort(tmp, (size_t)m_vec, sizeof(vso_rowlen), cmp_rowlen_desc);
+    for (int i = 0; i < m_vec; ++i) row_indices[i] = tmp[i].idx;
+    free(tmp);
+    return 0;
+}
+
+/* ---- masked row softmax over CVSE values (no reference code: parity unpinned) -------------------- */
+
+/* For every real row r = i*V+v: p[j*V+v] = exp(scale*s[j*V+v] - max_j) / sum_j exp(...), j over the
+ * entries of vector-row i.  Rows without entries produce nothing. */
+VSO_API void vso_softmax_f64(int m_vec, int V, const int *row_offsets, const float *scores, double scale,
+                             double *probs) {
+    for (int i = 0; i < m_vec; ++i) {
+        int b = row_offsets[i], e = row_offsets[i + 1];
+        for (int v = 0; v < V; ++v) {
+            double mx = -INFINITY;
+            for (int j = b; j < e; ++j) {
+                double s = scale * (double)scores[(size_t)j * V + v];
+                if (s > mx) mx = s;
+            }
+            double sum = 0.0;
+            for (int j = b; j < e; ++j) sum += exp(scale * (double)scores[(size_t)j * V + v] - mx);
+            for (int j = b; j < e; ++j)
+                probs[(size_t)j * V + v] = exp(scale * (double)scores[(size_t)j * V + v] - mx) / sum;
+        }
+    }
+}
+
+/* One head of fixed-mask sparse attention in double: SDDMM(Q, K) -> softmax(scale) -> SpMM(P, Vm).
+ * Q [M x d], Kmat [n x d], Vmat [n x dv], O [M x dv]; the probabilities are kept in double (no fp16
+ * rounding of the intermediate), scratch must hold 2*nnz_vec*V doubles. */
+VSO_API void vso_attention_f64(int m_vec, int V, int d, int dv, const int *row_offsets,
+                               const int *col_indices, const float *Q, const float *Kmat, const float *Vmat,
+                               double scale, double *O, double *scratch) {
+    int nnz_vec = row_offsets[m_vec];
+    double *s = scratch;
+    double *p = scratch + (size_t)nnz_vec * V;
+    vso_sddmm_f64(m_vec, d, V, row_offsets, col_indices, Q, Kmat, s, 1);
+    for (int i = 0; i < m_vec; ++i) {
+        int b = row_offsets[i], e = row_offsets[i + 1];
+        for (int v = 0; v < V; ++v) {
+            double mx = -INFINITY, sum = 0.0;
+            for (int j = b; j < e; ++j) {
+                double x = scale * s[(size_t)j * V + v];
+                if (x > mx) mx = x;
+            }
+            for (int j = b; j < e; ++j) sum += exp(scale * s[(size_t)j * V + v] - mx);
+            for (int j = b; j < e; ++j) p[(size_t)j * V + v] = exp(scale * s[(size_t)j * V + v] - mx) / sum;
+        }
+    }
+    memset(O, 0, sizeof(double) * (size_t)m_vec * V * dv);
+    for (int i = 0; i < m_vec; ++i)
+        for (int j = row_offsets[i]; j < row_offsets[i + 1]; ++j)
+            for (int v = 0; v < V; ++v) {
+                double a = p[(size_t)j * V + v];
+                double *o = O + ((size_t)i * V + v) * dv;
+                const float *b = Vmat + (size_t)col_indices[j] * dv;
+                for (int l = 0; l < dv; ++l) o[l] += a * (double)b[l];
+            }
+}

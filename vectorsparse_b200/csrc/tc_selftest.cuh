@@ -1,0 +1,89 @@
+// Self-test of the tcgen05 operand encodings: runs a handful of MMAs on a caller-built shared-memory image and
+// returns the raw accumulator, so that the host can check a descriptor / layout convention against a plain
+// matrix product.  Used by the GPU tests; never on a product path.
+#pragma once
+#include "tc_ptx.cuh"
+
+namespace vs {
+namespace tcselftest {
+
+constexpr uint32_t kStatusTimeout = 4u;
+constexpr int kTmemCols = 64;
+
+__device__ __forceinline__ void tmem_st_x8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]),
+                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// image: bytes copied to the 1024-byte aligned start of shared memory.  descs: n_mma pairs (A, B) of 64-bit
+// descriptors whose start-address field is RELATIVE to the image start.  The accumulator (128 lanes x ncols
+// fp32 columns, ncols a multiple of 8 up to 64) is pre-filled with `fill`, so lanes an instruction shape does
+// not write can be told apart, and copied to out[lane * ncols + col].
+__global__ void __launch_bounds__(128) sandbox_kernel(const uint8_t *image, int image_bytes, const uint64_t *descs,
+                                                      int n_mma, uint32_t idesc, int ncols, float fill, float *out,
+                                                      uint32_t *status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = tc::smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *sm = smem_raw + (base - raw);
+    const int padded = (image_bytes + 15) & ~15;
+    const uint32_t bar = base + padded;          // 8-byte mbarrier
+    const uint32_t holder = bar + 8;             // tensor-memory base address
+    const int t = threadIdx.x, warp = t >> 5;
+
+    for (int i = t; i < padded / 16; i += 128) {
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (i * 16 + 16 <= image_bytes) v = reinterpret_cast<const uint4 *>(image)[i];
+        reinterpret_cast<uint4 *>(sm)[i] = v;
+    }
+    if (t == 0) {
+        tc::mbar_init(bar, 1);
+        tc::fence_mbar_init();
+    }
+    if (warp == 0) {
+        tc::tmem_alloc(holder, kTmemCols);
+        tc::tmem_relinquish();
+    }
+    tc::fence_proxy_async();
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    tc::tc_fence_after_sync();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(sm + padded + 8);
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+
+    uint32_t f[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = __float_as_uint(fill);
+    for (int c = 0; c < ncols; c += 8) tmem_st_x8(lane_addr + c, f);
+    tmem_st_wait();
+    tc::tc_fence_before_sync();
+    __syncthreads();
+
+    if (t == 0) {
+        tc::tc_fence_after_sync();
+        for (int i = 0; i < n_mma; ++i) {
+            const uint64_t a = descs[2 * i] + (uint64_t)(base >> 4);
+            const uint64_t b = descs[2 * i + 1] + (uint64_t)(base >> 4);
+            tc::mma_f16_ss(tmem_base, a, b, idesc, i > 0 ? 1u : 0u);
+        }
+        tc::mma_commit(bar);
+    }
+    const bool ok = tc::mbar_wait(bar, 0);
+    tc::tc_fence_after_sync();
+    for (int c = 0; c < ncols; c += 8) {
+        uint32_t r[8];
+        tc::tmem_ld_x8(lane_addr + c, r);
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) out[(size_t)t * ncols + c + i] = __uint_as_float(r[i]);
+    }
+    if (!ok) atomicOr(status, kStatusTimeout);
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tc::tmem_dealloc(tmem_base, kTmemCols);
+}
+
+}  // namespace tcselftest
+}  // namespace vs

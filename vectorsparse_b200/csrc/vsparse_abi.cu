@@ -1,0 +1,426 @@
+// extern "C" entry points of libvsparse_b200: argument validation and kernel dispatch.
+//
+// Each operator entry point checks its arguments on the host, picks the template instantiation for
+// (path, element types, vector length) and enqueues the kernel(s) on the caller's stream.  Nothing here
+// synchronises or allocates, except the *_host convenience forms, which say so.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+
+#include "vsparse_b200.h"
+#include "common.cuh"
+#include "cuda_core.cuh"
+#include "spmm_tc.cuh"
+#include "sddmm_tc.cuh"
+#include "tc_selftest.cuh"
+
+#define VS_EXPORT extern "C" __attribute__((visibility("default")))
+
+namespace {
+
+using namespace vs;
+
+// Per-device status word, OR-ed into by kernels whose bounded waits ran out.
+__device__ uint32_t g_device_status = 0;
+
+constexpr int kMaxDevices = 64;
+struct DeviceInfo {
+    bool ready = false;
+    int sm_count = 0;
+    uint32_t *status = nullptr;
+};
+DeviceInfo g_devices[kMaxDevices];
+std::mutex g_devices_mutex;
+
+int device_info(DeviceInfo **out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return VS_ERR_ARG;
+    std::lock_guard<std::mutex> lock(g_devices_mutex);
+    DeviceInfo &d = g_devices[dev];
+    if (!d.ready) {
+        e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaGetSymbolAddress(reinterpret_cast<void **>(&d.status), g_device_status);
+        if (e != cudaSuccess) return (int)e;
+        d.ready = true;
+    }
+    *out = &d;
+    return VS_OK;
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline bool valid_v(int v) { return v == 1 || v == 2 || v == 4 || v == 8; }
+inline int elem_size(int dtype) { return dtype == VS_F16 ? 2 : 4; }
+inline bool stride_ok(int64_t stride, int dtype) { return stride >= 0 && (stride * elem_size(dtype)) % 16 == 0; }
+
+template <typename K> int set_smem(K kernel, int bytes) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    return e == cudaSuccess ? VS_OK : (int)e;
+}
+
+// ---- SpMM dispatch ----------------------------------------------------------------------------------------
+template <typename TIn, typename TOut, int V> int launch_spmm_cc(const SpmmParams &p, cudaStream_t s) {
+    constexpr int E = Chunk<TIn>::kElems;
+    const int64_t items = (int64_t)p.m_vec * (p.N / E);
+    const int64_t blocks = (items + kCcThreads - 1) / kCcThreads;
+    if (blocks > 0x7fffffffll) return VS_ERR_SHAPE;
+    dim3 grid((unsigned)blocks, (unsigned)p.batch, 1);
+    spmm_cc_kernel<TIn, TOut, V><<<grid, kCcThreads, 0, s>>>(p);
+    return (int)cudaGetLastError();
+}
+
+template <typename TIn, typename TOut> int spmm_cc_by_v(int V, const SpmmParams &p, cudaStream_t s) {
+    switch (V) {
+        case 1: return launch_spmm_cc<TIn, TOut, 1>(p, s);
+        case 2: return launch_spmm_cc<TIn, TOut, 2>(p, s);
+        case 4: return launch_spmm_cc<TIn, TOut, 4>(p, s);
+        case 8: return launch_spmm_cc<TIn, TOut, 8>(p, s);
+    }
+    return VS_ERR_VEC_LENGTH;
+}
+
+template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStream_t s) {
+    DeviceInfo *d;
+    int rc = device_info(&d);
+    if (rc != VS_OK) return rc;
+    auto kernel = tcspmm::spmm_tc_kernel<TOut, V>;
+    rc = set_smem(kernel, tcspmm::kSmemBytes);
+    if (rc != VS_OK) return rc;
+    const int n_tiles = (p.N + tcspmm::kTileN - 1) / tcspmm::kTileN;
+    const int64_t items = (int64_t)p.batch * n_tiles * p.m_vec;
+    const int64_t cap = 2ll * d->sm_count;  // two CTAs fit per SM (shared memory and tensor memory)
+    const unsigned grid = (unsigned)(items < cap ? items : cap);
+    kernel<<<grid, tcspmm::kThreads, tcspmm::kSmemBytes, s>>>(p, d->status);
+    return (int)cudaGetLastError();
+}
+
+template <typename TOut> int spmm_tc_by_v(int V, const SpmmParams &p, cudaStream_t s) {
+    switch (V) {
+        case 2: return launch_spmm_tc<TOut, 2>(p, s);
+        case 4: return launch_spmm_tc<TOut, 4>(p, s);
+        case 8: return launch_spmm_tc<TOut, 8>(p, s);
+    }
+    return VS_ERR_VEC_LENGTH;
+}
+
+// ---- SDDMM dispatch ---------------------------------------------------------------------------------------
+template <typename TIn, typename TOut, int V> int launch_sddmm_cc(const SddmmParams &p, cudaStream_t s) {
+    const int64_t blocks = ((int64_t)p.nnz_vec * 8 + kCcThreads - 1) / kCcThreads;
+    if (blocks > 0x7fffffffll) return VS_ERR_SHAPE;
+    dim3 grid((unsigned)blocks, (unsigned)p.batch, 1);
+    sddmm_cc_kernel<TIn, TOut, V><<<grid, kCcThreads, 0, s>>>(p);
+    return (int)cudaGetLastError();
+}
+
+template <typename TIn, typename TOut> int sddmm_cc_by_v(int V, const SddmmParams &p, cudaStream_t s) {
+    switch (V) {
+        case 1: return launch_sddmm_cc<TIn, TOut, 1>(p, s);
+        case 2: return launch_sddmm_cc<TIn, TOut, 2>(p, s);
+        case 4: return launch_sddmm_cc<TIn, TOut, 4>(p, s);
+        case 8: return launch_sddmm_cc<TIn, TOut, 8>(p, s);
+    }
+    return VS_ERR_VEC_LENGTH;
+}
+
+template <typename TOut, int V> int launch_sddmm_tc(const SddmmParams &p, cudaStream_t s) {
+    DeviceInfo *d;
+    int rc = device_info(&d);
+    if (rc != VS_OK) return rc;
+    auto kernel = tcsddmm::sddmm_tc_kernel<TOut, V>;
+    rc = set_smem(kernel, tcsddmm::kSmemBytes);
+    if (rc != VS_OK) return rc;
+    const int64_t items = (int64_t)p.batch * p.m_vec;
+    const int64_t cap = 2ll * d->sm_count;
+    const unsigned grid = (unsigned)(items < cap ? items : cap);
+    kernel<<<grid, tcsddmm::kThreads, tcsddmm::kSmemBytes, s>>>(p, d->status);
+    return (int)cudaGetLastError();
+}
+
+template <typename TOut> int sddmm_tc_by_v(int V, const SddmmParams &p, cudaStream_t s) {
+    switch (V) {
+        case 2: return launch_sddmm_tc<TOut, 2>(p, s);
+        case 4: return launch_sddmm_tc<TOut, 4>(p, s);
+        case 8: return launch_sddmm_tc<TOut, 8>(p, s);
+    }
+    return VS_ERR_VEC_LENGTH;
+}
+
+template <typename T> int softmax_by_v(int V, const SoftmaxParams &p, cudaStream_t s) {
+    const int64_t blocks = ((int64_t)p.m_vec * 32 + kCcThreads - 1) / kCcThreads;
+    dim3 grid((unsigned)blocks, (unsigned)p.batch, 1);
+    switch (V) {
+        case 1: softmax_cvse_kernel<T, 1><<<grid, kCcThreads, 0, s>>>(p); break;
+        case 2: softmax_cvse_kernel<T, 2><<<grid, kCcThreads, 0, s>>>(p); break;
+        case 4: softmax_cvse_kernel<T, 4><<<grid, kCcThreads, 0, s>>>(p); break;
+        case 8: softmax_cvse_kernel<T, 8><<<grid, kCcThreads, 0, s>>>(p); break;
+        default: return VS_ERR_VEC_LENGTH;
+    }
+    return (int)cudaGetLastError();
+}
+
+constexpr int kMaxBatch = 65535;  // grid.y of the CUDA-core kernels
+
+}  // namespace
+
+// =============================================================================================================
+
+VS_EXPORT int vs_spmm_batched(int path, int in_dtype, int out_dtype, int m_vec, int vec_length, int k, int n,
+                              const int32_t *row_indices, const int32_t *row_offsets, const int32_t *col_indices,
+                              const void *values, const void *rhs_matrix, void *output_matrix, int batch,
+                              int64_t stride_values, int64_t stride_rhs, int64_t stride_out, void *stream) {
+    if (path != VS_PATH_TENSOR && path != VS_PATH_CUDA_CORE) return VS_ERR_ARG;
+    if (path == VS_PATH_TENSOR ? !(vec_length == 2 || vec_length == 4 || vec_length == 8) : !valid_v(vec_length))
+        return VS_ERR_VEC_LENGTH;
+    const bool f16 = (in_dtype == VS_F16) && (out_dtype == VS_F16 || out_dtype == VS_F32);
+    const bool f32 = (in_dtype == VS_F32) && (out_dtype == VS_F32) && path == VS_PATH_CUDA_CORE;
+    if (!f16 && !f32) return VS_ERR_DTYPE;
+    if (m_vec < 0 || k < 0 || n < 0) return VS_ERR_SHAPE;
+    if (batch < 1 || batch > kMaxBatch) return VS_ERR_ARG;
+    if (path == VS_PATH_TENSOR ? (k % 64 != 0) : (k % (in_dtype == VS_F16 ? 8 : 4) != 0)) return VS_ERR_SHAPE;
+    if ((int64_t)m_vec * vec_length > 0x7fffffffll) return VS_ERR_SHAPE;
+    if (m_vec == 0 || k == 0) return VS_OK;
+    if (!row_indices || !row_offsets || !col_indices || !values || !rhs_matrix || !output_matrix) return VS_ERR_NULL;
+    if (!aligned16(values) || !aligned16(rhs_matrix) || !aligned16(output_matrix)) return VS_ERR_ALIGN;
+    if (!stride_ok(stride_values, in_dtype) || !stride_ok(stride_rhs, in_dtype) || !stride_ok(stride_out, out_dtype))
+        return VS_ERR_ALIGN;
+    if (batch > 1 && stride_out == 0) return VS_ERR_ARG;
+
+    SpmmParams p;
+    p.m_vec = m_vec; p.N = k; p.K = n; p.batch = batch;
+    p.row_indices = row_indices; p.row_offsets = row_offsets; p.col_indices = col_indices;
+    p.values = values; p.rhs = rhs_matrix; p.out = output_matrix;
+    p.stride_values = stride_values; p.stride_rhs = stride_rhs; p.stride_out = stride_out;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+    if (path == VS_PATH_TENSOR) {
+        return out_dtype == VS_F16 ? spmm_tc_by_v<__half>(vec_length, p, s) : spmm_tc_by_v<float>(vec_length, p, s);
+    }
+    if (in_dtype == VS_F32) return spmm_cc_by_v<float, float>(vec_length, p, s);
+    return out_dtype == VS_F16 ? spmm_cc_by_v<__half, __half>(vec_length, p, s)
+                               : spmm_cc_by_v<__half, float>(vec_length, p, s);
+}
+
+VS_EXPORT int vs_spmm(int path, int in_dtype, int out_dtype, int m_vec, int vec_length, int k, int n,
+                      const int32_t *row_indices, const int32_t *row_offsets, const int32_t *col_indices,
+                      const void *values, const void *rhs_matrix, void *output_matrix, void *stream) {
+    return vs_spmm_batched(path, in_dtype, out_dtype, m_vec, vec_length, k, n, row_indices, row_offsets,
+                           col_indices, values, rhs_matrix, output_matrix, 1, 0, 0, 0, stream);
+}
+
+VS_EXPORT int vs_sddmm_batched(int path, int in_dtype, int out_dtype, int m_vec, int k, int n, int nonzeros_vec,
+                               const int32_t *row_indices, const int32_t *row_offsets, const int32_t *col_indices,
+                               const void *lhs_matrix, const void *rhs_matrix, void *output_values,
+                               int vec_length, int batch, int64_t stride_lhs, int64_t stride_rhs,
+                               int64_t stride_out, void *stream, int algorithm) {
+    if (path != VS_PATH_TENSOR && path != VS_PATH_CUDA_CORE) return VS_ERR_ARG;
+    if (path == VS_PATH_TENSOR ? !(vec_length == 2 || vec_length == 4 || vec_length == 8) : !valid_v(vec_length))
+        return VS_ERR_VEC_LENGTH;
+    if (!(in_dtype == VS_F16 && (out_dtype == VS_F16 || out_dtype == VS_F32))) return VS_ERR_DTYPE;
+    if (path == VS_PATH_TENSOR && (algorithm < 0 || algorithm > 3)) return VS_ERR_ARG;
+    if (m_vec < 0 || k < 0 || n < 0 || nonzeros_vec < 0) return VS_ERR_SHAPE;
+    if (batch < 1 || batch > kMaxBatch) return VS_ERR_ARG;
+    if (path == VS_PATH_TENSOR ? (k % 64 != 0) : (k % 8 != 0)) return VS_ERR_SHAPE;
+    if ((int64_t)nonzeros_vec * vec_length > 0x7fffffffll) return VS_ERR_SHAPE;
+    if (m_vec == 0 || nonzeros_vec == 0) return VS_OK;
+    if (!row_indices || !row_offsets || !col_indices || !lhs_matrix || !rhs_matrix || !output_values)
+        return VS_ERR_NULL;
+    if (!aligned16(lhs_matrix) || !aligned16(rhs_matrix) || !aligned16(output_values)) return VS_ERR_ALIGN;
+    if (!stride_ok(stride_lhs, in_dtype) || !stride_ok(stride_rhs, in_dtype) || !stride_ok(stride_out, out_dtype))
+        return VS_ERR_ALIGN;
+    if (batch > 1 && stride_out == 0) return VS_ERR_ARG;
+
+    SddmmParams p;
+    p.m_vec = m_vec; p.k = k; p.n = n; p.nnz_vec = nonzeros_vec; p.batch = batch;
+    p.row_indices = row_indices; p.row_offsets = row_offsets; p.col_indices = col_indices;
+    p.lhs = lhs_matrix; p.rhs = rhs_matrix; p.out = output_values;
+    p.stride_lhs = stride_lhs; p.stride_rhs = stride_rhs; p.stride_out = stride_out;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+    if (k == 0) {  // empty contraction: every output is zero
+        for (int b = 0; b < batch; ++b) {
+            cudaError_t e = cudaMemsetAsync(static_cast<char *>(output_values) + (size_t)b * stride_out * elem_size(out_dtype),
+                                            0, (size_t)nonzeros_vec * vec_length * elem_size(out_dtype), s);
+            if (e != cudaSuccess) return (int)e;
+        }
+        return VS_OK;
+    }
+    if (path == VS_PATH_TENSOR) {
+        return out_dtype == VS_F16 ? sddmm_tc_by_v<__half>(vec_length, p, s) : sddmm_tc_by_v<float>(vec_length, p, s);
+    }
+    return out_dtype == VS_F16 ? sddmm_cc_by_v<__half, __half>(vec_length, p, s)
+                               : sddmm_cc_by_v<__half, float>(vec_length, p, s);
+}
+
+VS_EXPORT int vs_sddmm(int path, int in_dtype, int out_dtype, int m_vec, int k, int n, int nonzeros_vec,
+                       const int32_t *row_indices, const int32_t *row_offsets, const int32_t *col_indices,
+                       const void *lhs_matrix, const void *rhs_matrix, void *output_values, int vec_length,
+                       void *stream, int algorithm) {
+    return vs_sddmm_batched(path, in_dtype, out_dtype, m_vec, k, n, nonzeros_vec, row_indices, row_offsets,
+                            col_indices, lhs_matrix, rhs_matrix, output_values, vec_length, 1, 0, 0, 0, stream,
+                            algorithm);
+}
+
+VS_EXPORT int vs_softmax_cvse(int dtype, int m_vec, int vec_length, const int32_t *row_indices,
+                              const int32_t *row_offsets, const void *scores, void *probs, float scale, int batch,
+                              int64_t stride, void *stream) {
+    (void)row_indices;  // rows are independent and equally cheap to reach: the order is not needed
+    if (!valid_v(vec_length)) return VS_ERR_VEC_LENGTH;
+    if (dtype != VS_F16 && dtype != VS_F32) return VS_ERR_DTYPE;
+    if (m_vec < 0) return VS_ERR_SHAPE;
+    if (batch < 1 || batch > kMaxBatch) return VS_ERR_ARG;
+    if (m_vec == 0) return VS_OK;
+    if (!row_offsets || !scores || !probs) return VS_ERR_NULL;
+    if (stride < 0 || (batch > 1 && stride == 0)) return VS_ERR_ARG;
+    SoftmaxParams p;
+    p.m_vec = m_vec; p.batch = batch; p.row_offsets = row_offsets; p.scores = scores; p.probs = probs;
+    p.stride = stride; p.scale = scale;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return dtype == VS_F16 ? softmax_by_v<__half>(vec_length, p, s) : softmax_by_v<float>(vec_length, p, s);
+}
+
+VS_EXPORT int vs_attention_cvse(int path, int m_vec, int vec_length, int n, int d, int nonzeros_vec,
+                                const int32_t *row_indices, const int32_t *row_offsets, const int32_t *col_indices,
+                                const void *q, const void *kmat, const void *vmat, void *out, void *workspace,
+                                float scale, int batch, void *stream) {
+    if (!workspace && nonzeros_vec > 0) return VS_ERR_NULL;
+    const int64_t m = (int64_t)m_vec * vec_length;
+    const int64_t s_ws = (int64_t)nonzeros_vec * vec_length;
+    if ((s_ws * 2) % 16 != 0 && batch > 1) return VS_ERR_ALIGN;
+    int rc = vs_sddmm_batched(path, VS_F16, VS_F16, m_vec, d, n, nonzeros_vec, row_indices, row_offsets,
+                              col_indices, q, kmat, workspace, vec_length, batch, m * d, (int64_t)n * d, s_ws,
+                              stream, 0);
+    if (rc != VS_OK) return rc;
+    rc = vs_softmax_cvse(VS_F16, m_vec, vec_length, row_indices, row_offsets, workspace, workspace, scale, batch,
+                         s_ws, stream);
+    if (rc != VS_OK) return rc;
+    return vs_spmm_batched(path, VS_F16, VS_F16, m_vec, vec_length, d, n, row_indices, row_offsets, col_indices,
+                           workspace, vmat, out, batch, s_ws, (int64_t)n * d, m * d, stream);
+}
+
+// ---- host-buffer forms -------------------------------------------------------------------------------------
+
+namespace {
+struct DeviceBuffers {  // frees whatever was allocated when it goes out of scope
+    void *ptr[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    int count = 0;
+    cudaError_t alloc(void **out, size_t bytes) {
+        cudaError_t e = cudaMalloc(out, bytes ? bytes : 16);
+        if (e == cudaSuccess) ptr[count++] = *out;
+        return e;
+    }
+    ~DeviceBuffers() {
+        for (int i = 0; i < count; ++i) cudaFree(ptr[i]);
+    }
+};
+#define VS_CUDA_TRY(expr)                      \
+    do {                                       \
+        cudaError_t e__ = (expr);              \
+        if (e__ != cudaSuccess) return (int)e__; \
+    } while (0)
+}  // namespace
+
+VS_EXPORT int vs_spmm_host(int path, int in_dtype, int out_dtype, int m_vec, int vec_length, int k, int n,
+                           const int32_t *row_indices, const int32_t *row_offsets, const int32_t *col_indices,
+                           const void *values, const void *rhs_matrix, void *output_matrix) {
+    if (m_vec < 0 || k < 0 || n < 0) return VS_ERR_SHAPE;
+    if (!valid_v(vec_length)) return VS_ERR_VEC_LENGTH;
+    if ((in_dtype != VS_F16 && in_dtype != VS_F32) || (out_dtype != VS_F16 && out_dtype != VS_F32)) return VS_ERR_DTYPE;
+    if (!row_indices || !row_offsets || !output_matrix) return VS_ERR_NULL;
+    const int nnz_vec = row_offsets[m_vec];
+    int rc = vs_cvse_validate(m_vec, n, nnz_vec, row_offsets, col_indices);
+    if (rc != VS_OK) return rc;
+    if (nnz_vec > 0 && (!values || !rhs_matrix)) return VS_ERR_NULL;
+    const size_t si = elem_size(in_dtype), so = elem_size(out_dtype);
+    const size_t b_idx = (size_t)m_vec * 4, b_off = (size_t)(m_vec + 1) * 4, b_col = (size_t)nnz_vec * 4;
+    const size_t b_val = (size_t)nnz_vec * vec_length * si, b_rhs = (size_t)n * k * si;
+    const size_t b_out = (size_t)m_vec * vec_length * k * so;
+    DeviceBuffers bufs;
+    int32_t *d_idx, *d_off, *d_col;
+    void *d_val, *d_rhs, *d_out;
+    VS_CUDA_TRY(bufs.alloc((void **)&d_idx, b_idx));
+    VS_CUDA_TRY(bufs.alloc((void **)&d_off, b_off));
+    VS_CUDA_TRY(bufs.alloc((void **)&d_col, b_col));
+    VS_CUDA_TRY(bufs.alloc(&d_val, b_val));
+    VS_CUDA_TRY(bufs.alloc(&d_rhs, b_rhs));
+    VS_CUDA_TRY(bufs.alloc(&d_out, b_out));
+    VS_CUDA_TRY(cudaMemcpy(d_idx, row_indices, b_idx, cudaMemcpyHostToDevice));
+    VS_CUDA_TRY(cudaMemcpy(d_off, row_offsets, b_off, cudaMemcpyHostToDevice));
+    if (b_col) VS_CUDA_TRY(cudaMemcpy(d_col, col_indices, b_col, cudaMemcpyHostToDevice));
+    if (b_val) VS_CUDA_TRY(cudaMemcpy(d_val, values, b_val, cudaMemcpyHostToDevice));
+    if (b_rhs) VS_CUDA_TRY(cudaMemcpy(d_rhs, rhs_matrix, b_rhs, cudaMemcpyHostToDevice));
+    rc = vs_spmm(path, in_dtype, out_dtype, m_vec, vec_length, k, n, d_idx, d_off, d_col, d_val, d_rhs, d_out, nullptr);
+    if (rc != VS_OK) return rc;
+    VS_CUDA_TRY(cudaDeviceSynchronize());
+    if (b_out) VS_CUDA_TRY(cudaMemcpy(output_matrix, d_out, b_out, cudaMemcpyDeviceToHost));
+    return VS_OK;
+}
+
+VS_EXPORT int vs_sddmm_host(int path, int in_dtype, int out_dtype, int m_vec, int k, int n, int nonzeros_vec,
+                            const int32_t *row_indices, const int32_t *row_offsets, const int32_t *col_indices,
+                            const void *lhs_matrix, const void *rhs_matrix, void *output_values, int vec_length,
+                            int algorithm) {
+    if (m_vec < 0 || k < 0 || n < 0 || nonzeros_vec < 0) return VS_ERR_SHAPE;
+    if (!valid_v(vec_length)) return VS_ERR_VEC_LENGTH;
+    if ((in_dtype != VS_F16 && in_dtype != VS_F32) || (out_dtype != VS_F16 && out_dtype != VS_F32)) return VS_ERR_DTYPE;
+    if (!row_indices || !row_offsets) return VS_ERR_NULL;
+    int rc = vs_cvse_validate(m_vec, n, nonzeros_vec, row_offsets, col_indices);
+    if (rc != VS_OK) return rc;
+    if (nonzeros_vec > 0 && (!lhs_matrix || !rhs_matrix || !output_values)) return VS_ERR_NULL;
+    const size_t si = elem_size(in_dtype), so = elem_size(out_dtype);
+    const size_t b_idx = (size_t)m_vec * 4, b_off = (size_t)(m_vec + 1) * 4, b_col = (size_t)nonzeros_vec * 4;
+    const size_t b_lhs = (size_t)m_vec * vec_length * k * si, b_rhs = (size_t)n * k * si;
+    const size_t b_out = (size_t)nonzeros_vec * vec_length * so;
+    DeviceBuffers bufs;
+    int32_t *d_idx, *d_off, *d_col;
+    void *d_lhs, *d_rhs, *d_out;
+    VS_CUDA_TRY(bufs.alloc((void **)&d_idx, b_idx));
+    VS_CUDA_TRY(bufs.alloc((void **)&d_off, b_off));
+    VS_CUDA_TRY(bufs.alloc((void **)&d_col, b_col));
+    VS_CUDA_TRY(bufs.alloc(&d_lhs, b_lhs));
+    VS_CUDA_TRY(bufs.alloc(&d_rhs, b_rhs));
+    VS_CUDA_TRY(bufs.alloc(&d_out, b_out));
+    VS_CUDA_TRY(cudaMemcpy(d_idx, row_indices, b_idx, cudaMemcpyHostToDevice));
+    VS_CUDA_TRY(cudaMemcpy(d_off, row_offsets, b_off, cudaMemcpyHostToDevice));
+    if (b_col) VS_CUDA_TRY(cudaMemcpy(d_col, col_indices, b_col, cudaMemcpyHostToDevice));
+    if (b_lhs) VS_CUDA_TRY(cudaMemcpy(d_lhs, lhs_matrix, b_lhs, cudaMemcpyHostToDevice));
+    if (b_rhs) VS_CUDA_TRY(cudaMemcpy(d_rhs, rhs_matrix, b_rhs, cudaMemcpyHostToDevice));
+    rc = vs_sddmm(path, in_dtype, out_dtype, m_vec, k, n, nonzeros_vec, d_idx, d_off, d_col, d_lhs, d_rhs, d_out,
+                  vec_length, nullptr, algorithm);
+    if (rc != VS_OK) return rc;
+    VS_CUDA_TRY(cudaDeviceSynchronize());
+    if (b_out) VS_CUDA_TRY(cudaMemcpy(output_values, d_out, b_out, cudaMemcpyDeviceToHost));
+    return VS_OK;
+}
+
+VS_EXPORT int vs_device_status(int clear, uint32_t *status) {
+    if (!status) return VS_ERR_NULL;
+    DeviceInfo *d;
+    int rc = device_info(&d);
+    if (rc != VS_OK) return rc;
+    VS_CUDA_TRY(cudaDeviceSynchronize());
+    VS_CUDA_TRY(cudaMemcpy(status, d->status, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    if (clear) VS_CUDA_TRY(cudaMemset(d->status, 0, sizeof(uint32_t)));
+    return VS_OK;
+}
+
+VS_EXPORT int vs_selftest_mma(const void *image, int image_bytes, const uint64_t *descs, int n_mma,
+                              uint32_t idesc, int ncols, float fill, float *out, void *stream) {
+    if (!image || !descs || !out) return VS_ERR_NULL;
+    if (image_bytes <= 0 || image_bytes > 128 * 1024 || n_mma < 1 || n_mma > 64) return VS_ERR_SHAPE;
+    if (ncols < 8 || ncols > tcselftest::kTmemCols || ncols % 8 != 0) return VS_ERR_SHAPE;
+    if (!aligned16(image)) return VS_ERR_ALIGN;
+    DeviceInfo *d;
+    int rc = device_info(&d);
+    if (rc != VS_OK) return rc;
+    const int smem = ((image_bytes + 15) & ~15) + 16 + 1024;
+    rc = set_smem(tcselftest::sandbox_kernel, smem);
+    if (rc != VS_OK) return rc;
+    tcselftest::sandbox_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t *>(image), image_bytes, descs, n_mma, idesc, ncols, fill, out, d->status);
+    return (int)cudaGetLastError();
+}

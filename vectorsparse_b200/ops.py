@@ -1,0 +1,181 @@
+"""Operators on CUDA tensors, named and argued like the reference's C++ API.
+
+    spmm.wmmaSpmm / spmm.cudaSpmm       include/wmma_spmm.cuh:7-29, include/cuda_spmm.cuh:7-29
+    sddmm.wmmaSddmm / sddmm.cudaSddmm   include/wmma_sddmm.cuh:7-33, include/cuda_sddmm.cuh:7-32
+
+Arguments keep the reference's order and meaning (m_vec, vec_length, k, n, row_indices, row_offsets,
+column_indices, values, rhs_matrix, output_matrix); tensors replace raw device pointers and the element types
+are taken from them, which is what overload resolution does in the reference.  Every call enqueues on the
+current torch CUDA stream and returns 0; rejected arguments raise VsError (the reference prints and returns).
+PyTorch is used for device memory and streams only: the arithmetic is in libvsparse_b200.so.
+"""
+from __future__ import annotations
+
+import types
+
+import torch
+
+from . import _lib
+from ._lib import VS_F16, VS_F32, VS_PATH_CUDA_CORE, VS_PATH_TENSOR
+
+_DT = {torch.float16: VS_F16, torch.float32: VS_F32}
+
+
+def _dev(t: torch.Tensor, name: str, dtype=None):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise TypeError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    return t.data_ptr()
+
+
+def _dtype_code(t: torch.Tensor, name: str) -> int:
+    if t.dtype not in _DT:
+        raise _lib.VsError(-2, name)
+    return _DT[t.dtype]
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(t: torch.Tensor, numel: int, name: str):
+    if t.numel() < numel:
+        raise ValueError(f"{name} holds {t.numel()} elements, {numel} needed")
+
+
+def _spmm(path, m_vec, vec_length, k, n, row_indices, row_offsets, column_indices, values, rhs_matrix,
+          output_matrix, batch=1):
+    nnz_needed = None
+    _need(row_indices, m_vec, "row_indices")
+    _need(row_offsets, m_vec + 1, "row_offsets")
+    _need(rhs_matrix, batch * n * k if rhs_matrix.dim() == 3 else n * k, "rhs_matrix")
+    _need(output_matrix, batch * m_vec * vec_length * k, "output_matrix")
+    sv = values.stride(0) if values.dim() == 2 and batch > 1 else 0
+    sr = rhs_matrix.stride(0) if rhs_matrix.dim() == 3 and batch > 1 else 0
+    so = output_matrix.stride(0) if output_matrix.dim() == 3 and batch > 1 else 0
+    rc = _lib.lib().vs_spmm_batched(
+        path, _dtype_code(values, "values"), _dtype_code(output_matrix, "output_matrix"), m_vec, vec_length, k, n,
+        _dev(row_indices, "row_indices", torch.int32), _dev(row_offsets, "row_offsets", torch.int32),
+        _dev(column_indices, "column_indices", torch.int32), _dev(values, "values"),
+        _dev(rhs_matrix, "rhs_matrix", values.dtype), _dev(output_matrix, "output_matrix"), batch, sv, sr, so,
+        _stream())
+    _lib.check(rc, "vs_spmm")
+    return 0
+
+
+def _sddmm(path, m_vec, k, n, nonzeros_vec, row_indices, row_offsets, col_indices, lhs_matrix, rhs_matrix,
+           output_values, vec_length, algorithm, batch=1):
+    _need(row_indices, m_vec, "row_indices")
+    _need(row_offsets, m_vec + 1, "row_offsets")
+    _need(col_indices, nonzeros_vec, "col_indices")
+    _need(lhs_matrix, (batch if lhs_matrix.dim() == 3 else 1) * m_vec * vec_length * k, "lhs_matrix")
+    _need(rhs_matrix, (batch if rhs_matrix.dim() == 3 else 1) * n * k, "rhs_matrix")
+    _need(output_values, batch * nonzeros_vec * vec_length, "output_values")
+    sl = lhs_matrix.stride(0) if lhs_matrix.dim() == 3 and batch > 1 else 0
+    sr = rhs_matrix.stride(0) if rhs_matrix.dim() == 3 and batch > 1 else 0
+    so = output_values.stride(0) if output_values.dim() == 2 and batch > 1 else 0
+    rc = _lib.lib().vs_sddmm_batched(
+        path, _dtype_code(lhs_matrix, "lhs_matrix"), _dtype_code(output_values, "output_values"), m_vec, k, n,
+        nonzeros_vec, _dev(row_indices, "row_indices", torch.int32), _dev(row_offsets, "row_offsets", torch.int32),
+        _dev(col_indices, "col_indices", torch.int32), _dev(lhs_matrix, "lhs_matrix"),
+        _dev(rhs_matrix, "rhs_matrix", lhs_matrix.dtype), _dev(output_values, "output_values"), vec_length, batch,
+        sl, sr, so, _stream(), algorithm)
+    _lib.check(rc, "vs_sddmm")
+    return 0
+
+
+# ---- namespaces mirroring the reference -------------------------------------------------------------------
+
+def _wmmaSpmm(m_vec, vec_length, k, n, row_indices, row_offsets, column_indices, values, rhs_matrix, output_matrix):
+    """Tensor-core SpMM, V in {2,4,8}; fp16 in, fp16 or fp32 out (src/wmma_spmm.cu:388-409)."""
+    return _spmm(VS_PATH_TENSOR, m_vec, vec_length, k, n, row_indices, row_offsets, column_indices, values,
+                 rhs_matrix, output_matrix)
+
+
+def _cudaSpmm(m_vec, vec_length, k, n, row_indices, row_offsets, column_indices, values, rhs_matrix, output_matrix):
+    """CUDA-core SpMM, V in {1,2,4,8}; fp16 or fp32 (src/cuda_spmm.cu:304-338; fp32 is a stub there)."""
+    return _spmm(VS_PATH_CUDA_CORE, m_vec, vec_length, k, n, row_indices, row_offsets, column_indices, values,
+                 rhs_matrix, output_matrix)
+
+
+def _wmmaSddmm(m_vec, k, n, nonzeros_vec, row_indices, row_offsets, col_indices, lhs_matrix, rhs_matrix,
+               output_values, vec_length, stream=None, algorithm=1):
+    """Tensor-core SDDMM (src/wmma_sddmm.cu:3175-3202).  `stream`: a torch.cuda.Stream or None (current)."""
+    if stream is not None:
+        with torch.cuda.stream(stream):
+            return _sddmm(VS_PATH_TENSOR, m_vec, k, n, nonzeros_vec, row_indices, row_offsets, col_indices,
+                          lhs_matrix, rhs_matrix, output_values, vec_length, algorithm)
+    return _sddmm(VS_PATH_TENSOR, m_vec, k, n, nonzeros_vec, row_indices, row_offsets, col_indices, lhs_matrix,
+                  rhs_matrix, output_values, vec_length, algorithm)
+
+
+def _cudaSddmm(m_vec, k, n, nonzeros_vec, row_indices, row_offsets, col_indices, lhs_matrix, rhs_matrix,
+               output_values, vec_length, stream=None):
+    """CUDA-core SDDMM (src/cuda_sddmm.cu:1257-1331)."""
+    if stream is not None:
+        with torch.cuda.stream(stream):
+            return _sddmm(VS_PATH_CUDA_CORE, m_vec, k, n, nonzeros_vec, row_indices, row_offsets, col_indices,
+                          lhs_matrix, rhs_matrix, output_values, vec_length, 0)
+    return _sddmm(VS_PATH_CUDA_CORE, m_vec, k, n, nonzeros_vec, row_indices, row_offsets, col_indices, lhs_matrix,
+                  rhs_matrix, output_values, vec_length, 0)
+
+
+spmm = types.SimpleNamespace(wmmaSpmm=_wmmaSpmm, cudaSpmm=_cudaSpmm)
+sddmm = types.SimpleNamespace(wmmaSddmm=_wmmaSddmm, cudaSddmm=_cudaSddmm)
+
+
+# ---- batched forms, softmax and attention (no counterpart in the reference) ---------------------------------
+
+def spmm_batched(path, m_vec, vec_length, k, n, row_indices, row_offsets, column_indices, values, rhs_matrix,
+                 output_matrix):
+    """values [B, nnz] (or [nnz], shared), rhs [B, n, k] (or [n, k]), out [B, m, k]: one launch for B products."""
+    batch = output_matrix.shape[0]
+    return _spmm(path, m_vec, vec_length, k, n, row_indices, row_offsets, column_indices, values, rhs_matrix,
+                 output_matrix, batch)
+
+
+def sddmm_batched(path, m_vec, k, n, nonzeros_vec, row_indices, row_offsets, col_indices, lhs_matrix, rhs_matrix,
+                  output_values, vec_length, algorithm=1):
+    """lhs [B, m, k], rhs [B, n, k], out [B, nnz]."""
+    batch = output_values.shape[0]
+    return _sddmm(path, m_vec, k, n, nonzeros_vec, row_indices, row_offsets, col_indices, lhs_matrix, rhs_matrix,
+                  output_values, vec_length, algorithm, batch)
+
+
+def softmax_cvse(m_vec, vec_length, row_indices, row_offsets, scores, probs, scale=1.0):
+    """Row softmax over the CVSE values; scores/probs [nnz] or [B, nnz]; probs may be scores."""
+    batch = scores.shape[0] if scores.dim() == 2 else 1
+    stride = scores.stride(0) if scores.dim() == 2 and batch > 1 else 0
+    rc = _lib.lib().vs_softmax_cvse(_dtype_code(scores, "scores"), m_vec, vec_length,
+                                    _dev(row_indices, "row_indices", torch.int32),
+                                    _dev(row_offsets, "row_offsets", torch.int32), _dev(scores, "scores"),
+                                    _dev(probs, "probs", scores.dtype), float(scale), batch, stride, _stream())
+    _lib.check(rc, "vs_softmax_cvse")
+    return 0
+
+
+def attention_cvse(path, m_vec, vec_length, n, d, nonzeros_vec, row_indices, row_offsets, col_indices, q, kmat,
+                   vmat, out, workspace, scale):
+    """softmax(scale * SDDMM(q, k)) @ v for [B, ., d] fp16 tensors sharing one mask; workspace [B, nnz] fp16."""
+    batch = q.shape[0] if q.dim() == 3 else 1
+    _need(workspace, batch * nonzeros_vec * vec_length, "workspace")
+    rc = _lib.lib().vs_attention_cvse(path, m_vec, vec_length, n, d, nonzeros_vec,
+                                      _dev(row_indices, "row_indices", torch.int32),
+                                      _dev(row_offsets, "row_offsets", torch.int32),
+                                      _dev(col_indices, "col_indices", torch.int32),
+                                      _dev(q, "q", torch.float16), _dev(kmat, "kmat", torch.float16),
+                                      _dev(vmat, "vmat", torch.float16), _dev(out, "out", torch.float16),
+                                      _dev(workspace, "workspace", torch.float16), float(scale), batch, _stream())
+    _lib.check(rc, "vs_attention_cvse")
+    return 0
+
+
+def device_status(clear: bool = True) -> int:
+    """Status word of the current device: 0 unless a kernel gave up on a bounded wait."""
+    import ctypes as C
+    v = C.c_uint32(0)
+    _lib.check(_lib.lib().vs_device_status(1 if clear else 0, C.byref(v)), "vs_device_status")
+    return int(v.value)
