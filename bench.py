@@ -1,0 +1,368 @@
+#!/usr/bin/env python
+"""Benchmark of the column-vector sparse SpMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Default workload `spmm_v8_s90`: the tensor-core SpMM (wmmaSpmm entry point) on the pruned ResNet-50 layer shape
+the target is quoted on — A 2048 x 512 in CVSE with V = 8 at 90 % sparsity (Beta(2,2)-skewed rows), fp16 values
+N(0, 0.02), dense B 512 x 256 fp16 N(0,1), fp32 accumulate, fp16 C.  One such product is ~54 MFLOP / 1.6 MB,
+far below launch latency, so a STEP is a stream of 256 independent instances (distinct values, B and C buffers
+sharing one sparsity structure, 384 MB in all, three times the L2) issued as ONE batched launch.  At N GPUs
+every rank runs its own stream (weak scaling, no collective on the data path).
+
+Metric: effective TFLOP/s = 2 * nnz * N / time, nnz = nnz_vec * V, summed over all ranks.
+`roofline`: algorithmic HBM bytes per launch / CUDA-event time per launch against the measured copy bandwidth.
+`e2e`: the same step through the public Python API with operands in pinned HOST memory: H2D of values and B,
+the launch, D2H of C, all inside the timed region.
+`--impl reference`: the reference's own CPU path (its sequential host loop) timed on this box's host cores on a
+bounded sample of the same stream.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (op, M, K, V, sparsity, N or k, instances, pattern kind)
+    "spmm_v8_s90": dict(op="spmm", M=2048, K=512, V=8, s=0.9, N=256, inst=256, kind="beta"),
+    "spmm_v8_s50": dict(op="spmm", M=2048, K=512, V=8, s=0.5, N=256, inst=256, kind="beta"),
+    "spmm_v4_s90": dict(op="spmm", M=2048, K=512, V=4, s=0.9, N=256, inst=256, kind="beta"),
+    "spmm_v2_s90": dict(op="spmm", M=2048, K=512, V=2, s=0.9, N=256, inst=256, kind="beta"),
+    "sddmm_v8_s90": dict(op="sddmm", M=2048, K=512, V=8, s=0.9, N=256, inst=256, kind="beta"),
+    "spmm_cc_v8_s90": dict(op="spmm", M=2048, K=512, V=8, s=0.9, N=256, inst=256, kind="beta", path=1),
+}
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from an ncu capture of this
+# command (profiles/ holds the summary it comes from); None until one has been taken for the workload.
+NCU_TRAFFIC_BYTES = {}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_problem(w, seed=2026):
+    from vectorsparse_b200 import cvse
+    kind = {"beta": cvse.GEN_BETA, "fixed": cvse.GEN_FIXED, "uniform": cvse.GEN_UNIFORM}[w["kind"]]
+    a = cvse.generate(kind, seed, w["M"] // w["V"], w["K"], w["V"], w["s"])
+    return a
+
+
+def algorithmic(w, a):
+    """(flops, HBM bytes) of ONE launch = `inst` instances sharing the structure arrays."""
+    nnz_vec, V, inst = a.nnz_vec, w["V"], w["inst"]
+    structure = nnz_vec * 4 + (2 * a.m_vec + 1) * 4
+    if w["op"] == "spmm":
+        k_touched = int(np.unique(a.col_indices).size)
+        per = nnz_vec * V * 2 + k_touched * w["N"] * 2 + w["M"] * w["N"] * 2
+        flops = 2.0 * nnz_vec * V * w["N"]
+    else:  # sddmm: lhs M x k, rhs K x k, out nnz
+        k = w["N"]
+        n_touched = int(np.unique(a.col_indices).size)
+        per = w["M"] * k * 2 + n_touched * k * 2 + nnz_vec * V * 2
+        flops = 2.0 * nnz_vec * V * k
+    return flops * inst, float(structure + per * inst)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from vectorsparse_b200 import VS_PATH_CUDA_CORE, VS_PATH_TENSOR, cvse, ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    w = WORKLOADS[args.workload]
+    path = VS_PATH_CUDA_CORE if w.get("path") == 1 else VS_PATH_TENSOR
+    a = build_problem(w)
+    inst, V, M, K, N = w["inst"], w["V"], w["M"], w["K"], w["N"]
+    ri, ro, ci = a.to_device(dev)
+    flops, alg_bytes = algorithmic(w, a)
+
+    # operands of this rank's stream, in pinned host memory (for the end-to-end leg) and on the device
+    seed = 100 + rank
+    if w["op"] == "spmm":
+        row = (a.nnz_vec * V + 7) // 8 * 8  # per-instance stride kept 16-byte aligned for every V
+        h_a = torch.from_numpy(cvse.fill_random((inst, row), np.float16, cvse.DIST_NORMAL, seed, 0.02)).pin_memory()
+        h_b = torch.from_numpy(cvse.fill_random((inst, K, N), np.float16, cvse.DIST_NORMAL, seed + 1, 1.0)).pin_memory()
+        h_out = torch.empty((inst, M, N), dtype=torch.float16).pin_memory()
+        d_out = torch.empty((inst, M, N), dtype=torch.float16, device=dev)
+
+        def launch(d_a, d_b, out):
+            ops.spmm_batched(path, a.m_vec, V, N, K, ri, ro, ci, d_a, d_b, out)
+    else:
+        k = N
+        h_a = torch.from_numpy(cvse.fill_random((inst, M, k), np.float16, cvse.DIST_NORMAL, seed, 1.0)).pin_memory()
+        h_b = torch.from_numpy(cvse.fill_random((inst, K, k), np.float16, cvse.DIST_NORMAL, seed + 1, 1.0)).pin_memory()
+        h_out = torch.empty((inst, a.nnz_vec * V), dtype=torch.float16).pin_memory()
+        d_out = torch.empty((inst, a.nnz_vec * V), dtype=torch.float16, device=dev)
+
+        def launch(d_a, d_b, out):
+            ops.sddmm_batched(path, a.m_vec, k, K, a.nnz_vec, ri, ro, ci, d_a, d_b, out, V)
+    d_a = h_a.to(dev)
+    d_b = h_b.to(dev)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident leg: `value` and the roofline ------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        launch(d_a, d_b, d_out)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    ev[0].record()
+    for s in range(args.steps):
+        launch(d_a, d_b, d_out)
+        ev[s + 1].record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    per_launch_ms = [ev[s].elapsed_time(ev[s + 1]) for s in range(args.steps)]
+    total_ms = ev[0].elapsed_time(ev[args.steps])
+    assert ops.device_status() == 0, "a kernel gave up on a bounded wait"
+
+    # ---- end-to-end leg: host buffers, copies inside the timed region --------------------------------------
+    def e2e_step():
+        da = h_a.to(dev, non_blocking=True)
+        db = h_b.to(dev, non_blocking=True)
+        launch(da, db, d_out)
+        h_out.copy_(d_out, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+
+    # ---- single-launch latency of ONE instance (the reference API's granularity), L2-hot ----------------------
+    lat_us = None
+    if w["op"] == "spmm":
+        for _ in range(5):
+            ops.spmm.wmmaSpmm(a.m_vec, V, N, K, ri, ro, ci, d_a[0], d_b[0], d_out[0]) if path == VS_PATH_TENSOR else \
+                ops.spmm.cudaSpmm(a.m_vec, V, N, K, ri, ro, ci, d_a[0], d_b[0], d_out[0])
+        torch.cuda.synchronize()
+        l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0.record()
+        for _ in range(50):
+            ops.spmm.wmmaSpmm(a.m_vec, V, N, K, ri, ro, ci, d_a[0], d_b[0], d_out[0]) if path == VS_PATH_TENSOR else \
+                ops.spmm.cudaSpmm(a.m_vec, V, N, K, ri, ro, ci, d_a[0], d_b[0], d_out[0])
+        l1.record()
+        torch.cuda.synchronize()
+        lat_us = l0.elapsed_time(l1) * 1000.0 / 50
+
+    # max over ranks
+    t = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms = float(t[0]), float(t[1])
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        avg_launch_s = float(np.mean(per_launch_ms)) * 1e-3
+        achieved = alg_bytes / avg_launch_s / 1e9
+        h2d = h_a.numel() * 2 + h_b.numel() * 2
+        d2h = h_out.numel() * 2
+        line = {
+            "metric": "SpMM effective TFLOP/s (2*nnz*N)" if w["op"] == "spmm" else "SDDMM effective TFLOP/s (2*nnz*k)",
+            "value": flops * args.steps * world / (total_ms * 1e-3) / 1e12,
+            "unit": "TFLOP/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": max(args.warmup, 3),
+            "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "f16 (fp32 accumulate)",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "op": w["op"], "M": M, "K": K, "V": V, "sparsity": w["s"],
+                       "dense_width_or_k": N, "nnz_vec": a.nnz_vec, "instances_per_step": inst,
+                       "path": "cuda-core" if path == VS_PATH_CUDA_CORE else "tensor (tcgen05)",
+                       "l2": "working set 3x L2 (distinct operands per instance), no flush needed",
+                       "parallelism": f"independent streams x{world}"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "peak_source": f"of {peak_kind}",
+                         "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                         "algorithmic_bytes_per_launch": alg_bytes},
+            "e2e": {"value": flops * e2e_steps * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+            "gpu_launches": args.steps,
+            "single_launch_latency_us": lat_us,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_leg(w, a, budget_s=12.0)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_leg(w, a, budget_s, threads=None):
+    """The reference's CPU path on a bounded sample of the stream: its sequential host loop — the compiled
+    reference code where that library exists, else the oracle's restatement — one instance per host thread."""
+    import concurrent.futures as cf
+
+    import oracle
+    from vectorsparse_b200 import cvse
+
+    cores = threads or (os.cpu_count() or 1)
+    use_ref = oracle.ref() is not None
+    V, M, K, N = w["V"], w["M"], w["K"], w["N"]
+    if w["op"] == "spmm":
+        x = cvse.fill_random((a.nnz_vec * V,), np.float16, cvse.DIST_NORMAL, 1, 0.02)
+        y = cvse.fill_random((K, N), np.float16, cvse.DIST_NORMAL, 2, 1.0)
+        flops = 2.0 * a.nnz_vec * V * N
+
+        def one(_):
+            if use_ref:
+                return oracle.ref_spmm(a.m_vec, V, N, a.row_offsets, a.col_indices, x, y)
+            return oracle.spmm(a.m_vec, V, N, a.row_offsets, a.col_indices, x, y, acc="f32", threads=1)
+    else:
+        k = N
+        x = cvse.fill_random((M, k), np.float16, cvse.DIST_NORMAL, 1, 1.0)
+        y = cvse.fill_random((K, k), np.float16, cvse.DIST_NORMAL, 2, 1.0)
+        flops = 2.0 * a.nnz_vec * V * k
+
+        def one(_):
+            if use_ref:
+                return oracle.ref_sddmm(a.m_vec, k, V, a.row_offsets, a.col_indices, x, y)
+            return oracle.sddmm(a.m_vec, k, V, a.row_offsets, a.col_indices, x, y, acc="f32", threads=1)
+    t0 = time.perf_counter()
+    one(0)
+    t_one = time.perf_counter() - t0
+    count = int(max(cores, min(w["inst"], cores * max(1, int(budget_s / max(t_one, 1e-4))))))
+    t0 = time.perf_counter()
+    with cf.ThreadPoolExecutor(cores) as ex:
+        list(ex.map(one, range(count)))
+    dt = time.perf_counter() - t0
+    return {"value": flops * count / dt / 1e12, "unit": "TFLOP/s", "cores": cores,
+            "kind": "reference" if use_ref else "port",
+            "sample": f"{count} of {w['inst']} instances of the step, one instance per host thread, "
+                      f"{dt:.1f} s; single instance on one core {t_one * 1e3:.1f} ms"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    w = WORKLOADS[args.workload]
+    a = build_problem(w)
+    steps = max(1, args.steps)
+    budget = min(20.0, 120.0 / (steps + args.warmup))
+    vals = []
+    base = None
+    for i in range(args.warmup + steps):
+        base = cpu_leg(w, a, budget_s=budget)
+        if i >= args.warmup:
+            vals.append(base["value"])
+    v = float(np.mean(vals))
+    base["value"] = v
+    line = {
+        "impl": "reference",
+        "metric": "SpMM effective TFLOP/s (2*nnz*N)" if w["op"] == "spmm" else "SDDMM effective TFLOP/s (2*nnz*k)",
+        "value": v, "unit": "TFLOP/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": steps,
+        "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": args.workload, "op": w["op"], "M": w["M"], "K": w["K"], "V": w["V"],
+                   "sparsity": w["s"], "dense_width_or_k": w["N"], "nnz_vec": a.nnz_vec,
+                   "instances_per_step": w["inst"], "path": "host loop (spmm_benchmark.cpp:66-86)"},
+        "cpu_baseline": base,
+        "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="spmm_v8_s90", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,79 @@
+"""Operand-encoding self-test of the tensor path: a caller-built shared-memory image, explicit descriptors, and
+the raw accumulator compared with a plain matrix product.  Pins the two layout conventions the kernels rely on:
+  * K-major operands with the 128-byte swizzle (SDDMM: gathered rhs rows and lhs rows), and
+  * MN-major operands — A with the 128-byte swizzle, B unswizzled — (SpMM: gathered rows of the dense operand
+    and the value vectors)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from vectorsparse_b200 import _lib, ops
+
+pytestmark = pytest.mark.gpu
+
+
+def desc(start, lbo, sbo, swizzle):
+    return (start >> 4) | ((lbo >> 4) << 16) | ((sbo >> 4) << 32) | (1 << 46) | (swizzle << 61)
+
+
+def idesc(M, N, a_mn, b_mn):
+    return (1 << 4) | (a_mn << 15) | (b_mn << 16) | ((N >> 3) << 17) | ((M >> 4) << 24)
+
+
+def run(image, descs, idesc_, ncols):
+    img = torch.from_numpy(image.view(np.uint8)).to("cuda:0")
+    d = torch.tensor(np.array(descs, dtype=np.uint64).view(np.int64), device="cuda:0")
+    out = torch.zeros(128 * ncols, dtype=torch.float32, device="cuda:0")
+    rc = _lib.lib().vs_selftest_mma(img.data_ptr(), img.numel(), d.data_ptr(), len(descs) // 2, idesc_, ncols,
+                                    -77.0, out.data_ptr(), None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    return out.cpu().numpy().reshape(128, ncols)
+
+
+def put(image, byte_off, value):
+    image[byte_off // 2] = value
+
+
+def test_k_major_swizzle128():
+    rng = np.random.default_rng(0)
+    A = rng.integers(-4, 5, (128, 64)).astype(np.float16)
+    B = rng.integers(-4, 5, (16, 64)).astype(np.float16)
+    image = np.zeros((16384 + 2048) // 2, np.float16)
+    for (mat, base, rows) in ((A, 0, 128), (B, 16384, 16)):
+        for r in range(rows):
+            for kk in range(64):
+                off = base + (r // 8) * 1024 + (r % 8) * 128 + (((kk // 8) ^ (r % 8)) * 16) + (kk % 8) * 2
+                put(image, off, mat[r, kk])
+    descs = []
+    for mm in range(4):
+        descs += [desc(mm * 32, 16, 1024, 2), desc(16384 + mm * 32, 16, 1024, 2)]
+    got = run(image, descs, idesc(128, 16, 0, 0), 16)
+    want = A.astype(np.float32) @ B.astype(np.float32).T
+    assert np.array_equal(got, want)
+
+
+def test_mn_major_spmm_layout():
+    rng = np.random.default_rng(1)
+    KK = 32
+    A = rng.integers(-4, 5, (128, KK)).astype(np.float16)   # [dense column m][nonzero kk]
+    B = rng.integers(-4, 5, (KK, 16)).astype(np.float16)    # [nonzero kk][vector element nn]
+    a_bytes, v_base, z_off = 8192, 8192, 1024
+    image = np.zeros((a_bytes + 2048) // 2, np.float16)
+    for m in range(128):
+        for kk in range(KK):
+            off = (m // 64) * 4096 + (kk // 8) * 1024 + (kk % 8) * 128 + ((((m % 64) // 8) ^ (kk % 8)) * 16) + (m % 8) * 2
+            put(image, off, A[m, kk])
+    for kk in range(KK):
+        for nn in range(16):
+            off = v_base + (nn // 8) * z_off + kk * 16 + (nn % 8) * 2
+            put(image, off, B[kk, nn])
+    descs = []
+    for mm in range(KK // 16):
+        descs += [desc(mm * 2048, 4096, 1024, 2), desc(v_base + mm * 256, 128, z_off, 0)]
+    got = run(image, descs, idesc(128, 16, 1, 1), 16)
+    want = A.astype(np.float32) @ B.astype(np.float32)
+    assert np.array_equal(got, want)

@@ -142,6 +142,8 @@ __global__ void __launch_bounds__(kThreads) spmm_tc_kernel(const SpmmParams p, u
         prefetch();
 
         Pending fifo[kEpiLag];  // fifo[kEpiLag - fifo_n .. kEpiLag) are valid, oldest first
+#pragma unroll
+        for (int i = 0; i < kEpiLag; ++i) fifo[i] = Pending{0, 0, 0, 0, 0};
         int fifo_n = 0;
         const uint32_t g_base = g_stage;
         int phase_stages = -1;  // known once the iterator runs dry

@@ -36,7 +36,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Polls at most `kMaxPolls` times (each try_wait itself blocks for a hardware-defined short interval).
 // Returns false if the phase never completed.
-constexpr uint32_t kMaxPolls = 1u << 22;
+constexpr uint32_t kMaxPolls = 1u << 20;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     for (uint32_t i = 0; i < kMaxPolls; ++i)
         if (mbar_try_wait(bar, parity)) return true;
