@@ -198,8 +198,8 @@ def run_ours(args):
         launch(da, db, d_out)
         h_out.copy_(d_out, non_blocking=True)
 
-    e2e_steps = max(2, min(args.steps, 5))
-    for _ in range(2):
+    e2e_steps = 0 if args.kernel_only else max(2, min(args.steps, 5))
+    for _ in range(2 if e2e_steps else 0):
         e2e_step()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -208,11 +208,11 @@ def run_ours(args):
         e2e_step()
     e1.record()
     barrier()
-    e2e_ms = e0.elapsed_time(e1)
+    e2e_ms = e0.elapsed_time(e1) if e2e_steps else float("nan")
 
     # ---- single-launch latency of ONE instance (the reference API's granularity), L2-hot ----------------------
     lat_us = None
-    if w["op"] == "spmm":
+    if w["op"] == "spmm" and not args.kernel_only:
         for _ in range(5):
             ops.spmm.wmmaSpmm(a.m_vec, V, N, K, ri, ro, ci, d_a[0], d_b[0], d_out[0]) if path == VS_PATH_TENSOR else \
                 ops.spmm.cudaSpmm(a.m_vec, V, N, K, ri, ro, ci, d_a[0], d_b[0], d_out[0])
@@ -266,7 +266,7 @@ def run_ours(args):
             "single_launch_latency_us": lat_us,
             "clocks": clocks,
         }
-        if world == 1 and not args.no_cpu:
+        if world == 1 and not args.no_cpu and not args.kernel_only:
             line["cpu_baseline"] = cpu_leg(w, a, budget_s=12.0)
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -357,6 +357,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="spmm_v8_s90", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="device-resident leg only (for profiler captures): no end-to-end, latency or CPU legs")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

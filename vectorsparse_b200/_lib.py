@@ -8,7 +8,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libvsparse_b200.so")
+# VSPARSE_B200_LIB selects another build of the same library (an instrumented one, for instance)
+LIB_PATH = os.environ.get("VSPARSE_B200_LIB") or os.path.join(_HERE, "libvsparse_b200.so")
 
 VS_F16, VS_F32 = 0, 1
 VS_PATH_TENSOR, VS_PATH_CUDA_CORE = 0, 1

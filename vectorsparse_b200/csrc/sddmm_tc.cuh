@@ -46,7 +46,8 @@ struct Smem {
     static constexpr int kRow = kB + kStages * kBStageBytes;
     static constexpr int kJ0 = kRow + kItemsPerPhase * 4;
     static constexpr int kEnd = kJ0 + kItemsPerPhase * 4;
-    static constexpr int kMeta = kEnd + kItemsPerPhase * 4;
+    static constexpr int kItemB = kEnd + kItemsPerPhase * 4;
+    static constexpr int kMeta = kItemB + kItemsPerPhase * 4;
     static constexpr int kBarEmpty = kMeta + kMetaRing * (int)sizeof(StageMeta);
     static constexpr int kBarAcc = kBarEmpty + kStages * 8;
     static constexpr int kTmemHolder = kBarAcc + kAccSlots * 8;
@@ -70,6 +71,7 @@ __global__ void __launch_bounds__(kThreads) sddmm_tc_kernel(const SddmmParams p,
     int *l_row = reinterpret_cast<int *>(sm + Smem::kRow);
     int *l_j0 = reinterpret_cast<int *>(sm + Smem::kJ0);
     int *l_end = reinterpret_cast<int *>(sm + Smem::kEnd);
+    int *l_b = reinterpret_cast<int *>(sm + Smem::kItemB);
     StageMeta *meta = reinterpret_cast<StageMeta *>(sm + Smem::kMeta);
     volatile uint32_t *tmem_holder = reinterpret_cast<volatile uint32_t *>(sm + Smem::kTmemHolder);
     const uint32_t bar_empty = base + Smem::kBarEmpty;
@@ -109,9 +111,11 @@ __global__ void __launch_bounds__(kThreads) sddmm_tc_kernel(const SddmmParams p,
         const int cnt = (int)((my_items - ph0 < kItemsPerPhase) ? (my_items - ph0) : kItemsPerPhase);
         for (int q = t; q < cnt; q += kThreads) {
             const int64_t w = blockIdx.x + (ph0 + q) * G;
-            const int o = (int)(w % p.m_vec);
+            const int64_t b = w / p.m_vec;  // the only 64-bit division: once per item, not per stage
+            const int o = (int)(w - b * p.m_vec);
             const int row = __ldg(p.row_indices + o);
             l_row[q] = row;
+            l_b[q] = (int)b;
             l_j0[q] = __ldg(p.row_offsets + row);
             l_end[q] = __ldg(p.row_offsets + row + 1);
         }
@@ -175,8 +179,7 @@ __global__ void __launch_bounds__(kThreads) sddmm_tc_kernel(const SddmmParams p,
                 if (g_stage >= (uint32_t)kStages) {
                     if (!tc::mbar_wait(bar_empty + 8 * slot, ((g_stage / kStages) - 1u) & 1u)) timeout = 1;
                 }
-                const int64_t w = blockIdx.x + (ph0 + q) * G;
-                const int b = (int)(w / p.m_vec);
+                const int b = l_b[q];
                 const int row = l_row[q];
                 const __half *rhs = static_cast<const __half *>(p.rhs) + (int64_t)b * p.stride_rhs;
                 const __half *lhs = static_cast<const __half *>(p.lhs) + (int64_t)b * p.stride_lhs;

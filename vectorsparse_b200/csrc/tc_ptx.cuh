@@ -21,22 +21,39 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void fence_mbar_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
+// One poll: the thread may be suspended by the hardware for up to kSuspendNs while the phase is incomplete,
+// so a waiting warp does not burn issue slots.
+#ifndef VS_SUSPEND_NS
+#define VS_SUSPEND_NS 10000
+#endif
+constexpr uint32_t kSuspendNs = VS_SUSPEND_NS;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
+#ifdef VS_EXP_TESTWAIT
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
         "selp.u32 %0, 1, 0, p;\n"
         "}\n"
         : "=r"(ok)
         : "r"(bar), "r"(parity)
         : "memory");
+#else
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(kSuspendNs)
+        : "memory");
+#endif
     return ok != 0;
 }
-// Polls at most `kMaxPolls` times (each try_wait itself blocks for a hardware-defined short interval).
-// Returns false if the phase never completed.
-constexpr uint32_t kMaxPolls = 1u << 20;
+// Polls at most kMaxPolls times (a few seconds at worst).  Returns false if the phase never completed.
+constexpr uint32_t kMaxPolls = 1u << 18;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     for (uint32_t i = 0; i < kMaxPolls; ++i)
         if (mbar_try_wait(bar, parity)) return true;
@@ -94,6 +111,16 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
     return (uint64_t)((saddr & 0x3ffffu) >> 4) | ((uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16) |
            ((uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46) | (swizzle << 61);
 }
+// The same descriptor as two 32-bit halves: `hi` is constant for an operand, `lo` moves with the start address
+// (add bytes >> 4), which keeps per-MMA descriptor arithmetic to one 32-bit add.
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+    return ((saddr & 0x3ffffu) >> 4) | (((lbo_bytes >> 4) & 0x3fffu) << 16);
+}
+__device__ __forceinline__ uint32_t smem_desc_hi(uint32_t sbo_bytes, uint32_t swizzle) {
+    return ((sbo_bytes >> 4) & 0x3fffu) | (1u << 14) | (swizzle << 29);
+}
+__device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi) { return ((uint64_t)hi << 32) | lo; }
+
 // Instruction descriptor for kind::f16 with fp16 operands and fp32 accumulation.
 // a_mn / b_mn: 1 when the operand is MN-major (contiguous along M resp. N), 0 when K-major.
 __host__ __device__ constexpr uint32_t make_idesc_f16(int M, int N, int a_mn, int b_mn) {

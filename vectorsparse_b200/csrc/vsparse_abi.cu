@@ -93,7 +93,7 @@ template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStre
     if (rc != VS_OK) return rc;
     const int n_tiles = (p.N + tcspmm::kTileN - 1) / tcspmm::kTileN;
     const int64_t items = (int64_t)p.batch * n_tiles * p.m_vec;
-    const int64_t cap = 2ll * d->sm_count;  // two CTAs fit per SM (shared memory and tensor memory)
+    const int64_t cap = (int64_t)tcspmm::kCtasPerSm * d->sm_count;  // persistent CTAs
     const unsigned grid = (unsigned)(items < cap ? items : cap);
     kernel<<<grid, tcspmm::kThreads, tcspmm::kSmemBytes, s>>>(p, d->status);
     return (int)cudaGetLastError();
@@ -407,6 +407,17 @@ VS_EXPORT int vs_device_status(int clear, uint32_t *status) {
     if (clear) VS_CUDA_TRY(cudaMemset(d->status, 0, sizeof(uint32_t)));
     return VS_OK;
 }
+
+#ifdef VS_TC_PROFILE
+// Instrumented build only: reads (and clears) the per-role cycle counters of the tensor-core SpMM.
+VS_EXPORT int vs_debug_prof(unsigned long long *out16) {
+    VS_CUDA_TRY(cudaDeviceSynchronize());
+    VS_CUDA_TRY(cudaMemcpyFromSymbol(out16, tcspmm::g_prof, sizeof(unsigned long long) * 16));
+    unsigned long long zero[16] = {0};
+    VS_CUDA_TRY(cudaMemcpyToSymbol(tcspmm::g_prof, zero, sizeof(zero)));
+    return VS_OK;
+}
+#endif
 
 VS_EXPORT int vs_selftest_mma(const void *image, int image_bytes, const uint64_t *descs, int n_mma,
                               uint32_t idesc, int ncols, float fill, float *out, void *stream) {
