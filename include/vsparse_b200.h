@@ -159,6 +159,14 @@ int vs_device_status(int clear, uint32_t *status);
 int vs_selftest_mma(const void *image, int image_bytes, const uint64_t *descs, int n_mma, uint32_t idesc,
                     int ncols, float fill, float *out, void *stream);
 
+/* Row-gather self-test (diagnostic; no counterpart in the reference): `groups` (1..32) hardware row gathers of
+ * four rows each — indices from row_indices[4*groups] (device), rows >= `rows` read as zeros — 64 fp16 columns
+ * wide starting at column x (a multiple of 8) of the row-major fp16 matrix [rows x cols]; the 512-byte blocks
+ * land consecutively in a 1024-byte aligned shared-memory buffer with the 128-byte swizzle, which is copied raw
+ * to out[groups * 512] bytes. */
+int vs_selftest_gather4(const void *matrix, int rows, int cols, const int32_t *row_indices, int groups, int x,
+                        void *out, void *stream);
+
 /* ------------------------------------------------------------------------------------------------------
  * CVSE builder, row swizzle and generators — HOST functions on HOST arrays.
  * ---------------------------------------------------------------------------------------------------- */

@@ -77,3 +77,26 @@ def test_mn_major_spmm_layout():
     got = run(image, descs, idesc(128, 16, 1, 1), 16)
     want = A.astype(np.float32) @ B.astype(np.float32)
     assert np.array_equal(got, want)
+
+
+def test_tma_row_gather4():
+    """Four-row hardware gathers: rows land consecutively, 128 bytes each, 16-byte chunks XOR-swizzled with the
+    row's position inside its 1024-byte block; rows outside the matrix arrive as zeros."""
+    rng = np.random.default_rng(2)
+    rows, cols, groups, x = 50, 192, 6, 64
+    mat = rng.integers(-100, 100, (rows, cols)).astype(np.float16)
+    idx = rng.integers(0, rows, 4 * groups).astype(np.int32)
+    idx[5] = rows          # out of range: zero fill
+    idx[10] = rows + 7
+    d_mat = torch.from_numpy(mat).to("cuda:0")
+    d_idx = torch.from_numpy(idx).to("cuda:0")
+    out = torch.zeros(groups * 512, dtype=torch.uint8, device="cuda:0")
+    rc = _lib.lib().vs_selftest_gather4(d_mat.data_ptr(), rows, cols, d_idx.data_ptr(), groups, x, out.data_ptr(), None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    got = out.cpu().numpy().view(np.float16).reshape(groups * 4, 8, 8)   # [row slot][16-byte chunk][8 halves]
+    for slot in range(groups * 4):
+        src = mat[idx[slot], x:x + 64].reshape(8, 8) if idx[slot] < rows else np.zeros((8, 8), np.float16)
+        for c in range(8):
+            assert np.array_equal(got[slot, c ^ (slot % 8)], src[c]), (slot, c)

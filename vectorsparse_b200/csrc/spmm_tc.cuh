@@ -104,15 +104,21 @@ struct OwnIter {
     }
 };
 
-// Bounded mbarrier wait that also gives up when another role of the CTA has raised the abort flag.
+// Bounded mbarrier wait that also gives up when another role of the CTA has raised the abort flag.  Between
+// polls the warp sleeps kSleepNs, so that the many warps that are waiting at any moment (a role waits most of
+// the time in a balanced pipeline) leave the issue slots to the warps that are working.
+template <int kSleepNs>
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    if (tc::mbar_try_wait(bar, parity)) return true;
     for (uint32_t i = 0; i < tc::kMaxPolls; ++i) {
+        if (kSleepNs > 0) __nanosleep(kSleepNs);
         if (tc::mbar_try_wait(bar, parity)) return true;
         if ((i & 15u) == 15u && *abort_flag) return false;
     }
     *abort_flag = 1;
     return false;
 }
+constexpr int kSleepProducer = 200, kSleepMma = 0, kSleepEpilogue = 200;
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -258,7 +264,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) spmm_tc_kernel(const Spm
             bool ok_run = true;
             VS_PROF_T0();
             while (cur.valid() && ok_run) {
-                if (g >= (uint32_t)kStages) ok_run = wait_or_abort(bar_empty + 8 * slot, ((g / kStages) - 1u) & 1u, abort_flag);
+                if (g >= (uint32_t)kStages) ok_run = wait_or_abort<kSleepProducer>(bar_empty + 8 * slot, ((g / kStages) - 1u) & 1u, abort_flag);
                 if (!ok_run) break;
                 VS_PROF_ADD(0);   // producer: wait for the slot
                 // this stage's indices were fetched two of this warp's stages ago: at most the newest cp.async
@@ -335,13 +341,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) spmm_tc_kernel(const Spm
                     int rem = l_end[q] - l_j0[q];
                     const uint32_t acc = ic % kAccSlots;
                     if (ic >= (uint32_t)kAccSlots)
-                        ok_run = wait_or_abort(bar_acc_empty + 8 * acc, ((ic / kAccSlots) - 1u) & 1u, abort_flag);
+                        ok_run = wait_or_abort<kSleepMma>(bar_acc_empty + 8 * acc, ((ic / kAccSlots) - 1u) & 1u, abort_flag);
                     const uint32_t d = tmem_base + acc * kAccCols;
                     uint32_t accumulate = 0;
                     VS_PROF_ADD(3);   // mma: wait for a free accumulator (+ item bookkeeping)
                     do {
                         const uint32_t slot = g % kStages;
-                        if (ok_run) ok_run = wait_or_abort(bar_full + 8 * slot, (g / kStages) & 1u, abort_flag);
+                        if (ok_run) ok_run = wait_or_abort<kSleepMma>(bar_full + 8 * slot, (g / kStages) & 1u, abort_flag);
                         if (!ok_run) break;
                         VS_PROF_ADD(4);   // mma: wait for a full stage
 #ifndef VS_EXP_NOFENCE
@@ -385,7 +391,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) spmm_tc_kernel(const Spm
                 const uint32_t ic = g_item + (uint32_t)q;
                 const uint32_t acc = ic % kAccSlots;
                 // warp-uniform outcome: tcgen05.ld below needs all 32 lanes
-                ok_run = __all_sync(0xffffffffu, wait_or_abort(bar_acc_full + 8 * acc, (ic / kAccSlots) & 1u, abort_flag));
+                ok_run = __all_sync(0xffffffffu, wait_or_abort<kSleepEpilogue>(bar_acc_full + 8 * acc, (ic / kAccSlots) & 1u, abort_flag));
                 if (!ok_run) break;
                 VS_PROF_ADD(6);   // epilogue: wait for the accumulator
                 tc::tc_fence_after_sync();

@@ -83,6 +83,24 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
 // tcgen05.mma reads operands through.
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// ---- TMA row gather ------------------------------------------------------------------------------------------
+// Arms `bar` for `bytes` of asynchronous copies and arrives once (the barrier completes when the bytes land).
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Gathers four rows (r0..r3) of a 2-D row-major tensor, `box` columns wide starting at column x, into four
+// consecutive rows of shared memory at `dst`; the tensor map carries the box width (x 1 row), element type and
+// swizzle mode.  Rows outside the tensor arrive as zeros.  x * element size must be a multiple of 16 bytes.
+// No multicast: the destination is this CTA's own shared memory.
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const void *tensor_map, uint32_t bar, int x, int r0, int r1,
+                                            int r2, int r3) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(dst),
+        "l"(tensor_map), "r"(bar), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+        : "memory");
+}
+
 // ---- tensor memory ---------------------------------------------------------------------------------------
 // Executed by one full warp.  `ncols` is a power of two in [32, 512].  The base address lands in *dst_smem.
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {

@@ -2,6 +2,8 @@
 // returns the raw accumulator, so that the host can check a descriptor / layout convention against a plain
 // matrix product.  Used by the GPU tests; never on a product path.
 #pragma once
+#include <cuda.h>
+
 #include "tc_ptx.cuh"
 
 namespace vs {
@@ -83,6 +85,34 @@ __global__ void __launch_bounds__(128) sandbox_kernel(const uint8_t *image, int 
     tc::tc_fence_before_sync();
     __syncthreads();
     if (warp == 0) tc::tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// Row-gather self-test: `groups` gather4 operations (4 row indices each, from `rows`) at column x into
+// consecutive 512-byte blocks of a 1024-byte aligned buffer, which is then copied out raw.
+constexpr uint32_t kStatusGatherTimeout = 8u;
+__global__ void __launch_bounds__(32) gather4_kernel(const __grid_constant__ CUtensorMap map, const int *rows, int groups,
+                                                    int x, uint8_t *out, uint32_t *status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = tc::smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *sm = smem_raw + (base - raw);
+    const int lane = threadIdx.x;
+    const uint32_t bar = base + groups * 512;
+    for (int i = lane; i < groups * 512 / 16; i += 32) reinterpret_cast<uint4 *>(sm)[i] = make_uint4(0xdeadbeefu, 0xdeadbeefu, 0xdeadbeefu, 0xdeadbeefu);
+    if (lane == 0) {
+        tc::mbar_init(bar, 1);
+        tc::fence_mbar_init();
+    }
+    tc::fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) tc::mbar_expect_tx(bar, (uint32_t)groups * 512u);
+    __syncwarp();
+    if (lane < groups)
+        tc::tma_gather4(base + lane * 512, &map, bar, x, rows[4 * lane], rows[4 * lane + 1], rows[4 * lane + 2], rows[4 * lane + 3]);
+    const bool ok = tc::mbar_wait(bar, 0);
+    __syncwarp();
+    for (int i = lane; i < groups * 512 / 16; i += 32) reinterpret_cast<uint4 *>(out)[i] = reinterpret_cast<uint4 *>(sm)[i];
+    if (!ok && lane == 0) atomicOr(status, kStatusGatherTimeout);
 }
 
 }  // namespace tcselftest

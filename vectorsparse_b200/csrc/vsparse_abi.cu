@@ -8,12 +8,15 @@
 
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "vsparse_b200.h"
 #include "common.cuh"
 #include "cuda_core.cuh"
 #include "spmm_tc.cuh"
+#include "spmm_tma.cuh"
 #include "sddmm_tc.cuh"
 #include "tc_selftest.cuh"
 
@@ -63,6 +66,35 @@ template <typename K> int set_smem(K kernel, int bytes) {
     return e == cudaSuccess ? VS_OK : (int)e;
 }
 
+// cuTensorMapEncodeTiled, fetched from the driver at first use (the library does not link libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) return nullptr;
+        return q == cudaDriverEntryPointSuccess ? reinterpret_cast<EncodeTiledFn>(p) : nullptr;
+    }();
+    return fn;
+}
+
+// Tensor map of a row-major fp16 matrix [rows x cols] for row gathers: box = 64 columns x 1 row, 128-byte
+// swizzle, zero fill outside the matrix.
+int make_gather_map(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t cols) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return VS_ERR_DEVICE;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {64, 1};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? VS_OK : VS_ERR_ARG;
+}
+
 // ---- SpMM dispatch ----------------------------------------------------------------------------------------
 template <typename TIn, typename TOut, int V> int launch_spmm_cc(const SpmmParams &p, cudaStream_t s) {
     constexpr int E = Chunk<TIn>::kElems;
@@ -84,18 +116,45 @@ template <typename TIn, typename TOut> int spmm_cc_by_v(int V, const SpmmParams 
     return VS_ERR_VEC_LENGTH;
 }
 
-template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStream_t s) {
-    DeviceInfo *d;
-    int rc = device_info(&d);
-    if (rc != VS_OK) return rc;
+// Software (cp.async) gather: works for any batch stride.
+template <typename TOut, int V> int launch_spmm_tc_cpasync(const SpmmParams &p, cudaStream_t s, DeviceInfo *d) {
     auto kernel = tcspmm::spmm_tc_kernel<TOut, V>;
-    rc = set_smem(kernel, tcspmm::kSmemBytes);
+    int rc = set_smem(kernel, tcspmm::kSmemBytes);
     if (rc != VS_OK) return rc;
     const int n_tiles = (p.N + tcspmm::kTileN - 1) / tcspmm::kTileN;
     const int64_t items = (int64_t)p.batch * n_tiles * p.m_vec;
     const int64_t cap = (int64_t)tcspmm::kCtasPerSm * d->sm_count;  // persistent CTAs
     const unsigned grid = (unsigned)(items < cap ? items : cap);
     kernel<<<grid, tcspmm::kThreads, tcspmm::kSmemBytes, s>>>(p, d->status);
+    return (int)cudaGetLastError();
+}
+
+// TMA row gather: the dense operand of all batch entries must be addressable as one matrix of N-wide rows,
+// i.e. the batch stride is a multiple of N (or zero / a single entry).
+template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStream_t s) {
+    DeviceInfo *d;
+    int rc = device_info(&d);
+    if (rc != VS_OK) return rc;
+    static const bool force_cpasync = []() {
+        const char *e = std::getenv("VSPARSE_B200_GATHER");
+        return e && !std::strcmp(e, "cpasync");
+    }();
+    const bool one = p.batch == 1 || p.stride_rhs == 0;
+    const int64_t rows_per_batch = one ? 0 : p.stride_rhs / p.N;
+    const int64_t total_rows = (one ? 0 : (int64_t)(p.batch - 1) * rows_per_batch) + p.K;
+    const bool tma_ok = !force_cpasync && p.K > 0 && (one || p.stride_rhs % p.N == 0) && total_rows < 0x7fffffffll;
+    if (!tma_ok) return launch_spmm_tc_cpasync<TOut, V>(p, s, d);
+    CUtensorMap map;
+    rc = make_gather_map(&map, p.rhs, (uint64_t)total_rows, (uint64_t)p.N);
+    if (rc != VS_OK) return launch_spmm_tc_cpasync<TOut, V>(p, s, d);
+    auto kernel = tmaspmm::spmm_tma_kernel<TOut, V>;
+    rc = set_smem(kernel, tmaspmm::kSmemBytes);
+    if (rc != VS_OK) return rc;
+    const int n_tiles = (p.N + tmaspmm::kTileN - 1) / tmaspmm::kTileN;
+    const int64_t items = (int64_t)p.batch * n_tiles * p.m_vec;
+    const int64_t cap = (int64_t)tmaspmm::kCtasPerSm * d->sm_count;  // persistent CTAs
+    const unsigned grid = (unsigned)(items < cap ? items : cap);
+    kernel<<<grid, tmaspmm::kThreads, tmaspmm::kSmemBytes, s>>>(p, map, (int)rows_per_batch, (int)total_rows, d->status);
     return (int)cudaGetLastError();
 }
 
@@ -406,6 +465,23 @@ VS_EXPORT int vs_device_status(int clear, uint32_t *status) {
     VS_CUDA_TRY(cudaMemcpy(status, d->status, sizeof(uint32_t), cudaMemcpyDeviceToHost));
     if (clear) VS_CUDA_TRY(cudaMemset(d->status, 0, sizeof(uint32_t)));
     return VS_OK;
+}
+
+VS_EXPORT int vs_selftest_gather4(const void *matrix, int rows, int cols, const int32_t *row_indices, int groups,
+                                  int x, void *out, void *stream) {
+    if (!matrix || !row_indices || !out) return VS_ERR_NULL;
+    if (rows < 1 || cols < 64 || cols % 8 != 0 || groups < 1 || groups > 32 || x < 0 || x % 8 != 0) return VS_ERR_SHAPE;
+    if (!aligned16(matrix) || !aligned16(out)) return VS_ERR_ALIGN;
+    DeviceInfo *d;
+    int rc = device_info(&d);
+    if (rc != VS_OK) return rc;
+    CUtensorMap map;
+    rc = make_gather_map(&map, matrix, (uint64_t)rows, (uint64_t)cols);
+    if (rc != VS_OK) return rc;
+    const int smem = groups * 512 + 64 + 1024;
+    tcselftest::gather4_kernel<<<1, 32, smem, static_cast<cudaStream_t>(stream)>>>(
+        map, row_indices, groups, x, static_cast<uint8_t *>(out), d->status);
+    return (int)cudaGetLastError();
 }
 
 #ifdef VS_TC_PROFILE
