@@ -19,10 +19,10 @@
 // barrier inside a phase:
 //   * warps 0-3, epilogue: wait for `acc_full`, tcgen05.ld their 32 TMEM lanes, release the accumulator
 //     (`acc_empty`), transpose through a warp-private staging tile and write C with 16-byte stores.
-//   * warps 4-7, producers: warp w takes every 4th stage.  It waits for the stage's ring slot (`empty`), arms
+//   * warps 4-8, producers: warp w takes every 5th stage.  It waits for the stage's ring slot (`empty`), arms
 //     the slot's `full` mbarrier with the byte count, issues the gathers, copies the value vectors with
 //     cp.async (arriving on `full` when they land), and prefetches the column indices of its stage n+2.
-//   * warp 8, one thread: waits for `full` in ring order, issues the MMAs of the stage and commits them to the
+//   * warp 9, one thread: waits for `full` in ring order, issues the MMAs of the stage and commits them to the
 //     slot's `empty` mbarrier and, at the end of a row, to `acc_full`.
 // Work items are (batch, column tile, vector-row in row_indices order), dealt round-robin to the CTAs so that
 // the descending-length order the row swizzle produces becomes a longest-first schedule; each CTA decodes its
@@ -40,12 +40,13 @@ namespace tmaspmm {
 
 constexpr int kEpiWarps = 4;                             // warps 0..3 (TMEM lane quarter = warp index)
 constexpr int kProducerWarp0 = 4;
-constexpr int kProducerWarps = 4;                        // warps 4..7
-constexpr int kMmaWarp = kProducerWarp0 + kProducerWarps;  // warp 8
-constexpr int kThreads = (kMmaWarp + 1) * 32;            // 288
+constexpr int kProducerWarps = 5;                        // warps 4..8: one per ring slot
+constexpr int kMmaWarp = kProducerWarp0 + kProducerWarps;  // warp 9
+constexpr int kThreads = (kMmaWarp + 1) * 32;            // 320
 constexpr int kCtasPerSm = 2;
 constexpr int kTileN = 128;                              // dense columns per work item (MMA M)
 constexpr int kStageNnz = 64;                            // nonzero vectors per stage (up to four K=16 MMAs)
+constexpr int kMmaPerStage = kStageNnz / 16;
 constexpr int kStages = 5;                               // shared-memory ring
 constexpr int kAStageBytes = kStageNnz * kTileN * 2;     // 16 KiB
 constexpr int kVStageBytes = 2 * kStageNnz * 16;         // 2 KiB: 64 value slots of 16 B, then 1 KiB of zeros
@@ -255,15 +256,18 @@ spmm_tma_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map, int
             uint32_t g = g_stage + (uint32_t)s0;
             int n = 0;
             bool ok_run = true;
+            VS_PROF_T0();
             while (cur.valid() && ok_run) {
                 const uint32_t slot = g % kStages;
                 if (g >= (uint32_t)kStages)
                     ok_run = wait_or_abort<kSleepProducer>(bar_empty + 8 * slot, ((g / kStages) - 1u) & 1u, abort_flag);
                 if (!ok_run) break;
+                VS_PROF_ADD(0);   // producer: wait for the slot
                 // this stage's indices were fetched two of this warp's stages ago: at most the newest cp.async
                 // group may still be pending; the warp barrier publishes the landed indices to all lanes
                 tc::cp_async_wait<1>();
                 __syncwarp();
+                VS_PROF_ADD(1);   // producer: wait for indices
                 const int q = cur.q;
                 const int b = l_b[q];
                 const int n0 = l_n0[q];
@@ -310,8 +314,10 @@ spmm_tma_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map, int
                 cur.advance(kProducerWarps);
                 g += kProducerWarps;
                 ++n;
+                VS_PROF_ADD(2);   // producer: issue
             }
             tc::cp_async_wait<0>();
+            VS_PROF_FLUSH(0);
         } else if (warp == kMmaWarp) {
             // =========================== MMA issuer ========================================================
             // One issuing thread for all stages, in ring order: an mbarrier parity wait is only safe for a
@@ -322,47 +328,62 @@ spmm_tma_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map, int
                 const uint32_t a_hi = tc::smem_desc_hi(1024, (uint32_t)tc::kSwizzle128B);
                 const uint32_t b_lo0 = tc::smem_desc_lo(base + Smem::kV, 128);
                 const uint32_t b_hi = tc::smem_desc_hi(kVStageBytes / 2, (uint32_t)tc::kSwizzleNone);
-                uint32_t g = g_stage, ic = g_item;
+                // ring / accumulator positions are carried incrementally: this thread's instruction stream is the
+                // serial part of the pipeline, so every division or dependent shared-memory load counts
+                uint32_t slot = g_stage % kStages, full_parity = (g_stage / kStages) & 1u;
+                uint32_t acc = g_item % kAccSlots, acc_parity = ((g_item / kAccSlots) & 1u) ^ 1u;   // parity of the PREVIOUS use
+                bool acc_wait = g_item >= (uint32_t)kAccSlots;
+                uint32_t a_lo = a_lo0 + slot * (kAStageBytes >> 4), b_lo = b_lo0 + slot * (kVStageBytes >> 4);
                 bool ok_run = true;
-                for (int q = 0; q < cnt && ok_run; ++q, ++ic) {
-                    int rem = l_end[q] - l_j0[q];
-                    const uint32_t acc = ic % kAccSlots;
-                    if (ic >= (uint32_t)kAccSlots)
-                        ok_run = wait_or_abort<kSleepMma>(bar_acc_empty + 8 * acc, ((ic / kAccSlots) - 1u) & 1u, abort_flag);
+                int len = l_end[0] - l_j0[0];
+                VS_PROF_T0();
+                for (int q = 0; q < cnt && ok_run; ++q) {
+                    int rem = len;
+                    if (q + 1 < cnt) len = l_end[q + 1] - l_j0[q + 1];   // next item's length: off the critical path
+                    if (acc_wait) ok_run = wait_or_abort<kSleepMma>(bar_acc_empty + 8 * acc, acc_parity, abort_flag);
                     const uint32_t d = tmem_base + acc * kAccCols;
                     uint32_t accumulate = 0;
+                    VS_PROF_ADD(3);   // mma: wait for a free accumulator (+ item bookkeeping)
                     do {
-                        const uint32_t slot = g % kStages;
-                        if (ok_run) ok_run = wait_or_abort<kSleepMma>(bar_full + 8 * slot, (g / kStages) & 1u, abort_flag);
+                        if (ok_run) ok_run = wait_or_abort<kSleepMma>(bar_full + 8 * slot, full_parity, abort_flag);
                         if (!ok_run) break;
+                        VS_PROF_ADD(4);   // mma: wait for a full stage
                         tc::fence_proxy_async();   // the value vectors were written by cp.async (generic proxy)
                         tc::tc_fence_after_sync();
-                        const int n_mma = rem >= kStageNnz ? 4 : max(1, (rem + 15) >> 4);
-                        const uint32_t a_lo = a_lo0 + slot * (kAStageBytes >> 4);
-                        const uint32_t b_lo = b_lo0 + slot * (kVStageBytes >> 4);
+                        const int n_mma = rem >= kStageNnz ? kMmaPerStage : max(1, (rem + 15) >> 4);
                         tc::mma_f16_ss(d, tc::desc64(a_lo, a_hi), tc::desc64(b_lo, b_hi), kIdesc, accumulate);
                         if (n_mma > 1) tc::mma_f16_ss(d, tc::desc64(a_lo + 128, a_hi), tc::desc64(b_lo + 16, b_hi), kIdesc, 1u);
-                        if (n_mma > 2) tc::mma_f16_ss(d, tc::desc64(a_lo + 256, a_hi), tc::desc64(b_lo + 32, b_hi), kIdesc, 1u);
-                        if (n_mma > 3) tc::mma_f16_ss(d, tc::desc64(a_lo + 384, a_hi), tc::desc64(b_lo + 48, b_hi), kIdesc, 1u);
+                        if (kMmaPerStage > 2 && n_mma > 2) tc::mma_f16_ss(d, tc::desc64(a_lo + 256, a_hi), tc::desc64(b_lo + 32, b_hi), kIdesc, 1u);
+                        if (kMmaPerStage > 3 && n_mma > 3) tc::mma_f16_ss(d, tc::desc64(a_lo + 384, a_hi), tc::desc64(b_lo + 48, b_hi), kIdesc, 1u);
                         tc::mma_commit(bar_empty + 8 * slot);
                         accumulate = 1;
                         rem -= kStageNnz;
-                        ++g;
+                        if (++slot == (uint32_t)kStages) {
+                            slot = 0; full_parity ^= 1u;
+                            a_lo = a_lo0; b_lo = b_lo0;
+                        } else {
+                            a_lo += kAStageBytes >> 4; b_lo += kVStageBytes >> 4;
+                        }
+                        VS_PROF_ADD(5);   // mma: issue
                     } while (rem > 0);
                     if (ok_run) tc::mma_commit(bar_acc_full + 8 * acc);
+                    if (++acc == (uint32_t)kAccSlots) { acc = 0; acc_parity ^= 1u; acc_wait = true; }
                 }
+                VS_PROF_FLUSH(3);
             }
         } else {
             // =========================== epilogue ==========================================================
             const int quarter = warp;                     // warps 0..3: TMEM lanes 32*warp .. +31
             uint8_t *stg = sm + Smem::kStaging + warp * kStagingBytes;
             bool ok_run = true;
+            VS_PROF_T0();
             for (int q = 0; q < cnt && ok_run; ++q) {
                 const uint32_t ic = g_item + (uint32_t)q;
                 const uint32_t acc = ic % kAccSlots;
                 // warp-uniform outcome: tcgen05.ld below needs all 32 lanes
                 ok_run = __all_sync(0xffffffffu, wait_or_abort<kSleepEpilogue>(bar_acc_full + 8 * acc, (ic / kAccSlots) & 1u, abort_flag));
                 if (!ok_run) break;
+                VS_PROF_ADD(6);   // epilogue: wait for the accumulator
                 tc::tc_fence_after_sync();
                 uint32_t r[8];
                 tc::tmem_ld_x8(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kAccCols, r);
@@ -391,7 +412,9 @@ spmm_tma_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map, int
                         }
                     }
                 }
+                VS_PROF_ADD(7);   // epilogue: load, transpose, store
             }
+            VS_PROF_FLUSH(6);
         }
 
         // ---- phase end: everybody is done with the lists; advance the global counters identically ------------

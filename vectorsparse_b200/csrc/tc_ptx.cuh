@@ -8,6 +8,20 @@
 #include <stdint.h>
 
 namespace vs {
+
+#ifdef VS_TC_PROFILE
+// Instrumented build only: clock cycles spent per role and wait site, kept in registers and summed over CTAs
+// (lane 0 of each warp) when the role finishes a phase.
+__device__ unsigned long long g_prof[16];
+#define VS_PROF_T0() long long prof_t0 = clock64(); long long prof_acc[3] = {0, 0, 0}
+#define VS_PROF_ADD(slot) do { long long prof_t1 = clock64(); prof_acc[(slot) % 3] += prof_t1 - prof_t0; prof_t0 = prof_t1; } while (0)
+#define VS_PROF_FLUSH(first) do { if (lane == 0) { for (int pi = 0; pi < 3; ++pi) atomicAdd(&g_prof[(first) + pi], (unsigned long long)prof_acc[((first) + pi) % 3]); } } while (0)
+#else
+#define VS_PROF_T0() do { } while (0)
+#define VS_PROF_ADD(slot) do { } while (0)
+#define VS_PROF_FLUSH(first) do { } while (0)
+#endif
+
 namespace tc {
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {

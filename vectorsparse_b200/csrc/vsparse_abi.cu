@@ -488,9 +488,9 @@ VS_EXPORT int vs_selftest_gather4(const void *matrix, int rows, int cols, const 
 // Instrumented build only: reads (and clears) the per-role cycle counters of the tensor-core SpMM.
 VS_EXPORT int vs_debug_prof(unsigned long long *out16) {
     VS_CUDA_TRY(cudaDeviceSynchronize());
-    VS_CUDA_TRY(cudaMemcpyFromSymbol(out16, tcspmm::g_prof, sizeof(unsigned long long) * 16));
+    VS_CUDA_TRY(cudaMemcpyFromSymbol(out16, vs::g_prof, sizeof(unsigned long long) * 16));
     unsigned long long zero[16] = {0};
-    VS_CUDA_TRY(cudaMemcpyToSymbol(tcspmm::g_prof, zero, sizeof(zero)));
+    VS_CUDA_TRY(cudaMemcpyToSymbol(vs::g_prof, zero, sizeof(zero)));
     return VS_OK;
 }
 #endif
