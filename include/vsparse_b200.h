@@ -126,6 +126,27 @@ int vs_attention_cvse(int path, int m_vec, int vec_length, int n, int d, int non
                       const void *q, const void *kmat, const void *vmat, void *out, void *workspace,
                       float scale, int batch, void *stream);
 
+/* vs_attention_cvse for callers that may not allocate device memory.  No counterpart in the reference.
+ *
+ * Some hosts of this library cannot hand it a workspace: an inference runtime that plans all device memory
+ * ahead of time and gives plug-ins no allocator, a service loop that must never hit the implicit device-wide
+ * synchronisation of cudaMalloc / cudaFree, a caller that simply has no allocation hook at the point where
+ * attention runs.  For them the probabilities (batch * nonzeros_vec * vec_length fp16 values) live in an
+ * 8 MiB (8 388 608 byte) array that is part of the library image; every GPU that loads the library holds it
+ * until the process exits.  Same arguments and results as vs_attention_cvse, minus `workspace`.
+ *
+ *  - Larger requests are refused with VS_ERR_SHAPE and a message on stderr; nothing is launched.
+ *  - The call itself, and everything it calls, uses no cudaMalloc, cudaFree or allocating library routine.
+ *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *    current).  Make that first call outside any stream capture.
+ *  - All calls on a device share the one array, and it keeps what the last call left in it.  Nothing in it has
+ *    to start at zero: each call writes every probability before it reads it.  Two calls that overlap on the
+ *    GPU (different streams, or graphs replayed concurrently) race on it: serialise them. */
+int vs_attention_cvse_static(int path, int m_vec, int vec_length, int n, int d, int nonzeros_vec,
+                             const int32_t *row_indices, const int32_t *row_offsets, const int32_t *col_indices,
+                             const void *q, const void *kmat, const void *vmat, void *out, float scale, int batch,
+                             void *stream);
+
 /* ------------------------------------------------------------------------------------------------------
  * Host-buffer convenience forms (every pointer is a HOST pointer).  They allocate device buffers, copy the
  * operands in, run the operator, copy the result back and free the buffers, synchronising before returning:

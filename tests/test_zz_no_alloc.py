@@ -1,0 +1,59 @@
+"""vs_attention_cvse_static: fixed-mask attention for callers that cannot allocate device memory (a runtime that
+pre-plans every buffer, a loop that must stay clear of cudaMalloc's device-wide synchronisation).  Its scratch
+is an array inside the library, so the test checks, through the C ABI, that it gives exactly what
+vs_attention_cvse gives with a caller workspace — on two calls in a row, the second on a different problem, since
+the array keeps the first call's contents — and that an oversized request is refused before anything runs.
+
+Collected last on purpose: a failure here must not hide the other tests from a run that stops at the first failure."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from vectorsparse_b200 import VS_PATH_CUDA_CORE, VS_PATH_TENSOR, _lib, cvse, ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def attention_pair(path, seed, heads, n, band, sparsity):
+    """Runs both entry points on one seeded problem; returns (with caller workspace, with built-in scratch)."""
+    V, d = 8, 64
+    a = cvse.generate(cvse.GEN_BAND, seed, n // V, n, V, sparsity, band=band)
+    ri, ro, ci = a.to_device(DEV)
+    q, k, v = (torch.from_numpy(cvse.fill_random((heads, n, d), np.float16, cvse.DIST_NORMAL, seed + i, 1.0)).to(DEV)
+               for i in range(3))
+    want = torch.full((heads, n, d), float("nan"), dtype=torch.float16, device=DEV)
+    got = torch.full_like(want, float("nan"))
+    ws = torch.empty((heads, a.nnz_vec * V), dtype=torch.float16, device=DEV)
+    L = _lib.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    args = (path, a.m_vec, V, n, d, a.nnz_vec, ri.data_ptr(), ro.data_ptr(), ci.data_ptr(), q.data_ptr(),
+            k.data_ptr(), v.data_ptr())
+    assert L.vs_attention_cvse(*args, want.data_ptr(), ws.data_ptr(), C.c_float(0.125), heads, stream) == 0
+    assert L.vs_attention_cvse_static(*args, got.data_ptr(), C.c_float(0.125), heads, stream) == 0
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    return want, got
+
+
+@pytest.mark.parametrize("path", [VS_PATH_TENSOR, VS_PATH_CUDA_CORE])
+def test_two_calls_in_a_row_match_the_workspace_form(path):
+    want, got = attention_pair(path, seed=31, heads=3, n=512, band=64, sparsity=0.8)
+    assert not torch.isnan(got).any()
+    assert torch.equal(got, want)          # same kernels in the same order: the results are bit-identical
+    # second call: a smaller, different problem over the scratch the first call left behind
+    want2, got2 = attention_pair(path, seed=77, heads=2, n=256, band=32, sparsity=0.7)
+    assert not torch.isnan(got2).any()
+    assert torch.equal(got2, want2)
+
+
+def test_requests_beyond_the_built_in_scratch_are_refused():
+    L = _lib.lib()
+    z = torch.zeros(64, dtype=torch.int32, device=DEV)
+    p = z.data_ptr()
+    # 64 heads x 100000 vectors x 8 values x 2 bytes = 102 MB > 8 MiB: rejected on the host, nothing launched
+    rc = L.vs_attention_cvse_static(VS_PATH_TENSOR, 512, 8, 4096, 64, 100000, p, p, p, p, p, p, p, C.c_float(1.0), 64, None)
+    assert rc == -3
+    torch.cuda.synchronize()

@@ -361,6 +361,58 @@ VS_EXPORT int vs_attention_cvse(int path, int m_vec, int vec_length, int n, int 
                            workspace, vmat, out, batch, s_ws, (int64_t)n * d, m * d, stream);
 }
 
+// ---- attention without a caller workspace --------------------------------------------------------------------
+//
+// Scratch for vs_attention_cvse_static: the probabilities between its SDDMM, softmax and SpMM steps.  The array
+// is part of the library image, so every GPU that loads the library carries these 8 MiB until the process exits.
+// In host code the NAME below is only a handle; the device address comes from cudaGetSymbolAddress.
+constexpr size_t kStaticScratchBytes = size_t(8) << 20;
+static __device__ __align__(256) unsigned char g_attention_scratch[kStaticScratchBytes];
+
+namespace {
+void *g_attention_scratch_ptr[kMaxDevices];   // device address of the array, looked up once per device
+std::mutex g_attention_scratch_mutex;
+
+// Must run with the target device current.  The look-up is a runtime query, not an allocation.
+int attention_scratch(void **out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return VS_ERR_ARG;
+    std::lock_guard<std::mutex> lock(g_attention_scratch_mutex);
+    if (!g_attention_scratch_ptr[dev]) {
+        void *ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_attention_scratch);
+        if (e != cudaSuccess) return (int)e;
+        g_attention_scratch_ptr[dev] = ptr;
+    }
+    *out = g_attention_scratch_ptr[dev];
+    return VS_OK;
+}
+}  // namespace
+
+VS_EXPORT int vs_attention_cvse_static(int path, int m_vec, int vec_length, int n, int d, int nonzeros_vec,
+                                       const int32_t *row_indices, const int32_t *row_offsets,
+                                       const int32_t *col_indices, const void *q, const void *kmat, const void *vmat,
+                                       void *out, float scale, int batch, void *stream) {
+    if (batch < 1) return VS_ERR_ARG;
+    if (nonzeros_vec < 0) return VS_ERR_SHAPE;
+    if (!valid_v(vec_length)) return VS_ERR_VEC_LENGTH;
+    const unsigned long long need = 2ull * (unsigned long long)batch * (unsigned long long)nonzeros_vec * (unsigned long long)vec_length;
+    if (need > kStaticScratchBytes) {
+        fprintf(stderr,
+                "vs_attention_cvse_static: batch * nonzeros_vec * vec_length = %llu fp16 probabilities need %llu bytes, "
+                "the built-in scratch holds %zu; use vs_attention_cvse with a workspace of your own\n",
+                need / 2, need, kStaticScratchBytes);
+        return VS_ERR_SHAPE;
+    }
+    void *scratch = nullptr;
+    int rc = attention_scratch(&scratch);
+    if (rc != VS_OK) return rc;
+    return vs_attention_cvse(path, m_vec, vec_length, n, d, nonzeros_vec, row_indices, row_offsets, col_indices, q, kmat,
+                             vmat, out, scratch, scale, batch, stream);
+}
+
 // ---- host-buffer forms -------------------------------------------------------------------------------------
 
 namespace {
