@@ -18,6 +18,7 @@
 #include "spmm_tc.cuh"
 #include "spmm_tma.cuh"
 #include "sddmm_tc.cuh"
+#include "sddmm_tma.cuh"
 #include "tc_selftest.cuh"
 
 #define VS_EXPORT extern "C" __attribute__((visibility("default")))
@@ -186,17 +187,48 @@ template <typename TIn, typename TOut> int sddmm_cc_by_v(int V, const SddmmParam
     return VS_ERR_VEC_LENGTH;
 }
 
-template <typename TOut, int V> int launch_sddmm_tc(const SddmmParams &p, cudaStream_t s) {
-    DeviceInfo *d;
-    int rc = device_info(&d);
-    if (rc != VS_OK) return rc;
+// Software (cp.async) gather: works for any batch stride.
+template <typename TOut, int V> int launch_sddmm_tc_cpasync(const SddmmParams &p, cudaStream_t s, DeviceInfo *d) {
     auto kernel = tcsddmm::sddmm_tc_kernel<TOut, V>;
-    rc = set_smem(kernel, tcsddmm::kSmemBytes);
+    int rc = set_smem(kernel, tcsddmm::kSmemBytes);
     if (rc != VS_OK) return rc;
     const int64_t items = (int64_t)p.batch * p.m_vec;
     const int64_t cap = 2ll * d->sm_count;
     const unsigned grid = (unsigned)(items < cap ? items : cap);
     kernel<<<grid, tcsddmm::kThreads, tcsddmm::kSmemBytes, s>>>(p, d->status);
+    return (int)cudaGetLastError();
+}
+
+// TMA row gather: lhs and rhs of all batch entries must each be addressable as one matrix of k-wide rows, i.e.
+// their batch strides are multiples of k (or zero / a single entry).
+template <typename TOut, int V> int launch_sddmm_tc(const SddmmParams &p, cudaStream_t s) {
+    DeviceInfo *d;
+    int rc = device_info(&d);
+    if (rc != VS_OK) return rc;
+    static const bool force_cpasync = []() {
+        const char *e = std::getenv("VSPARSE_B200_GATHER");
+        return e && !std::strcmp(e, "cpasync");
+    }();
+    const int64_t m = (int64_t)p.m_vec * V;
+    const bool one_r = p.batch == 1 || p.stride_rhs == 0, one_l = p.batch == 1 || p.stride_lhs == 0;
+    const int64_t rpb_r = one_r ? 0 : p.stride_rhs / p.k, rpb_l = one_l ? 0 : p.stride_lhs / p.k;
+    const int64_t rows_r = (one_r ? 0 : (int64_t)(p.batch - 1) * rpb_r) + p.n;
+    const int64_t rows_l = (one_l ? 0 : (int64_t)(p.batch - 1) * rpb_l) + m;
+    const bool tma_ok = !force_cpasync && p.n > 0 && (one_r || p.stride_rhs % p.k == 0) && (one_l || p.stride_lhs % p.k == 0) &&
+                        rows_r < 0x7fffffffll && rows_l < 0x7fffffffll;
+    if (!tma_ok) return launch_sddmm_tc_cpasync<TOut, V>(p, s, d);
+    CUtensorMap map_r, map_l;
+    if (make_gather_map(&map_r, p.rhs, (uint64_t)rows_r, (uint64_t)p.k) != VS_OK ||
+        make_gather_map(&map_l, p.lhs, (uint64_t)rows_l, (uint64_t)p.k) != VS_OK)
+        return launch_sddmm_tc_cpasync<TOut, V>(p, s, d);
+    auto kernel = tmasddmm::sddmm_tma_kernel<TOut, V>;
+    rc = set_smem(kernel, tmasddmm::kSmemBytes);
+    if (rc != VS_OK) return rc;
+    const int64_t items = (int64_t)p.batch * p.m_vec;
+    const int64_t cap = (int64_t)tmasddmm::kCtasPerSm * d->sm_count;
+    const unsigned grid = (unsigned)(items < cap ? items : cap);
+    kernel<<<grid, tmasddmm::kThreads, tmasddmm::kSmemBytes, s>>>(p, map_r, map_l, (int)rpb_r, (int)rows_r, (int)rpb_l,
+                                                                  (int)rows_l, d->status);
     return (int)cudaGetLastError();
 }
 
