@@ -175,3 +175,28 @@ def test_attention_small(path):
         want = oracle.attention(a.m_vec, V, d, d, a.row_offsets, a.col_indices, q[h].astype(np.float32),
                                 k[h].astype(np.float32), v[h].astype(np.float32), 0.125)
         assert_close(out[h].float().cpu().numpy(), want, f"attention head {h}")
+
+
+def test_software_gather_kernel_for_strides_tma_cannot_address():
+    """Batch strides that are not multiples of k fall back to the cp.async tensor-core SDDMM."""
+    V, k, batch = 8, 64, 2
+    a = problem(cvse.GEN_BETA, 17, 40, 200, V, 0.5)
+    lhs = cvse.fill_random((batch, a.m, k), np.float16, cvse.DIST_NORMAL, 1, 0.25)
+    rhs = cvse.fill_random((batch, a.n, k), np.float16, cvse.DIST_NORMAL, 2, 0.25)
+    pad = 8
+    fl = torch.zeros((batch, a.m * k + pad), dtype=torch.float16, device=DEV)
+    fr = torch.zeros((batch, a.n * k + pad), dtype=torch.float16, device=DEV)
+    fl[:, :a.m * k] = dev(lhs).reshape(batch, -1)
+    fr[:, :a.n * k] = dev(rhs).reshape(batch, -1)
+    ri, ro, ci = structure(a)
+    nnz = a.nnz_vec * V
+    out = torch.empty((batch, nnz), dtype=torch.float32, device=DEV)
+    from vectorsparse_b200 import _lib
+    rc = _lib.lib().vs_sddmm_batched(VS_PATH_TENSOR, 0, 1, a.m_vec, k, a.n, a.nnz_vec, ri.data_ptr(), ro.data_ptr(),
+                                     ci.data_ptr(), fl.data_ptr(), fr.data_ptr(), out.data_ptr(), V, batch,
+                                     a.m * k + pad, a.n * k + pad, nnz, torch.cuda.current_stream().cuda_stream, 1)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    for b in range(batch):
+        assert_close(out[b].cpu().numpy(), sddmm_oracle(a, k, lhs[b], rhs[b]), f"software gather, entry {b}")

@@ -179,3 +179,27 @@ def test_rejected_arguments_raise():
     with pytest.raises(VsError) as e:
         ops.spmm.wmmaSpmm(2, 8, 64, 16, ri, ro, ci, v.float(), B.float(), out.float())  # float tensor path
     assert e.value.code == -2
+
+
+@pytest.mark.parametrize("V", [2, 8])
+def test_software_gather_kernel_for_strides_tma_cannot_address(V):
+    """A batch stride of B that is not a multiple of the dense width cannot be described by one tensor map: the
+    cp.async tensor-core kernel takes over.  Same tolerance; the padding between entries must stay untouched."""
+    N, K, batch = 128, 160, 3
+    a = problem(cvse.GEN_BETA, 91 + V, 48, K, V, 0.6)
+    vals = cvse.fill_random((a.nnz_vec * V,), np.float16, cvse.DIST_NORMAL, 1, 0.5)
+    B = cvse.fill_random((batch, K, N), np.float16, cvse.DIST_NORMAL, 2, 1.0)
+    pad = 8   # 16 bytes: keeps alignment, breaks divisibility by N
+    flat = torch.zeros((batch, K * N + pad), dtype=torch.float16, device=DEV)
+    flat[:, :K * N] = dev(B).reshape(batch, K * N)
+    ri, ro, ci = structure(a)
+    out = torch.empty((batch, a.m, N), dtype=torch.float32, device=DEV)
+    from vectorsparse_b200 import _lib
+    rc = _lib.lib().vs_spmm_batched(VS_PATH_TENSOR, 0, 1, a.m_vec, V, N, K, ri.data_ptr(), ro.data_ptr(), ci.data_ptr(),
+                                    dev(vals).data_ptr(), flat.data_ptr(), out.data_ptr(), batch, 0, K * N + pad,
+                                    a.m * N, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    for b in range(batch):
+        assert_close(out[b].cpu().numpy(), spmm_oracle(a, N, vals, B[b]), f"software gather, entry {b}")
