@@ -45,7 +45,10 @@ WORKLOADS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from an ncu capture of this
 # command (profiles/ holds the summary it comes from); None until one has been taken for the workload.
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    "spmm_v8_s90": 339.8e6,    # profiles/spmm_tma_kernel__spmm_v8_s90.md
+    "sddmm_v8_s90": 380.2e6,   # profiles/sddmm_tma_kernel__sddmm_v8_s90.md
+}
 
 
 def measured_peaks():
@@ -174,19 +177,20 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     # ---- device-resident leg: `value` and the roofline ------------------------------------------------------
-    for _ in range(max(args.warmup, 3)):
-        launch(d_a, d_b, d_out)
-    barrier()
+    # clocks are sampled from here to the end of the end-to-end leg: the timed region alone (a few ms) is shorter
+    # than nvidia-smi's sampling period
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        launch(d_a, d_b, d_out)
+    barrier()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     ev[0].record()
     for s in range(args.steps):
         launch(d_a, d_b, d_out)
         ev[s + 1].record()
     barrier()
-    clocks = sampler.stop() if rank == 0 else None
     per_launch_ms = [ev[s].elapsed_time(ev[s + 1]) for s in range(args.steps)]
     total_ms = ev[0].elapsed_time(ev[args.steps])
     assert ops.device_status() == 0, "a kernel gave up on a bounded wait"
@@ -209,6 +213,12 @@ def run_ours(args):
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1) if e2e_steps else float("nan")
+    if rank == 0 and args.steps * 0.3 < 500:   # keep the GPU under the same load until ~0.5 s of samples exist
+        t_end = time.time() + 0.5
+        while time.time() < t_end:
+            launch(d_a, d_b, d_out)
+            torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
 
     # ---- single-launch latency of ONE instance (the reference API's granularity), L2-hot ----------------------
     lat_us = None
@@ -306,14 +316,14 @@ def cpu_leg(w, a, budget_s, threads=None):
     t0 = time.perf_counter()
     one(0)
     t_one = time.perf_counter() - t0
-    count = int(max(cores, min(w["inst"], cores * max(1, int(budget_s / max(t_one, 1e-4))))))
+    count = int(cores * max(1, int(budget_s / max(t_one, 1e-4))))   # ~budget_s of wall time on every core
     t0 = time.perf_counter()
     with cf.ThreadPoolExecutor(cores) as ex:
         list(ex.map(one, range(count)))
     dt = time.perf_counter() - t0
     return {"value": flops * count / dt / 1e12, "unit": "TFLOP/s", "cores": cores,
             "kind": "reference" if use_ref else "port",
-            "sample": f"{count} of {w['inst']} instances of the step, one instance per host thread, "
+            "sample": f"{count} instances of the step's problem (the step has {w['inst']}), one instance per host thread, "
                       f"{dt:.1f} s; single instance on one core {t_one * 1e3:.1f} ms"}
 
 
