@@ -41,6 +41,10 @@ WORKLOADS = {
     "spmm_v2_s90": dict(op="spmm", M=2048, K=512, V=2, s=0.9, N=256, inst=256, kind="beta"),
     "sddmm_v8_s90": dict(op="sddmm", M=2048, K=512, V=8, s=0.9, N=256, inst=256, kind="beta"),
     "spmm_cc_v8_s90": dict(op="spmm", M=2048, K=512, V=8, s=0.9, N=256, inst=256, kind="beta", path=1),
+    # fp32 CUDA-core SpMM (the cudaSpmm entry point), M = K = 4096, uniform random positions, values and B U(-1,1)
+    "spmm_f32_v4_s90_n1024": dict(op="spmm", M=4096, K=4096, V=4, s=0.9, N=1024, inst=8, kind="uniform", path=1, dtype="f32"),
+    "spmm_f32_v1_s90_n1024": dict(op="spmm", M=4096, K=4096, V=1, s=0.9, N=1024, inst=8, kind="uniform", path=1, dtype="f32"),
+    "spmm_f32_v4_s80_n8192": dict(op="spmm", M=4096, K=4096, V=4, s=0.8, N=8192, inst=2, kind="uniform", path=1, dtype="f32"),
 }
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from an ncu capture of this
@@ -115,9 +119,10 @@ def algorithmic(w, a):
     """(flops, HBM bytes) of ONE launch = `inst` instances sharing the structure arrays."""
     nnz_vec, V, inst = a.nnz_vec, w["V"], w["inst"]
     structure = nnz_vec * 4 + (2 * a.m_vec + 1) * 4
+    es = 4 if w.get("dtype") == "f32" else 2
     if w["op"] == "spmm":
         k_touched = int(np.unique(a.col_indices).size)
-        per = nnz_vec * V * 2 + k_touched * w["N"] * 2 + w["M"] * w["N"] * 2
+        per = nnz_vec * V * es + k_touched * w["N"] * es + w["M"] * w["N"] * es
         flops = 2.0 * nnz_vec * V * w["N"]
     else:  # sddmm: lhs M x k, rhs K x k, out nnz
         k = w["N"]
@@ -149,12 +154,15 @@ def run_ours(args):
 
     # operands of this rank's stream, in pinned host memory (for the end-to-end leg) and on the device
     seed = 100 + rank
+    f32 = w.get("dtype") == "f32"
     if w["op"] == "spmm":
         row = (a.nnz_vec * V + 7) // 8 * 8  # per-instance stride kept 16-byte aligned for every V
-        h_a = torch.from_numpy(cvse.fill_random((inst, row), np.float16, cvse.DIST_NORMAL, seed, 0.02)).pin_memory()
-        h_b = torch.from_numpy(cvse.fill_random((inst, K, N), np.float16, cvse.DIST_NORMAL, seed + 1, 1.0)).pin_memory()
-        h_out = torch.empty((inst, M, N), dtype=torch.float16).pin_memory()
-        d_out = torch.empty((inst, M, N), dtype=torch.float16, device=dev)
+        npdt, tdt = (np.float32, torch.float32) if f32 else (np.float16, torch.float16)
+        dist_a, dist_b, sig = (cvse.DIST_UNIFORM, cvse.DIST_UNIFORM, 1.0) if f32 else (cvse.DIST_NORMAL, cvse.DIST_NORMAL, 0.02)
+        h_a = torch.from_numpy(cvse.fill_random((inst, row), npdt, dist_a, seed, sig)).pin_memory()
+        h_b = torch.from_numpy(cvse.fill_random((inst, K, N), npdt, dist_b, seed + 1, 1.0)).pin_memory()
+        h_out = torch.empty((inst, M, N), dtype=tdt).pin_memory()
+        d_out = torch.empty((inst, M, N), dtype=tdt, device=dev)
 
         def launch(d_a, d_b, out):
             ops.spmm_batched(path, a.m_vec, V, N, K, ri, ro, ci, d_a, d_b, out)
@@ -246,8 +254,8 @@ def run_ours(args):
         peak, peak_kind = measured_peaks()
         avg_launch_s = float(np.mean(per_launch_ms)) * 1e-3
         achieved = alg_bytes / avg_launch_s / 1e9
-        h2d = h_a.numel() * 2 + h_b.numel() * 2
-        d2h = h_out.numel() * 2
+        h2d = h_a.numel() * h_a.element_size() + h_b.numel() * h_b.element_size()
+        d2h = h_out.numel() * h_out.element_size()
         line = {
             "metric": "SpMM effective TFLOP/s (2*nnz*N)" if w["op"] == "spmm" else "SDDMM effective TFLOP/s (2*nnz*k)",
             "value": flops * args.steps * world / (total_ms * 1e-3) / 1e12,
@@ -259,7 +267,7 @@ def run_ours(args):
             "higher_is_better": True,
             "scaling": "weak",
             "vs_baseline": None,
-            "dtype": "f16 (fp32 accumulate)",
+            "dtype": "f32" if f32 else "f16 (fp32 accumulate)",
             "data": "synthetic",
             "config": {"workload": args.workload, "op": w["op"], "M": M, "K": K, "V": V, "sparsity": w["s"],
                        "dense_width_or_k": N, "nnz_vec": a.nnz_vec, "instances_per_step": inst,
@@ -295,8 +303,12 @@ def cpu_leg(w, a, budget_s, threads=None):
     use_ref = oracle.ref() is not None
     V, M, K, N = w["V"], w["M"], w["K"], w["N"]
     if w["op"] == "spmm":
-        x = cvse.fill_random((a.nnz_vec * V,), np.float16, cvse.DIST_NORMAL, 1, 0.02)
-        y = cvse.fill_random((K, N), np.float16, cvse.DIST_NORMAL, 2, 1.0)
+        if w.get("dtype") == "f32":
+            x = cvse.fill_random((a.nnz_vec * V,), np.float32, cvse.DIST_UNIFORM, 1)
+            y = cvse.fill_random((K, N), np.float32, cvse.DIST_UNIFORM, 2)
+        else:
+            x = cvse.fill_random((a.nnz_vec * V,), np.float16, cvse.DIST_NORMAL, 1, 0.02)
+            y = cvse.fill_random((K, N), np.float16, cvse.DIST_NORMAL, 2, 1.0)
         flops = 2.0 * a.nnz_vec * V * N
 
         def one(_):
