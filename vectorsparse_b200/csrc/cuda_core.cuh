@@ -134,10 +134,71 @@ __global__ void __launch_bounds__(kCcThreads) sddmm_cc_kernel(const SddmmParams 
 
 // ---- masked row softmax -----------------------------------------------------------------------------------
 // One warp per vector-row: lanes stride over the row's entries, each entry carrying the V real rows, so the V
-// softmaxes of a vector-row run side by side on contiguous loads.  fp32 arithmetic, three passes over a row
-// that stays in L1/L2.  probs may alias scores.
+// softmaxes of a vector-row run side by side on contiguous vector loads.  fp32 arithmetic.  Rows of up to
+// 32 * kCache entries are read from memory ONCE: each lane keeps its entries' raw words in registers across the
+// max, sum and normalise steps (2 passes over HBM instead of 4).  Longer rows take three passes over a row that
+// stays in L1/L2.  probs may alias scores.
+template <typename T, int V> struct EntryWords {  // one entry = V values of T = kWords 32-bit words
+    static constexpr int kBytes = V * (int)sizeof(T);
+    static constexpr int kWords = kBytes >= 4 ? kBytes / 4 : 1;
+    static constexpr bool kVector = kBytes >= 4;
+    __device__ __forceinline__ static void load(const T *p, uint32_t (&w)[kWords]) {
+        if constexpr (kBytes == 4) {
+            w[0] = __ldg(reinterpret_cast<const uint32_t *>(p));
+        } else if constexpr (kBytes == 8) {
+            const uint2 v = __ldg(reinterpret_cast<const uint2 *>(p));
+            w[0] = v.x; w[1] = v.y;
+        } else {
+#pragma unroll
+            for (int q = 0; q < kBytes / 16; ++q) {
+                const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p) + q);
+                w[4 * q] = v.x; w[4 * q + 1] = v.y; w[4 * q + 2] = v.z; w[4 * q + 3] = v.w;
+            }
+        }
+    }
+    __device__ __forceinline__ static void unpack(const uint32_t (&w)[kWords], float (&f)[V]) {
+        if constexpr (sizeof(T) == 4) {
+#pragma unroll
+            for (int v = 0; v < V; ++v) f[v] = __uint_as_float(w[v]);
+        } else {
+#pragma unroll
+            for (int q = 0; q < V / 2; ++q) {
+                const float2 t = __half22float2(*reinterpret_cast<const __half2 *>(&w[q]));
+                f[2 * q] = t.x; f[2 * q + 1] = t.y;
+            }
+        }
+    }
+    __device__ __forceinline__ static void pack(const float (&f)[V], uint32_t (&w)[kWords]) {
+        if constexpr (sizeof(T) == 4) {
+#pragma unroll
+            for (int v = 0; v < V; ++v) w[v] = __float_as_uint(f[v]);
+        } else {
+#pragma unroll
+            for (int q = 0; q < V / 2; ++q) {
+                const __half2 h = __floats2half2_rn(f[2 * q], f[2 * q + 1]);
+                w[q] = *reinterpret_cast<const uint32_t *>(&h);
+            }
+        }
+    }
+    __device__ __forceinline__ static void store(T *p, const float (&f)[V]) {
+        uint32_t w[kWords];
+        pack(f, w);
+        if constexpr (kBytes == 4) {
+            *reinterpret_cast<uint32_t *>(p) = w[0];
+        } else if constexpr (kBytes == 8) {
+            *reinterpret_cast<uint2 *>(p) = make_uint2(w[0], w[1]);
+        } else {
+#pragma unroll
+            for (int q = 0; q < kBytes / 16; ++q)
+                reinterpret_cast<uint4 *>(p)[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+        }
+    }
+};
+
 template <typename T, int V>
 __global__ void __launch_bounds__(kCcThreads) softmax_cvse_kernel(const SoftmaxParams p) {
+    using EW = EntryWords<T, V>;
+    constexpr int kCache = EW::kVector ? (64 / EW::kWords > 16 ? 16 : 64 / EW::kWords) : 0;   // entries per lane
     const int warp = (blockIdx.x * kCcThreads + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (warp >= p.m_vec) return;
@@ -150,6 +211,66 @@ __global__ void __launch_bounds__(kCcThreads) softmax_cvse_kernel(const SoftmaxP
     float mx[V], sum[V];
 #pragma unroll
     for (int v = 0; v < V; ++v) { mx[v] = -INFINITY; sum[v] = 0.f; }
+
+    if constexpr (kCache > 0) {
+        if (end - beg <= 32 * kCache) {
+            uint32_t cache[kCache][EW::kWords];
+#pragma unroll
+            for (int c = 0; c < kCache; ++c) {
+                const int j = beg + lane + 32 * c;
+                if (j < end) {
+                    EW::load(s + (int64_t)j * V, cache[c]);
+                    float f[V];
+                    EW::unpack(cache[c], f);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) mx[v] = fmaxf(mx[v], p.scale * f[v]);
+                }
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+                for (int v = 0; v < V; ++v) mx[v] = fmaxf(mx[v], __shfl_xor_sync(0xffffffffu, mx[v], off));
+            // exponentials are computed once (exp2 of a pre-scaled argument), kept in the cache in the element
+            // type, and scaled by 1 / sum on the way out
+            const float sl2 = p.scale * 1.4426950408889634f;
+            float ml2[V];
+#pragma unroll
+            for (int v = 0; v < V; ++v) ml2[v] = mx[v] * 1.4426950408889634f;
+#pragma unroll
+            for (int c = 0; c < kCache; ++c) {
+                if (beg + lane + 32 * c < end) {
+                    float f[V];
+                    EW::unpack(cache[c], f);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) {
+                        f[v] = exp2f(fmaf(f[v], sl2, -ml2[v]));
+                        sum[v] += f[v];
+                    }
+                    EW::pack(f, cache[c]);
+                }
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+                for (int v = 0; v < V; ++v) sum[v] += __shfl_xor_sync(0xffffffffu, sum[v], off);
+            float inv[V];
+#pragma unroll
+            for (int v = 0; v < V; ++v) inv[v] = 1.0f / sum[v];
+#pragma unroll
+            for (int c = 0; c < kCache; ++c) {
+                const int j = beg + lane + 32 * c;
+                if (j < end) {
+                    float f[V];
+                    EW::unpack(cache[c], f);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) f[v] *= inv[v];
+                    EW::store(o + (int64_t)j * V, f);
+                }
+            }
+            return;
+        }
+    }
+
     for (int j = beg + lane; j < end; j += 32) {
 #pragma unroll
         for (int v = 0; v < V; ++v) mx[v] = fmaxf(mx[v], p.scale * load_scalar(s + (int64_t)j * V + v));

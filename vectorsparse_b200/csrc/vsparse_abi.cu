@@ -367,6 +367,12 @@ VS_EXPORT int vs_softmax_cvse(int dtype, int m_vec, int vec_length, const int32_
     if (m_vec == 0) return VS_OK;
     if (!row_offsets || !scores || !probs) return VS_ERR_NULL;
     if (stride < 0 || (batch > 1 && stride == 0)) return VS_ERR_ARG;
+    {   // one entry (V values) is read and written as one vector of up to 16 bytes
+        const size_t entry = (size_t)vec_length * elem_size(dtype), al = entry < 16 ? entry : 16;
+        if (reinterpret_cast<uintptr_t>(scores) % al || reinterpret_cast<uintptr_t>(probs) % al ||
+            ((size_t)stride * elem_size(dtype)) % al)
+            return VS_ERR_ALIGN;
+    }
     SoftmaxParams p;
     p.m_vec = m_vec; p.batch = batch; p.row_offsets = row_offsets; p.scores = scores; p.probs = probs;
     p.stride = stride; p.scale = scale;
