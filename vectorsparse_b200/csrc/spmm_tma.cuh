@@ -15,15 +15,15 @@
 // ONE warp instruction: lane l issues the gather of rows 4*(l/2).. of column half l%2.  That replaces 32
 // cp.async instructions per lane of a software gather and their address arithmetic.
 //
-// Organisation.  Two persistent CTAs per SM (two MMA-issuing threads per SM), warp-specialised, no CTA-wide
+// Organisation.  Two persistent CTAs per SM (four MMA-issuing threads per SM), warp-specialised, no CTA-wide
 // barrier inside a phase:
 //   * warps 0-3, epilogue: wait for `acc_full`, tcgen05.ld their 32 TMEM lanes, release the accumulator
 //     (`acc_empty`), transpose through a warp-private staging tile and write C with 16-byte stores.
 //   * warps 4-8, producers: warp w takes every 5th stage.  It waits for the stage's ring slot (`empty`), arms
 //     the slot's `full` mbarrier with the byte count, issues the gathers, copies the value vectors with
 //     cp.async (arriving on `full` when they land), and prefetches the column indices of its stage n+2.
-//   * warp 9, one thread: waits for `full` in ring order, issues the MMAs of the stage and commits them to the
-//     slot's `empty` mbarrier and, at the end of a row, to `acc_full`.
+//   * warps 9-10, one thread each (even / odd work items): wait for `full`, issue the MMAs of the stage and
+//     commit them to the slot's `empty` mbarrier and, at the end of a row, to `acc_full`.
 // Work items are (batch, column tile, vector-row in row_indices order), dealt round-robin to the CTAs so that
 // the descending-length order the row swizzle produces becomes a longest-first schedule; each CTA decodes its
 // next 128 items in bulk ("phase") so that no role chases row_indices -> row_offsets per item.
@@ -42,7 +42,8 @@ constexpr int kEpiWarps = 4;                             // warps 0..3 (TMEM lan
 constexpr int kProducerWarp0 = 4;
 constexpr int kProducerWarps = 5;                        // warps 4..8: one per ring slot
 constexpr int kMmaWarp = kProducerWarp0 + kProducerWarps;  // warp 9
-constexpr int kThreads = (kMmaWarp + 1) * 32;            // 320
+constexpr int kMmaWarps = 2;                             // two issuing threads (even / odd work items)
+constexpr int kThreads = (kMmaWarp + kMmaWarps) * 32;    // 352
 constexpr int kCtasPerSm = 2;
 constexpr int kTileN = 128;                              // dense columns per work item (MMA M)
 constexpr int kStageNnz = 64;                            // nonzero vectors per stage (up to four K=16 MMAs)
@@ -53,7 +54,7 @@ constexpr int kVStageBytes = 2 * kStageNnz * 16;         // 2 KiB: 64 value slot
 constexpr int kAccCols = 16;                             // TMEM columns per accumulator
 constexpr int kTmemCols = 256;
 constexpr int kAccSlots = kTmemCols / kAccCols;          // 16
-constexpr int kIdxRing = 3;                              // per-warp ring of index blocks (kStageNnz ints each)
+constexpr int kIdxRing = 2;                              // per-warp index blocks (kStageNnz ints each), alternating
 constexpr int kItemsPerPhase = 128;
 constexpr int kStagingBytes = 8 * 32 * 4;                // per epilogue warp: 8 rows x 32 columns, fp32 worst case
 
@@ -76,7 +77,8 @@ struct Smem {  // offsets from the 1024-byte aligned base
     static constexpr int kTmemHolder = kBarAccEmpty + kAccSlots * 8;
     static constexpr int kAbort = kTmemHolder + 8;
     static constexpr int kPhaseStages = kAbort + 8;          // two counters, used by alternate phases
-    static constexpr int kTotal = kPhaseStages + 8;
+    static constexpr int kMmaDone = kPhaseStages + 8;        // per MMA issuer: stages below this index are waited on
+    static constexpr int kTotal = kMmaDone + 8;
 };
 constexpr int kSmemBytes = Smem::kTotal + 1024;  // + slack for the manual 1024-byte alignment
 static_assert(kCtasPerSm * (kSmemBytes + 1024) <= 227 * 1024, "shared memory budget");
@@ -177,6 +179,8 @@ spmm_tma_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map, int
         *abort_flag = 0;
         phase_stage_count[0] = 0;
         phase_stage_count[1] = 0;
+        reinterpret_cast<volatile uint32_t *>(sm + Smem::kMmaDone)[0] = 0;
+        reinterpret_cast<volatile uint32_t *>(sm + Smem::kMmaDone)[1] = 0;
         tc::fence_mbar_init();
     }
     if (warp == kMmaWarp) {
@@ -232,54 +236,62 @@ spmm_tma_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map, int
             // destination of this lane's four rows inside a stage: M-atom `half`, k-group grp/2, upper/lower 512 B
             const uint32_t a_off = (uint32_t)(half * (kAStageBytes / 2) + (grp >> 1) * 1024 + (grp & 1) * 512);
             int *ring = reinterpret_cast<int *>(sm + Smem::kIdx) + pw * kIdxRing * kStageNnz;
-            const uint32_t ring_u32 = base + Smem::kIdx + pw * kIdxRing * kStageNnz * 4;
 
-            // first stage of this phase that is this warp's: global stage index = pw (mod kProducerWarps)
+            // This warp's stages are kProducerWarps apart.  One iterator runs two of them ahead; the positions
+            // and column indices of the next two stages wait in registers (indices loaded with plain loads two
+            // stages early, so their latency is never seen), and are dropped into shared memory when their stage
+            // comes up so that the gathering lanes can read four of them at once.
             const int s0 = (int)(((uint32_t)pw + kProducerWarps - (g_stage % kProducerWarps)) % kProducerWarps);
-            OwnIter cur, fetch;
-            cur.init(l_j0, l_end, cnt);
-            cur.advance(s0);
-            fetch = cur;
-            // indices of this warp's first two stages: plain loads, once per phase
-            for (int n = 0; n < 2; ++n) {
-                if (fetch.valid()) {
+            OwnIter it;
+            it.init(l_j0, l_end, cnt);
+            it.advance(s0);
+            int pq[2], pj[2], pe[2], pidx[2][kStageNnz / 32];   // [0] = the stage being gathered, [1] = the next one
 #pragma unroll
-                    for (int u = 0; u < kStageNnz / 32; ++u) {
-                        const int jj = fetch.j() + lane + 32 * u;
-                        ring[n * kStageNnz + lane + 32 * u] = (jj < fetch.je) ? __ldg(p.col_indices + jj) : 0;
-                    }
-                    fetch.advance(kProducerWarps);
+            for (int z = 0; z < 2; ++z) {
+                pq[z] = it.valid() ? it.q : cnt;
+                pj[z] = it.j();
+                pe[z] = it.je;
+#pragma unroll
+                for (int u = 0; u < kStageNnz / 32; ++u) {
+                    const int jj = pj[z] + lane + 32 * u;
+                    pidx[z][u] = (pq[z] < cnt && jj < pe[z]) ? __ldg(p.col_indices + jj) : 0;
                 }
+                it.advance(kProducerWarps);
             }
-            __syncwarp();
 
             uint32_t g = g_stage + (uint32_t)s0;
             int n = 0;
             bool ok_run = true;
             VS_PROF_T0();
-            while (cur.valid() && ok_run) {
+            while (pq[0] < cnt && ok_run) {
                 const uint32_t slot = g % kStages;
                 if (g >= (uint32_t)kStages)
                     ok_run = wait_or_abort<kSleepProducer>(bar_empty + 8 * slot, ((g / kStages) - 1u) & 1u, abort_flag);
                 if (!ok_run) break;
-                VS_PROF_ADD(0);   // producer: wait for the slot
-                // this stage's indices were fetched two of this warp's stages ago: at most the newest cp.async
-                // group may still be pending; the warp barrier publishes the landed indices to all lanes
-                tc::cp_async_wait<1>();
-                __syncwarp();
-                VS_PROF_ADD(1);   // producer: wait for indices
-                const int q = cur.q;
+                int *my_ring = ring + (n & 1) * kStageNnz;
+#pragma unroll
+                for (int u = 0; u < kStageNnz / 32; ++u) my_ring[lane + 32 * u] = pidx[0][u];
+                const int q = pq[0];
                 const int b = l_b[q];
                 const int n0 = l_n0[q];
-                const int j = cur.j();
-                const int nnz = cur.nnz();
+                const int j = pj[0];
+                const int nnz = min(kStageNnz, max(0, pe[0] - j));
                 const int n_mma = max(1, (nnz + 15) >> 4);
                 const bool two_halves = (n0 + 64) < p.N;       // N % 128 == 64: the last tile has one half
                 const uint32_t bar = bar_full + 8 * slot;
-                if (lane == 0) mbar_expect_tx_only(bar, (uint32_t)(4 * n_mma * (two_halves ? 2 : 1)) * 512u);
-                __syncwarp();
+                const uint32_t v_base = base + Smem::kV + slot * kVStageBytes;
+                const __half *vals = static_cast<const __half *>(p.values) + (int64_t)b * p.stride_values;
+                constexpr bool kBulkValues = (V == 8);   // a value vector is exactly one 16-byte operand row
+                if (lane == 0) {
+                    uint32_t bytes = (uint32_t)(4 * n_mma * (two_halves ? 2 : 1)) * 512u;
+                    if (kBulkValues) bytes += (uint32_t)nnz * 16u;
+                    mbar_expect_tx_only(bar, bytes);
+                    if (kBulkValues && nnz > 0) tc::bulk_copy_g2s(v_base, vals + (int64_t)j * V, (uint32_t)nnz * 16u, bar);
+                }
+                __syncwarp();                                  // indices in shared memory, byte count armed
+                VS_PROF_ADD(0);   // producer: waits + stage set-up
                 if (grp < 4 * n_mma && (half == 0 || two_halves)) {
-                    const int4 c = *reinterpret_cast<const int4 *>(ring + (n % kIdxRing) * kStageNnz + 4 * grp);
+                    const int4 c = *reinterpret_cast<const int4 *>(my_ring + 4 * grp);
                     const int row0 = b * rows_per_batch;
                     const int e = 4 * grp;
                     // rows past the end of the vector-row get an out-of-range coordinate: they arrive as zeros
@@ -287,70 +299,101 @@ spmm_tma_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map, int
                                     e + 0 < nnz ? row0 + c.x : total_rows, e + 1 < nnz ? row0 + c.y : total_rows,
                                     e + 2 < nnz ? row0 + c.z : total_rows, e + 3 < nnz ? row0 + c.w : total_rows);
                 }
-                const __half *vals = static_cast<const __half *>(p.values) + (int64_t)b * p.stride_values;
-                const uint32_t v_base = base + Smem::kV + slot * kVStageBytes;
-#pragma unroll
-                for (int u = 0; u < kStageNnz / 32; ++u) {
-                    const int e = lane + 32 * u;
-                    if (e < 16 * n_mma) {
-                        const bool ok = e < nnz;
-                        tc::cp_async_small<V * 2>(v_base + e * 16, ok ? vals + (int64_t)(j + e) * V : vals,
-                                                  ok ? (uint32_t)(V * 2) : 0u);
-                    }
-                }
-                // column indices of this warp's stage n + 2
-                if (fetch.valid()) {
+                VS_PROF_ADD(1);   // producer: gather issue
+                if constexpr (kBulkValues) {
+                    // value slots between the row's end and the end of the last MMA must read as zeros
 #pragma unroll
                     for (int u = 0; u < kStageNnz / 32; ++u) {
-                        const int jj = fetch.j() + lane + 32 * u;
-                        const bool ok = jj < fetch.je;
-                        tc::cp_async_small<4>(ring_u32 + (((n + 2) % kIdxRing) * kStageNnz + lane + 32 * u) * 4,
-                                              ok ? p.col_indices + jj : p.col_indices, ok ? 4u : 0u);
+                        const int e = lane + 32 * u;
+                        if (e >= nnz && e < 16 * n_mma) *reinterpret_cast<uint4 *>(sm + Smem::kV + slot * kVStageBytes + e * 16) = make_uint4(0, 0, 0, 0);
                     }
-                    fetch.advance(kProducerWarps);
+                    mbar_arrive(bar);
+                } else {
+#pragma unroll
+                    for (int u = 0; u < kStageNnz / 32; ++u) {
+                        const int e = lane + 32 * u;
+                        if (e < 16 * n_mma) {
+                            const bool ok = e < nnz;
+                            tc::cp_async_small<V * 2>(v_base + e * 16, ok ? vals + (int64_t)(j + e) * V : vals,
+                                                      ok ? (uint32_t)(V * 2) : 0u);
+                        }
+                    }
+                    cp_async_arrive_noinc(bar);
                 }
-                cp_async_arrive_noinc(bar);
-                tc::cp_async_commit();
-                cur.advance(kProducerWarps);
+                // rotate the look-ahead: the next stage moves up, the one after it is located and its indices loaded
+                pq[0] = pq[1]; pj[0] = pj[1]; pe[0] = pe[1];
+                pq[1] = it.valid() ? it.q : cnt;
+                pj[1] = it.j();
+                pe[1] = it.je;
+#pragma unroll
+                for (int u = 0; u < kStageNnz / 32; ++u) {
+                    pidx[0][u] = pidx[1][u];
+                    const int jj = pj[1] + lane + 32 * u;
+                    pidx[1][u] = (pq[1] < cnt && jj < pe[1]) ? __ldg(p.col_indices + jj) : 0;
+                }
+                it.advance(kProducerWarps);
                 g += kProducerWarps;
                 ++n;
-                VS_PROF_ADD(2);   // producer: issue
+                VS_PROF_ADD(2);   // producer: values, look-ahead
             }
             tc::cp_async_wait<0>();
             VS_PROF_FLUSH(0);
-        } else if (warp == kMmaWarp) {
-            // =========================== MMA issuer ========================================================
-            // One issuing thread for all stages, in ring order: an mbarrier parity wait is only safe for a
-            // consumer that has itself seen the slot's previous use complete.
+        } else if (warp >= kMmaWarp) {
+            // =========================== MMA issuers =======================================================
+            // Two issuing threads share the work by item parity (a tcgen05.mma costs its issuing thread ~64
+            // cycles and a commit ~59, more than the tensor pipe needs for these small MMAs).  Both walk the
+            // whole stage sequence.  An mbarrier parity wait is only meaningful for a consumer that knows the
+            // slot's previous use has completed, so before waiting on stage g a thread makes sure the OTHER
+            // thread has passed every stage of its own up to g - kStages (`mma_done`, a monotone counter).
             if (lane == 0) {
+                const uint32_t mine = (uint32_t)(warp - kMmaWarp);
+                volatile uint32_t *mma_done = reinterpret_cast<volatile uint32_t *>(sm + Smem::kMmaDone);
                 constexpr uint32_t kIdesc = tc::make_idesc_f16(kTileN, 16, 1, 1);
                 const uint32_t a_lo0 = tc::smem_desc_lo(base + Smem::kA, kAStageBytes / 2);
                 const uint32_t a_hi = tc::smem_desc_hi(1024, (uint32_t)tc::kSwizzle128B);
                 const uint32_t b_lo0 = tc::smem_desc_lo(base + Smem::kV, 128);
                 const uint32_t b_hi = tc::smem_desc_hi(kVStageBytes / 2, (uint32_t)tc::kSwizzleNone);
-                // ring / accumulator positions are carried incrementally: this thread's instruction stream is the
-                // serial part of the pipeline, so every division or dependent shared-memory load counts
+                uint32_t g = g_stage;
                 uint32_t slot = g_stage % kStages, full_parity = (g_stage / kStages) & 1u;
                 uint32_t acc = g_item % kAccSlots, acc_parity = ((g_item / kAccSlots) & 1u) ^ 1u;   // parity of the PREVIOUS use
                 bool acc_wait = g_item >= (uint32_t)kAccSlots;
-                uint32_t a_lo = a_lo0 + slot * (kAStageBytes >> 4), b_lo = b_lo0 + slot * (kVStageBytes >> 4);
+                uint32_t item_parity = g_item & 1u;
                 bool ok_run = true;
                 int len = l_end[0] - l_j0[0];
                 VS_PROF_T0();
-                for (int q = 0; q < cnt && ok_run; ++q) {
+                for (int q = 0; q < cnt && ok_run; ++q, item_parity ^= 1u) {
                     int rem = len;
                     if (q + 1 < cnt) len = l_end[q + 1] - l_j0[q + 1];   // next item's length: off the critical path
+                    if (item_parity != mine) {   // the other issuer's item: step over its stages and accumulator
+                        const uint32_t nst = (uint32_t)stages_of(rem);
+                        g += nst;
+                        const uint32_t tmp = slot + nst;
+                        full_parity ^= (tmp / kStages) & 1u;
+                        slot = tmp % kStages;
+                        if (++acc == (uint32_t)kAccSlots) { acc = 0; acc_parity ^= 1u; acc_wait = true; }
+                        mma_done[mine] = g;   // every stage of mine below g has been waited on (the skipped ones are not mine)
+                        continue;
+                    }
                     if (acc_wait) ok_run = wait_or_abort<kSleepMma>(bar_acc_empty + 8 * acc, acc_parity, abort_flag);
                     const uint32_t d = tmem_base + acc * kAccCols;
                     uint32_t accumulate = 0;
                     VS_PROF_ADD(3);   // mma: wait for a free accumulator (+ item bookkeeping)
                     do {
+                        if (ok_run && g >= (uint32_t)kStages) {   // bounded wait for the other issuer (see above)
+                            const uint32_t need = g - kStages;
+                            uint32_t polls = 0;
+                            while ((int32_t)(mma_done[mine ^ 1u] - need) <= 0) {
+                                if (++polls > (1u << 24) || *abort_flag) { *abort_flag = 1; ok_run = false; break; }
+                            }
+                        }
                         if (ok_run) ok_run = wait_or_abort<kSleepMma>(bar_full + 8 * slot, full_parity, abort_flag);
                         if (!ok_run) break;
+                        mma_done[mine] = g + 1;
                         VS_PROF_ADD(4);   // mma: wait for a full stage
                         tc::fence_proxy_async();   // the value vectors were written by cp.async (generic proxy)
                         tc::tc_fence_after_sync();
                         const int n_mma = rem >= kStageNnz ? kMmaPerStage : max(1, (rem + 15) >> 4);
+                        const uint32_t a_lo = a_lo0 + slot * (kAStageBytes >> 4), b_lo = b_lo0 + slot * (kVStageBytes >> 4);
                         tc::mma_f16_ss(d, tc::desc64(a_lo, a_hi), tc::desc64(b_lo, b_hi), kIdesc, accumulate);
                         if (n_mma > 1) tc::mma_f16_ss(d, tc::desc64(a_lo + 128, a_hi), tc::desc64(b_lo + 16, b_hi), kIdesc, 1u);
                         if (kMmaPerStage > 2 && n_mma > 2) tc::mma_f16_ss(d, tc::desc64(a_lo + 256, a_hi), tc::desc64(b_lo + 32, b_hi), kIdesc, 1u);
@@ -358,20 +401,17 @@ spmm_tma_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map, int
                         tc::mma_commit(bar_empty + 8 * slot);
                         accumulate = 1;
                         rem -= kStageNnz;
-                        if (++slot == (uint32_t)kStages) {
-                            slot = 0; full_parity ^= 1u;
-                            a_lo = a_lo0; b_lo = b_lo0;
-                        } else {
-                            a_lo += kAStageBytes >> 4; b_lo += kVStageBytes >> 4;
-                        }
+                        ++g;
+                        if (++slot == (uint32_t)kStages) { slot = 0; full_parity ^= 1u; }
                         VS_PROF_ADD(5);   // mma: issue
                     } while (rem > 0);
                     if (ok_run) tc::mma_commit(bar_acc_full + 8 * acc);
                     if (++acc == (uint32_t)kAccSlots) { acc = 0; acc_parity ^= 1u; acc_wait = true; }
                 }
+                mma_done[mine] = g_stage + stages_here;   // nothing of this phase is left for this thread to wait on
                 VS_PROF_FLUSH(3);
             }
-        } else {
+        } else if (warp < kEpiWarps) {
             // =========================== epilogue ==========================================================
             const int quarter = warp;                     // warps 0..3: TMEM lanes 32*warp .. +31
             uint8_t *stg = sm + Smem::kStaging + warp * kStagingBytes;

@@ -102,6 +102,13 @@ __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// Contiguous global -> shared copy by the bulk-copy engine: both addresses 16-byte aligned, `bytes` a multiple
+// of 16; completes `bytes` on `bar`.
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar)
+                 : "memory");
+}
 // Gathers four rows (r0..r3) of a 2-D row-major tensor, `box` columns wide starting at column x, into four
 // consecutive rows of shared memory at `dst`; the tensor map carries the box width (x 1 row), element type and
 // swizzle mode.  Rows outside the tensor arrive as zeros.  x * element size must be a multiple of 16 bytes.
