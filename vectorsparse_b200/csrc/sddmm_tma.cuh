@@ -66,6 +66,8 @@ struct Smem {
     static constexpr int kTotal = kPhaseStages + 8;
 };
 constexpr int kSmemBytes = Smem::kTotal + 1024;
+// a ring slot must always be refilled by the same warp (see the SpMM kernel)
+static_assert(kStages % kProducerWarps == 0, "each ring slot needs a fixed owner warp");
 static_assert(kCtasPerSm * (kSmemBytes + 1024) <= 227 * 1024, "shared memory budget");
 
 // Stage s of an item: tile s / nkb, k-block s % nkb.  Rows without entries have no stages.

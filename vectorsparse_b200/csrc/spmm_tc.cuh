@@ -74,6 +74,7 @@ struct Smem {  // offsets from the 1024-byte aligned base
 };
 constexpr int kSmemBytes = Smem::kTotal + 1024;  // + slack for the manual 1024-byte alignment
 static_assert(kCtasPerSm * (kSmemBytes + 1024) <= 227 * 1024, "shared memory budget");
+static_assert(kStages == kProducerWarps, "each ring slot is owned by one producer warp");
 
 __device__ __forceinline__ int stages_of(int len) { return max(1, (len + kStageNnz - 1) / kStageNnz); }
 

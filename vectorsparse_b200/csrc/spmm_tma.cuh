@@ -81,6 +81,10 @@ struct Smem {  // offsets from the 1024-byte aligned base
     static constexpr int kTotal = kMmaDone + 8;
 };
 constexpr int kSmemBytes = Smem::kTotal + 1024;  // + slack for the manual 1024-byte alignment
+// A ring slot must always be refilled by the same warp: a producer's parity wait on `empty` is only meaningful
+// if that producer has itself seen the slot's previous release (two warps sharing a slot could run a full ring
+// apart, pass the wait spuriously and arrive twice in one phase, which traps).
+static_assert(kStages % kProducerWarps == 0, "each ring slot needs a fixed owner warp");
 static_assert(kCtasPerSm * (kSmemBytes + 1024) <= 227 * 1024, "shared memory budget");
 
 __device__ __forceinline__ int stages_of(int len) { return max(1, (len + kStageNnz - 1) / kStageNnz); }
