@@ -174,7 +174,7 @@ int vs_device_status(int clear, uint32_t *status);
  * caller-built shared-memory image (device pointer) to the start of a 1024-byte aligned buffer, issues n_mma
  * tcgen05.mma kind::f16 instructions with the given 64-bit (A, B) descriptor pairs — their start-address field
  * relative to the image — accumulating into one tile, and copies the accumulator, pre-filled with `fill`, to
- * out[lane * ncols + col] (128 lanes, ncols a multiple of 8, at most 64).  Lets the host confirm an operand
+ * out[lane * ncols + col] (128 lanes, ncols a multiple of 8, at most 128).  Lets the host confirm an operand
  * layout convention against a plain matrix product before trusting a kernel built on it.
  * ---------------------------------------------------------------------------------------------------- */
 int vs_selftest_mma(const void *image, int image_bytes, const uint64_t *descs, int n_mma, uint32_t idesc,

@@ -16,7 +16,11 @@ __device__ unsigned long long g_prof[16];
 #define VS_PROF_T0() long long prof_t0 = clock64(); long long prof_acc[3] = {0, 0, 0}
 #define VS_PROF_ADD(slot) do { long long prof_t1 = clock64(); prof_acc[(slot) % 3] += prof_t1 - prof_t0; prof_t0 = prof_t1; } while (0)
 #define VS_PROF_FLUSH(first) do { if (lane == 0) { for (int pi = 0; pi < 3; ++pi) atomicAdd(&g_prof[(first) + pi], (unsigned long long)prof_acc[((first) + pi) % 3]); } } while (0)
+// Time line of one CTA (block 0): clock64 at event `ev` of stage / item `idx`.
+__device__ long long g_trace[12][2048];
+#define VS_TRACE(ev, idx) do { if (blockIdx.x == 0 && (idx) < 2048u) g_trace[ev][idx] = clock64(); } while (0)
 #else
+#define VS_TRACE(ev, idx) do { } while (0)
 #define VS_PROF_T0() do { } while (0)
 #define VS_PROF_ADD(slot) do { } while (0)
 #define VS_PROF_FLUSH(first) do { } while (0)
@@ -122,6 +126,40 @@ __device__ __forceinline__ void tma_gather4(uint32_t dst, const void *tensor_map
         : "memory");
 }
 
+// Tile load from a 3-D tensor map (box set in the map) into this CTA's shared memory; coordinates innermost
+// first.  x * element size must be a multiple of 16 bytes.  Elements outside the tensor arrive as zeros.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *tensor_map, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+        "l"(tensor_map), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+// Tile store from this CTA's shared memory through a 3-D tensor map; elements outside the tensor are not
+// written.  Coordinates must not be negative and x * element size must be a multiple of 16 bytes.  Completion
+// is tracked per thread in bulk groups.
+__device__ __forceinline__ void tma_store_3d(const void *tensor_map, uint32_t src, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(tensor_map),
+                 "r"(src), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most N of this thread's bulk groups still READ their shared-memory source.
+template <int N> __device__ __forceinline__ void bulk_wait_group_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Waits until at most N of this thread's bulk groups are incomplete (their global writes done).
+template <int N> __device__ __forceinline__ void bulk_wait_group() {
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+// Adds `bytes` to the byte count `bar` waits for, without arriving.
+__device__ __forceinline__ void mbar_expect_tx_only(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
 // ---- tensor memory ---------------------------------------------------------------------------------------
 // Executed by one full warp.  `ncols` is a power of two in [32, 512].  The base address lands in *dst_smem.
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
@@ -198,6 +236,17 @@ __device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
 }

@@ -10,7 +10,7 @@ namespace vs {
 namespace tcselftest {
 
 constexpr uint32_t kStatusTimeout = 4u;
-constexpr int kTmemCols = 64;
+constexpr int kTmemCols = 128;
 
 __device__ __forceinline__ void tmem_st_x8(uint32_t taddr, const uint32_t (&r)[8]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]),
@@ -21,7 +21,7 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 
 // image: bytes copied to the 1024-byte aligned start of shared memory.  descs: n_mma pairs (A, B) of 64-bit
 // descriptors whose start-address field is RELATIVE to the image start.  The accumulator (128 lanes x ncols
-// fp32 columns, ncols a multiple of 8 up to 64) is pre-filled with `fill`, so lanes an instruction shape does
+// fp32 columns, ncols a multiple of 8 up to 128) is pre-filled with `fill`, so lanes an instruction shape does
 // not write can be told apart, and copied to out[lane * ncols + col].
 __global__ void __launch_bounds__(128) sandbox_kernel(const uint8_t *image, int image_bytes, const uint64_t *descs,
                                                       int n_mma, uint32_t idesc, int ncols, float fill, float *out,

@@ -2,7 +2,9 @@
 //
 // Each operator entry point checks its arguments on the host, picks the template instantiation for
 // (path, element types, vector length) and enqueues the kernel(s) on the caller's stream.  Nothing here
-// synchronises or allocates, except the *_host convenience forms, which say so.
+// synchronises; the *_host convenience forms allocate and say so, and the tensor-core SpMM keeps one plan
+// scratch buffer per calling stream, taken from the stream-ordered allocator the first time (and when a larger
+// matrix needs a larger one).
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -11,12 +13,14 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <unordered_map>
 
 #include "vsparse_b200.h"
 #include "common.cuh"
 #include "cuda_core.cuh"
 #include "spmm_tc.cuh"
 #include "spmm_tma.cuh"
+#include "spmm_dense.cuh"
 #include "sddmm_tc.cuh"
 #include "sddmm_tma.cuh"
 #include "tc_selftest.cuh"
@@ -31,10 +35,17 @@ using namespace vs;
 __device__ uint32_t g_device_status = 0;
 
 constexpr int kMaxDevices = 64;
+struct Scratch {
+    void *ptr = nullptr;
+    size_t bytes = 0;
+};
 struct DeviceInfo {
     bool ready = false;
     int sm_count = 0;
     uint32_t *status = nullptr;
+    // Plan scratch of the densifying SpMM, one buffer per stream that has called it: calls on one stream run
+    // in order, so they can share a buffer; calls on different streams cannot.
+    std::unordered_map<cudaStream_t, Scratch> scratch;
 };
 DeviceInfo g_devices[kMaxDevices];
 std::mutex g_devices_mutex;
@@ -54,6 +65,29 @@ int device_info(DeviceInfo **out) {
         d.ready = true;
     }
     *out = &d;
+    return VS_OK;
+}
+
+// Scratch of at least `bytes` for work enqueued on `stream`.  Grows by stream-ordered allocation (the old buffer
+// is released behind the work already enqueued); in the steady state this makes no CUDA call.  Buffers live
+// until the process ends.
+int stream_scratch(DeviceInfo *d, cudaStream_t stream, size_t bytes, void **out) {
+    std::lock_guard<std::mutex> lock(g_devices_mutex);
+    Scratch &sc = d->scratch[stream];
+    if (sc.bytes < bytes) {
+        size_t want = 1u << 20;
+        while (want < bytes) want <<= 1;
+        void *fresh = nullptr;
+        cudaError_t e = cudaMallocAsync(&fresh, want, stream);
+        if (e != cudaSuccess) {
+            (void)cudaGetLastError();
+            return (int)e;
+        }
+        if (sc.ptr) (void)cudaFreeAsync(sc.ptr, stream);
+        sc.ptr = fresh;
+        sc.bytes = want;
+    }
+    *out = sc.ptr;
     return VS_OK;
 }
 
@@ -96,6 +130,24 @@ int make_gather_map(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t c
     return r == CUDA_SUCCESS ? VS_OK : VS_ERR_ARG;
 }
 
+// Tensor map of a batch of row-major matrices, dimensions {cols, rows, batch}, for tile loads / stores of
+// box_cols x box_rows elements with the 128-byte swizzle (box_cols * element size = 128); loads read zeros
+// outside the matrix, stores are clipped there.
+int make_tile_map(CUtensorMap *map, const void *ptr, bool f32, uint64_t rows, uint64_t cols, uint64_t batch,
+                  uint64_t batch_stride, uint32_t box_cols, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return VS_ERR_DEVICE;
+    const uint64_t es = f32 ? 4 : 2;
+    const cuuint64_t dims[3] = {cols, rows, batch};
+    const cuuint64_t strides[2] = {cols * es, (batch > 1 ? batch_stride : rows * cols) * es};
+    const cuuint32_t box[3] = {box_cols, box_rows, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? VS_OK : VS_ERR_ARG;
+}
+
 // ---- SpMM dispatch ----------------------------------------------------------------------------------------
 template <typename TIn, typename TOut, int V> int launch_spmm_cc(const SpmmParams &p, cudaStream_t s) {
     constexpr int E = Chunk<TIn>::kElems;
@@ -118,7 +170,8 @@ template <typename TIn, typename TOut> int spmm_cc_by_v(int V, const SpmmParams 
 }
 
 // Software (cp.async) gather: works for any batch stride.
-template <typename TOut, int V> int launch_spmm_tc_cpasync(const SpmmParams &p, cudaStream_t s, DeviceInfo *d) {
+template <typename TOut, int V>
+int launch_spmm_tc_cpasync(const SpmmParams &p, cudaStream_t s, DeviceInfo *d, const int32_t *skip_flag = nullptr) {
     auto kernel = tcspmm::spmm_tc_kernel<TOut, V>;
     int rc = set_smem(kernel, tcspmm::kSmemBytes);
     if (rc != VS_OK) return rc;
@@ -126,16 +179,15 @@ template <typename TOut, int V> int launch_spmm_tc_cpasync(const SpmmParams &p, 
     const int64_t items = (int64_t)p.batch * n_tiles * p.m_vec;
     const int64_t cap = (int64_t)tcspmm::kCtasPerSm * d->sm_count;  // persistent CTAs
     const unsigned grid = (unsigned)(items < cap ? items : cap);
-    kernel<<<grid, tcspmm::kThreads, tcspmm::kSmemBytes, s>>>(p, d->status);
+    kernel<<<grid, tcspmm::kThreads, tcspmm::kSmemBytes, s>>>(p, d->status, skip_flag);
     return (int)cudaGetLastError();
 }
 
 // TMA row gather: the dense operand of all batch entries must be addressable as one matrix of N-wide rows,
-// i.e. the batch stride is a multiple of N (or zero / a single entry).
-template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStream_t s) {
-    DeviceInfo *d;
-    int rc = device_info(&d);
-    if (rc != VS_OK) return rc;
+// i.e. the batch stride is a multiple of N (or zero / a single entry).  With `skip_flag` the kernel returns at
+// once when the word it points to is non-zero (the densifying kernel has taken the call).
+template <typename TOut, int V>
+int launch_spmm_gather(const SpmmParams &p, cudaStream_t s, DeviceInfo *d, const int32_t *skip_flag) {
     static const bool force_cpasync = []() {
         const char *e = std::getenv("VSPARSE_B200_GATHER");
         return e && !std::strcmp(e, "cpasync");
@@ -144,10 +196,10 @@ template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStre
     const int64_t rows_per_batch = one ? 0 : p.stride_rhs / p.N;
     const int64_t total_rows = (one ? 0 : (int64_t)(p.batch - 1) * rows_per_batch) + p.K;
     const bool tma_ok = !force_cpasync && p.K > 0 && (one || p.stride_rhs % p.N == 0) && total_rows < 0x7fffffffll;
-    if (!tma_ok) return launch_spmm_tc_cpasync<TOut, V>(p, s, d);
+    if (!tma_ok) return launch_spmm_tc_cpasync<TOut, V>(p, s, d, skip_flag);
     CUtensorMap map;
-    rc = make_gather_map(&map, p.rhs, (uint64_t)total_rows, (uint64_t)p.N);
-    if (rc != VS_OK) return launch_spmm_tc_cpasync<TOut, V>(p, s, d);
+    int rc = make_gather_map(&map, p.rhs, (uint64_t)total_rows, (uint64_t)p.N);
+    if (rc != VS_OK) return launch_spmm_tc_cpasync<TOut, V>(p, s, d, skip_flag);
     auto kernel = tmaspmm::spmm_tma_kernel<TOut, V>;
     rc = set_smem(kernel, tmaspmm::kSmemBytes);
     if (rc != VS_OK) return rc;
@@ -155,8 +207,76 @@ template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStre
     const int64_t items = (int64_t)p.batch * n_tiles * p.m_vec;
     const int64_t cap = (int64_t)tmaspmm::kCtasPerSm * d->sm_count;  // persistent CTAs
     const unsigned grid = (unsigned)(items < cap ? items : cap);
-    kernel<<<grid, tmaspmm::kThreads, tmaspmm::kSmemBytes, s>>>(p, map, (int)rows_per_batch, (int)total_rows, d->status);
+    kernel<<<grid, tmaspmm::kThreads, tmaspmm::kSmemBytes, s>>>(p, map, (int)rows_per_batch, (int)total_rows, d->status,
+                                                                skip_flag);
     return (int)cudaGetLastError();
+}
+
+// Which tensor-core SpMM runs.  The densifying kernel multiplies zero-filled 256 x 64 tiles of A, the gather
+// kernels fetch one row of B per nonzero vector: the first costs the same whatever the sparsity, the second is
+// proportional to the nonzeros.  The number of nonzeros is only known on the device (the reference signature
+// does not pass it), so the choice is made there: the plan kernel compares the density with a threshold and
+// leaves a flag that one of the two kernels, both enqueued, finds set against it and returns at once.  The
+// densifying kernel clears the flag again if it produced a non-finite sum, so that the gather kernel redoes the
+// call with the reference's semantics for Inf / NaN in rows of B that no nonzero names.
+enum class SpmmMode { kAuto, kDense, kGather };
+SpmmMode spmm_mode() {   // read at every call, so that a test can switch kernels inside one process
+    const char *e = std::getenv("VSPARSE_B200_SPMM");
+    if (e && !std::strcmp(e, "dense")) return SpmmMode::kDense;
+    if (e && !std::strcmp(e, "gather")) return SpmmMode::kGather;
+    return SpmmMode::kAuto;
+}
+constexpr int64_t kMaxPlanBytes = 512ll << 20;
+constexpr float kDenseDensityPerV = 0.003f;   // dense from this density on, per element of the vector length
+
+template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStream_t s) {
+    DeviceInfo *d;
+    int rc = device_info(&d);
+    if (rc != VS_OK) return rc;
+    const SpmmMode mode = spmm_mode();
+    const int k_blocks = (p.K + densespmm::kBlockK - 1) / densespmm::kBlockK;
+    const int m_tiles = (p.m_vec * V + densespmm::kTileM - 1) / densespmm::kTileM;
+    const int n_tiles = (p.N + densespmm::kTileN - 1) / densespmm::kTileN;
+    const int groups = m_tiles * densespmm::kFillPerSlot;
+    const int rows_per_group = densespmm::kGroupRows / V;
+    // entries are addressed like the nonzero vectors: at most one per (vector-row, column), and never more than
+    // fit between two matrices of a batch
+    int64_t capacity = (int64_t)p.m_vec * p.K;
+    if (p.batch > 1 && p.stride_values > 0 && p.stride_values / V < capacity) capacity = p.stride_values / V;
+    const int64_t offsets_bytes = (((int64_t)groups * (k_blocks + 1) * 4) + 15) & ~15ll;
+    const int64_t plan_bytes = 16 + offsets_bytes + capacity * 8;
+    const size_t plan_smem = (size_t)(2 * k_blocks + rows_per_group + 1) * 4;
+    const bool dense_ok = mode != SpmmMode::kGather && p.K > 0 && p.m_vec > 0 && p.N % 8 == 0 && plan_bytes <= kMaxPlanBytes &&
+                          plan_smem <= 40 * 1024 && (p.batch == 1 || (p.stride_rhs * 2) % 16 == 0) &&
+                          (p.batch == 1 || (p.stride_out * sizeof(TOut)) % 16 == 0) && aligned16(p.rhs) && aligned16(p.out);
+    if (!dense_ok) return launch_spmm_gather<TOut, V>(p, s, d, nullptr);
+
+    constexpr bool kOutF32 = sizeof(TOut) == 4;
+    CUtensorMap map, map_out;
+    if (make_tile_map(&map, p.rhs, false, (uint64_t)p.K, (uint64_t)p.N, (uint64_t)p.batch, (uint64_t)p.stride_rhs, 64, 64) != VS_OK ||
+        make_tile_map(&map_out, p.out, kOutF32, (uint64_t)p.m_vec * V, (uint64_t)p.N, (uint64_t)p.batch,
+                      (uint64_t)p.stride_out, 128 / sizeof(TOut), 32) != VS_OK)
+        return launch_spmm_gather<TOut, V>(p, s, d, nullptr);
+    auto kernel = densespmm::spmm_dense_kernel<TOut, V>;
+    rc = set_smem(kernel, densespmm::kSmemBytes);
+    if (rc != VS_OK) return rc;
+    uint8_t *plan = nullptr;
+    if (stream_scratch(d, s, (size_t)plan_bytes, reinterpret_cast<void **>(&plan)) != VS_OK)
+        return launch_spmm_gather<TOut, V>(p, s, d, nullptr);
+    int32_t *flag = reinterpret_cast<int32_t *>(plan);
+    int32_t *blk_offsets = reinterpret_cast<int32_t *>(plan + 16);
+    uint2 *blk_entries = reinterpret_cast<uint2 *>(plan + 16 + offsets_bytes);
+    const float threshold = mode == SpmmMode::kDense ? 0.0f : kDenseDensityPerV * V;
+    densespmm::dense_plan_kernel<<<groups, densespmm::kPlanThreads, plan_smem, s>>>(
+        p.row_offsets, p.col_indices, p.m_vec, p.K, rows_per_group, k_blocks, blk_offsets, blk_entries, capacity, threshold,
+        flag);
+    const int64_t items = (int64_t)p.batch * n_tiles * m_tiles;
+    const unsigned grid = (unsigned)(items < d->sm_count ? items : d->sm_count);   // one persistent CTA per SM
+    kernel<<<grid, densespmm::kThreads, densespmm::kSmemBytes, s>>>(p, map, map_out, blk_offsets, blk_entries, m_tiles,
+                                                                    n_tiles, k_blocks, d->status, flag);
+    rc = (int)cudaGetLastError();
+    if (rc == VS_OK) rc = launch_spmm_gather<TOut, V>(p, s, d, flag);
+    return rc;
 }
 
 template <typename TOut> int spmm_tc_by_v(int V, const SpmmParams &p, cudaStream_t s) {
@@ -581,6 +701,14 @@ VS_EXPORT int vs_debug_prof(unsigned long long *out16) {
     VS_CUDA_TRY(cudaMemcpyFromSymbol(out16, vs::g_prof, sizeof(unsigned long long) * 16));
     unsigned long long zero[16] = {0};
     VS_CUDA_TRY(cudaMemcpyToSymbol(vs::g_prof, zero, sizeof(zero)));
+    return VS_OK;
+}
+#endif
+
+#ifdef VS_TC_PROFILE
+VS_EXPORT int vs_debug_trace(long long *out_12x2048) {
+    VS_CUDA_TRY(cudaDeviceSynchronize());
+    VS_CUDA_TRY(cudaMemcpyFromSymbol(out_12x2048, vs::g_trace, sizeof(long long) * 12 * 2048));
     return VS_OK;
 }
 #endif
