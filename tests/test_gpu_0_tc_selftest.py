@@ -102,26 +102,27 @@ def test_tma_row_gather4():
             assert np.array_equal(got[slot, c ^ (slot % 8)], src[c]), (slot, c)
 
 
-def test_k_major_a_times_mn_major_b_wide():
-    """Densified SpMM: A K-major (rows of the sparse tile), B MN-major (64-row x 64-column boxes of the dense
-    operand as TMA writes them, one box per 64 columns, 8 KiB apart), N = 128."""
+def test_mn_major_both_swizzled_wide():
+    """Densified SpMM: A MN-major (128 rows of the sparse tile contiguous, two 64-row atoms 8 KiB apart), B
+    MN-major (64-row x 64-column boxes of the dense operand as TMA writes them, one box per 64 columns, 8 KiB
+    apart), both with the 128-byte swizzle, N = 128, four K = 16 steps 2 KiB apart."""
     rng = np.random.default_rng(3)
     KK, NN = 64, 128
     A = rng.integers(-4, 5, (128, KK)).astype(np.float16)
     B = rng.integers(-4, 5, (KK, NN)).astype(np.float16)
     b_base = 16384
     image = np.zeros((b_base + 2 * 8192) // 2, np.float16)
-    for r in range(128):
+    for m in range(128):
         for kk in range(KK):
-            off = (r // 8) * 1024 + (r % 8) * 128 + (((kk // 8) ^ (r % 8)) * 16) + (kk % 8) * 2
-            put(image, off, A[r, kk])
+            off = (m // 64) * 8192 + (kk // 8) * 1024 + (kk % 8) * 128 + ((((m % 64) // 8) ^ (kk % 8)) * 16) + (m % 8) * 2
+            put(image, off, A[m, kk])
     for kk in range(KK):
         for n in range(NN):
             off = b_base + (n // 64) * 8192 + (kk // 8) * 1024 + (kk % 8) * 128 + ((((n % 64) // 8) ^ (kk % 8)) * 16) + (n % 8) * 2
             put(image, off, B[kk, n])
     descs = []
     for mm in range(KK // 16):
-        descs += [desc(mm * 32, 16, 1024, 2), desc(b_base + mm * 2048, 8192, 1024, 2)]
-    got = run(image, descs, idesc(128, NN, 0, 1), NN)
+        descs += [desc(mm * 2048, 8192, 1024, 2), desc(b_base + mm * 2048, 8192, 1024, 2)]
+    got = run(image, descs, idesc(128, NN, 1, 1), NN)
     want = A.astype(np.float32) @ B.astype(np.float32)
     assert np.array_equal(got, want)

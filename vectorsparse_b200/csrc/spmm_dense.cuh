@@ -6,23 +6,23 @@
 // x 16 MMA takes ~65 cycles, while gathering the rows a vector-row needs costs hundreds of cycles of TMA / LSU
 // issue.  Up to ~97 % sparsity it is cheaper to multiply a zero-filled dense tile of A:
 //     C[256 rows x 128 cols] += A_dense[256 x 64] * B[64 x 128]          per 64-wide block of A's columns.
-// A_dense is built in shared memory from the CVSE arrays (zero fill + one 2-byte store per nonzero element, in
-// the K-major, 128-byte-swizzled layout the MMA reads); B arrives by plain TMA tile loads (two 8 KiB boxes per
+// A_dense is built in shared memory from the CVSE arrays (zero fill + one store per nonzero vector: the operand
+// is kept MN-major, rows contiguous, in the 128-byte-swizzled layout the MMA reads); B arrives by plain TMA tile loads (two 8 KiB boxes per
 // stage, no gather); the products with the zeros are free.  The result is the same sum in another order, except
 // when B holds Inf / NaN in rows no nonzero names (0 x Inf = NaN): the epilogue therefore watches for
 // non-finite sums and, if it sees one, clears the flag that keeps the gather kernel behind it from running.
 //
-// Plan.  A small kernel first buckets the nonzero vectors by (64-row group, 64-column block): `blk_offsets`
+// Plan.  A small kernel first buckets the nonzero vectors by (128-row group, 64-column block): `blk_offsets`
 // [row groups][column blocks + 1] and `blk_entries` (vector index, vector-row within the group, column within
 // the block).  The plan depends on the structure only and is shared by every matrix of a batch.
 //
 // Organisation: one persistent CTA per SM.  Work items are (batch, 128-column tile of B, 256-row tile of A),
 // consecutive CTAs taking consecutive row tiles of the same B so that it stays in L2.  A stage is one 64-wide
 // block of A's columns: 32 KiB of A (two 128-row MMA operands) + 16 KiB of B, four stages in a ring.
-//   warps 0-3    epilogue: TMEM -> registers -> swizzled shared-memory boxes -> TMA stores of whole rows
-//   warps 4-19   fill: four warps per ring slot, each owning 64 rows of the A tile; the first of them also
+//   warps 0-7    epilogue: TMEM -> registers -> swizzled shared-memory boxes -> TMA stores of whole rows
+//   warps 8-15   fill: two warps per ring slot, each owning 128 rows of the A tile; the first of them also
 //                issues the stage's B loads
-//   warps 20-21  one MMA-issuing thread per 128-row half of the tile
+//   warps 16-17  one MMA-issuing thread per 128-row half of the tile
 // Accumulators: 2 halves x 128 columns, double buffered (all 512 TMEM columns), so the epilogue of one item
 // overlaps the MMAs of the next.  Every wait is bounded; a wait that runs out raises the CTA's abort flag, all
 // roles fall through to the end, a status bit is set and tensor memory is freed.
@@ -37,16 +37,17 @@ namespace densespmm {
 
 constexpr int kTileM = 256;                              // rows of A per work item: two MMA operands of 128 rows
 constexpr int kTileN = 128;                              // columns of B per work item (MMA N)
-constexpr int kBlockK = 64;                              // columns of A per stage: 128 bytes of a K-major operand row
-constexpr int kGroupRows = 64;                           // rows per plan bucket = rows one fill warp owns
+constexpr int kBlockK = 64;                              // columns of A (rows of B) per stage
+constexpr int kGroupRows = 128;                          // rows per plan bucket = rows one fill warp owns = one MMA operand
 constexpr int kStages = 4;
-constexpr int kEpiWarps = 4;                             // warps 0..3 (TMEM lane quarter = warp index)
+constexpr int kEpiWarps = 8;                             // warps 0..7: TMEM lane quarter = warp % 4, half of the tile = warp / 4
 constexpr int kFillWarp0 = kEpiWarps;
-constexpr int kFillPerSlot = kTileM / kGroupRows;        // 4
-constexpr int kFillWarps = kStages * kFillPerSlot;       // 16: warp f fills slot f % kStages, rows 64 * (f / kStages) ..
-constexpr int kMmaWarp = kFillWarp0 + kFillWarps;        // 20, 21
+constexpr int kFillPerSlot = kTileM / kGroupRows;        // 2
+constexpr int kFillWarps = kStages * kFillPerSlot;       // 8: warp f fills slot f % kStages, rows 128 * (f / kStages) ..
+constexpr int kFillBatches = 4;                          // entries a fill warp keeps in flight: 4 x 32
+constexpr int kMmaWarp = kFillWarp0 + kFillWarps;        // 16, 17
 constexpr int kMmaWarps = kTileM / 128;                  // 2
-constexpr int kThreads = (kMmaWarp + kMmaWarps) * 32;    // 704
+constexpr int kThreads = (kMmaWarp + kMmaWarps) * 32;    // 576
 constexpr int kAStageBytes = kTileM * kBlockK * 2;       // 32 KiB
 constexpr int kBSlabBytes = kBlockK * 64 * 2;            // 8 KiB: 64 rows of B x 64 columns
 constexpr int kBStageBytes = (kTileN / 64) * kBSlabBytes;  // 16 KiB
@@ -60,8 +61,8 @@ constexpr uint32_t kStatusTimeout = 64u;  // bit raised in the status word when 
 struct Smem {  // offsets from the 1024-byte aligned base
     static constexpr int kA = 0;
     static constexpr int kB = kA + kStages * kAStageBytes;
-    static constexpr int kStaging = kB + kStages * kBStageBytes;   // per epilogue warp: two 32-row x 128-byte boxes
-    static constexpr int kBarFull = kStaging + kEpiWarps * 2 * kStoreBoxBytes;
+    static constexpr int kStaging = kB + kStages * kBStageBytes;   // per epilogue warp: one 32-row x 128-byte box
+    static constexpr int kBarFull = kStaging + kEpiWarps * kStoreBoxBytes;
     static constexpr int kBarEmpty = kBarFull + kStages * 8;
     static constexpr int kBarAccFull = kBarEmpty + kStages * 8;
     static constexpr int kBarAccEmpty = kBarAccFull + 2 * 8;
@@ -74,7 +75,7 @@ static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 static_assert(kFillWarps % kStages == 0, "each ring slot needs fixed owner warps");
 
 // ---- plan -------------------------------------------------------------------------------------------------
-// One CTA per 64-row group (64 / V vector-rows, whose nonzero vectors are contiguous in the CVSE arrays).
+// One CTA per 128-row group (128 / V vector-rows, whose nonzero vectors are contiguous in the CVSE arrays).
 // blk_offsets[g * (k_blocks + 1) + kb] .. [.. + kb + 1] delimit the entries of group g in column block kb;
 // entry = (vector index j, (vector-row within the group << 6) | column within the block).  Columns outside
 // [0, K) are dropped (the gather kernels read zeros for them).
@@ -159,21 +160,20 @@ __device__ __forceinline__ Item decode_item(int64_t w, int m_tiles, int n_tiles,
     const int nt = (int)(r % n_tiles);
     it.b = (int)(r / n_tiles);
     it.n0 = nt * kTileN;
-    it.tn = min(kTileN, (N - it.n0 + 15) & ~15);   // MMA N: a multiple of 16
+    it.tn = min(kTileN, (N - it.n0 + 63) & ~63);   // MMA N: whole 64-column boxes of B (zero-filled past N)
     return it;
 }
 
-// Scatters one nonzero vector (V halves at `v`) into the fill warp's 64 rows of the A stage at `a_part`.
-template <int V>
-__device__ __forceinline__ void scatter_vector(uint8_t *a_part, uint32_t packed, const __half *v) {
-    const uint32_t cb = packed & 63u;
-    const uint32_t row = ((packed >> 6) * V) & (kGroupRows - 1);   // first row of the vector inside the group
-    uint8_t *base = a_part + (row >> 3) * 1024 + (cb & 7u) * 2;
-#pragma unroll
-    for (int e = 0; e < V; ++e) {
-        const uint32_t r8 = (row & 7u) + e;                        // V divides 8: the vector stays in one 8-row block
-        *reinterpret_cast<__half *>(base + r8 * 128 + (((cb >> 3) ^ r8) << 4)) = v[e];
-    }
+// Drops one nonzero vector (`raw`: its V halves) into the fill warp's 128 rows of the A stage at `a_part`.
+// The operand is MN-major (rows of A contiguous) with the 128-byte swizzle: element (row m, column k) of the
+// 128 x 64 block lives at (m / 64) * 8 KiB + (k / 8) * 1 KiB + (k % 8) * 128 + (((m % 64) / 8) ^ (k % 8)) * 16 +
+// (m % 8) * 2, so the V consecutive rows of a vector (V divides 8) are one contiguous store.
+template <int V, typename Raw>
+__device__ __forceinline__ void scatter_vector(uint8_t *a_part, uint32_t packed, const Raw &raw) {
+    const uint32_t k = packed & 63u;
+    const uint32_t m = ((packed >> 6) * V) & (kGroupRows - 1);   // first row of the vector inside the group
+    uint8_t *dst = a_part + (m >> 6) * 8192 + (k >> 3) * 1024 + (k & 7u) * 128 + ((((m & 63u) >> 3) ^ (k & 7u)) << 4) + (m & 7u) * 2;
+    *reinterpret_cast<Raw *>(dst) = raw;
 }
 
 template <int V> struct ValueVec;   // the V fp16 values of one nonzero vector, loaded with one instruction
@@ -238,12 +238,12 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
         // =========================== fill ================================================================
         const int fw = warp - kFillWarp0;
         const uint32_t slot = (uint32_t)(fw % kStages);
-        const int part = fw / kStages;                     // rows 64 * part .. + 63 of the tile
+        const int part = fw / kStages;                     // rows 128 * part .. + 127 of the tile
         uint8_t *a_part = sm + Smem::kA + slot * kAStageBytes + part * (kGroupRows * kBlockK * 2);
         const uint32_t bar = bar_full + 8 * slot;
 
         // Software pipeline over this warp's stages (slot, slot + 4, ...): bucket bounds two stages ahead, the
-        // first 64 entries one stage ahead, their values before the wait for the slot.
+        // first 128 entries one stage ahead, their values before the wait for the slot.
         struct Pos { int b, n0, tn, mt, kb; bool valid; };
         auto locate = [&](uint32_t g) {
             Pos q;
@@ -266,9 +266,9 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
         int c_e0, c_e1, n_e0, n_e1;
         bounds(cur, c_e0, c_e1);
         bounds(nxt, n_e0, n_e1);
-        uint2 c_ent[2];
+        uint2 c_ent[kFillBatches];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < kFillBatches; ++u) {
             const int e = c_e0 + lane + 32 * u;
             c_ent[u] = e < c_e1 ? __ldg(blk_entries + e) : make_uint2(0u, 0u);
         }
@@ -276,15 +276,15 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
         VS_PROF_T0();
         for (uint32_t g = slot; g < total_stages && ok_run; g += kStages) {
             const __half *vals = static_cast<const __half *>(p.values) + (int64_t)cur.b * p.stride_values;
-            // values of the first 64 entries, entries of the next stage, bounds of the one after: all in flight
+            // values of the first 128 entries, entries of the next stage, bounds of the one after: all in flight
             // while this warp waits for its slot
-            ValueVec<V> c_val[2];
+            ValueVec<V> c_val[kFillBatches];
 #pragma unroll
-            for (int u = 0; u < 2; ++u)
+            for (int u = 0; u < kFillBatches; ++u)
                 if (c_e0 + lane + 32 * u < c_e1) c_val[u].load(vals + (int64_t)c_ent[u].x * V);
-            uint2 n_ent[2];
+            uint2 n_ent[kFillBatches];
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
+            for (int u = 0; u < kFillBatches; ++u) {
                 const int e = n_e0 + lane + 32 * u;
                 n_ent[u] = e < n_e1 ? __ldg(blk_entries + e) : make_uint2(0u, 0u);
             }
@@ -303,27 +303,29 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                     tc::tma_load_3d(base + Smem::kB + slot * kBStageBytes + s * kBSlabBytes, &map_b, bar, cur.n0 + 64 * s,
                                     cur.kb * kBlockK, cur.b);
             }
-            // zero this warp's 8 KiB of the A stage, then drop the nonzeros in
+            // zero this warp's 16 KiB of the A stage, then drop the nonzeros in
 #pragma unroll
             for (int i = 0; i < (kGroupRows * kBlockK * 2) / (32 * 16); ++i)
                 reinterpret_cast<uint4 *>(a_part)[i * 32 + lane] = make_uint4(0, 0, 0, 0);
             __syncwarp();
             VS_PROF_ADD(1);   // fill: B loads + zero fill
 #pragma unroll
-            for (int u = 0; u < 2; ++u)
+            for (int u = 0; u < kFillBatches; ++u)
                 if (c_e0 + lane + 32 * u < c_e1)
-                    scatter_vector<V>(a_part, c_ent[u].y, reinterpret_cast<const __half *>(&c_val[u].raw));
-            for (int e = c_e0 + 64 + lane; e < c_e1; e += 32) {   // buckets with more than 64 entries (dense rows)
+                    scatter_vector<V>(a_part, c_ent[u].y, c_val[u].raw);
+            for (int e = c_e0 + 32 * kFillBatches + lane; e < c_e1; e += 32) {   // buckets with more entries (denser rows)
                 const uint2 ent = __ldg(blk_entries + e);
                 ValueVec<V> val;
                 val.load(vals + (int64_t)ent.x * V);
-                scatter_vector<V>(a_part, ent.y, reinterpret_cast<const __half *>(&val.raw));
+                scatter_vector<V>(a_part, ent.y, val.raw);
             }
             tc::fence_proxy_async();   // the tile was written by ordinary stores; the MMA reads through the async proxy
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(bar);
 
-            cur = nxt; c_e0 = n_e0; c_e1 = n_e1; c_ent[0] = n_ent[0]; c_ent[1] = n_ent[1];
+            cur = nxt; c_e0 = n_e0; c_e1 = n_e1;
+#pragma unroll
+            for (int u = 0; u < kFillBatches; ++u) c_ent[u] = n_ent[u];
             nxt = nn; n_e0 = nn_e0; n_e1 = nn_e1;
             VS_PROF_ADD(2);   // fill: scatter, arrive
         }
@@ -334,7 +336,7 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
         // to its `empty` barrier, so each has seen every earlier use of a slot complete.
         if (lane == 0) {
             const int h = warp - kMmaWarp;
-            const uint32_t a_lo0 = tc::smem_desc_lo(base + Smem::kA + h * (128 * kBlockK * 2), 16);
+            const uint32_t a_lo0 = tc::smem_desc_lo(base + Smem::kA + h * (128 * kBlockK * 2), 8192);   // 64-row atoms 8 KiB apart
             const uint32_t a_hi = tc::smem_desc_hi(1024, (uint32_t)tc::kSwizzle128B);
             const uint32_t b_lo0 = tc::smem_desc_lo(base + Smem::kB, kBSlabBytes);
             const uint32_t b_hi = tc::smem_desc_hi(1024, (uint32_t)tc::kSwizzle128B);
@@ -343,7 +345,7 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
             VS_PROF_T0();
             for (uint32_t i = 0; i < my_items && ok_run; ++i) {
                 const Item it = decode_item(blockIdx.x + (int64_t)i * G, m_tiles, n_tiles, p.N);
-                const uint32_t idesc = tc::make_idesc_f16(128, it.tn, 0, 1);
+                const uint32_t idesc = tc::make_idesc_f16(128, it.tn, 1, 1);   // both operands MN-major
                 const uint32_t buf = i & 1u;
                 if (i >= 2) ok_run = wait_or_abort<kSleepMma>(bar_acc_empty + 8 * buf, ((i >> 1) - 1u) & 1u, abort_flag);
                 const uint32_t d = tmem_base + buf * kAccCols + (uint32_t)h * kTileN;
@@ -358,8 +360,8 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                     const int n_k16 = min(kBlockK / 16, (p.K - kb * kBlockK + 15) >> 4);
 #pragma unroll
                     for (int kk = 0; kk < kBlockK / 16; ++kk)
-                        if (kk < n_k16)   // 16 columns of A = 32 bytes along its rows = 16 rows of B = 2 KiB
-                            tc::mma_f16_ss(d, tc::desc64(a_lo + 2 * kk, a_hi), tc::desc64(b_lo + 128 * kk, b_hi), idesc,
+                        if (kk < n_k16)   // 16 columns of A = 16 rows of B = 2 KiB further on in either operand
+                            tc::mma_f16_ss(d, tc::desc64(a_lo + 128 * kk, a_hi), tc::desc64(b_lo + 128 * kk, b_hi), idesc,
                                            (kb == 0 && kk == 0) ? 0u : 1u);
                     tc::mma_commit(bar_empty + 8 * slot);
                     VS_PROF_ADD(5);   // mma: issue
@@ -371,10 +373,10 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
     } else {
         // =========================== epilogue ============================================================
         bool ok_run = true;
-        uint32_t non_finite = 0;
-        uint32_t store_count = 0;
-        uint8_t *stg = sm + Smem::kStaging + warp * 2 * kStoreBoxBytes;
-        const uint32_t stg_u32 = base + Smem::kStaging + warp * 2 * kStoreBoxBytes;
+        float finite_probe = 0.0f;
+        const int quarter = warp & 3, half = warp >> 2;   // TMEM lanes 32 * quarter .. + 31; rows 128 * half .. of the tile
+        uint8_t *stg = sm + Smem::kStaging + warp * kStoreBoxBytes;
+        const uint32_t stg_u32 = base + Smem::kStaging + warp * kStoreBoxBytes;
         VS_PROF_T0();
         for (uint32_t i = 0; i < my_items && ok_run; ++i) {
             const Item it = decode_item(blockIdx.x + (int64_t)i * G, m_tiles, n_tiles, p.N);
@@ -384,69 +386,65 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
             if (!ok_run) break;
             VS_PROF_ADD(6);   // epilogue: wait for the accumulator
             tc::tc_fence_after_sync();
-            // Each warp moves its 32 rows through two 4 KiB boxes of shared memory (32 rows x 128 bytes, the
-            // 16-byte chunks XOR-swizzled by row so that the row-per-thread writes spread over the banks) and
-            // lets TMA write them out as whole rows; a box is refilled once the store issued from it two boxes
-            // earlier has read it.
+            // Each warp moves its 32 rows, 128 bytes of columns at a time, through a 4 KiB box of shared memory
+            // (the 16-byte chunks XOR-swizzled by row so that the row-per-thread writes spread over the banks)
+            // and lets TMA write them out as whole rows; the box is refilled once the previous store has read it.
             constexpr int kBoxCols = 128 / (int)sizeof(TOut);   // 64 fp16 or 32 fp32 columns
+            const int row0 = it.mt * kTileM + half * 128 + quarter * 32;   // first row of this warp's boxes
 #pragma unroll 1
-            for (int h = 0; h < kMmaWarps; ++h) {
-                const int row0 = it.mt * kTileM + h * 128 + warp * 32;   // first row of this warp's box
-#pragma unroll 1
-                for (int c0 = 0; c0 < it.tn; c0 += kBoxCols) {
-                    uint32_t r[kBoxCols];
-                    const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * kAccCols + (uint32_t)(h * kTileN + c0);
-                    if constexpr (kBoxCols == 64) {
-                        tc::tmem_ld_x32(taddr, reinterpret_cast<uint32_t(&)[32]>(r[0]));
-                        tc::tmem_ld_x32(taddr + 32, reinterpret_cast<uint32_t(&)[32]>(r[32]));
-                    } else {
-                        tc::tmem_ld_x32(taddr, r);
+            for (int c0 = 0; c0 < it.tn; c0 += kBoxCols) {
+                uint32_t r[kBoxCols];
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * kAccCols + (uint32_t)(half * kTileN + c0);
+                if constexpr (kBoxCols == 64) {
+                    tc::tmem_ld_x32(taddr, reinterpret_cast<uint32_t(&)[32]>(r[0]));
+                    tc::tmem_ld_x32(taddr + 32, reinterpret_cast<uint32_t(&)[32]>(r[32]));
+                } else {
+                    tc::tmem_ld_x32(taddr, r);
+                }
+                tc::tmem_ld_wait();
+                if (row0 < m_rows && it.n0 + c0 < p.N) {   // warp-uniform
+                    // x * 0 is 0 for a finite x and NaN otherwise: one FMA per element finds a non-finite sum
+                    // (every column of the box was written by the MMA: columns past N multiply zero-filled B)
+                    if (row0 + lane < m_rows) {
+#pragma unroll
+                        for (int e = 0; e < kBoxCols; ++e) finite_probe = fmaf(__uint_as_float(r[e]), 0.0f, finite_probe);
                     }
-                    tc::tmem_ld_wait();
-                    if (row0 < m_rows && it.n0 + c0 < p.N) {   // warp-uniform
-                        if (row0 + lane < m_rows) {   // only what reaches the output counts
-                            const int valid = p.N - it.n0 - c0;
+                    VS_PROF_ADD(6);
+                    if (lane == 0) tc::bulk_wait_group_read<0>();   // the previous store has read the box
+                    __syncwarp();
+                    VS_PROF_ADD(7);
+                    uint8_t *dst = stg + lane * 128;
 #pragma unroll
-                            for (int e = 0; e < kBoxCols; ++e)
-                                non_finite |= (e < valid && (r[e] & 0x7f800000u) == 0x7f800000u) ? 1u : 0u;
-                        }
-                        const uint32_t box = store_count & 1u;
-                        if (lane == 0) tc::bulk_wait_group_read<1>();   // the store that used this box before has read it
-                        __syncwarp();
-                        uint8_t *dst = stg + box * kStoreBoxBytes + lane * 128;
+                    for (int u = 0; u < 8; ++u) {   // eight 16-byte chunks per row
+                        uint4 v;
+                        if constexpr (sizeof(TOut) == 2) {
+                            __half2 *hh = reinterpret_cast<__half2 *>(&v);
 #pragma unroll
-                        for (int u = 0; u < 8; ++u) {   // eight 16-byte chunks per row
-                            uint4 v;
-                            if constexpr (sizeof(TOut) == 2) {
-                                __half2 *hh = reinterpret_cast<__half2 *>(&v);
-#pragma unroll
-                                for (int e = 0; e < 4; ++e)
-                                    hh[e] = __floats2half2_rn(__uint_as_float(r[8 * u + 2 * e]), __uint_as_float(r[8 * u + 2 * e + 1]));
-                            } else {
-                                v = make_uint4(r[4 * u], r[4 * u + 1], r[4 * u + 2], r[4 * u + 3]);
-                            }
-                            *reinterpret_cast<uint4 *>(dst + ((u ^ (lane & 7)) << 4)) = v;
+                            for (int e = 0; e < 4; ++e)
+                                hh[e] = __floats2half2_rn(__uint_as_float(r[8 * u + 2 * e]), __uint_as_float(r[8 * u + 2 * e + 1]));
+                        } else {
+                            v = make_uint4(r[4 * u], r[4 * u + 1], r[4 * u + 2], r[4 * u + 3]);
                         }
-                        tc::fence_proxy_async();
-                        __syncwarp();
-                        if (lane == 0) {
-                            tc::tma_store_3d(&map_out, stg_u32 + box * kStoreBoxBytes, it.n0 + c0, row0, it.b);
-                            tc::bulk_commit_group();
-                        }
-                        ++store_count;
+                        *reinterpret_cast<uint4 *>(dst + ((u ^ (lane & 7)) << 4)) = v;
                     }
+                    tc::fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tc::tma_store_3d(&map_out, stg_u32, it.n0 + c0, row0, it.b);
+                        tc::bulk_commit_group();
+                    }
+                    VS_PROF_ADD(8);
                 }
             }
             tc::tc_fence_before_sync();
             tc::mbar_arrive(bar_acc_empty + 8 * buf);   // both halves are in registers or stored: the buffer is free
-            VS_PROF_ADD(7);   // epilogue: TMEM loads, stores
         }
         VS_PROF_FLUSH(6);
         // A zero of the densified tile times an Inf or NaN of B is a NaN that the reference, which only reads
         // the rows of B its nonzeros name, would not produce.  Any non-finite sum hands the call to the gather
         // kernel enqueued behind this one, which then overwrites the output.
         if (lane == 0) tc::bulk_wait_group<0>();   // every store of this warp has reached global memory
-        if (__any_sync(0xffffffffu, non_finite != 0) && lane == 0) atomicExch(use_dense, 0);
+        if (__any_sync(0xffffffffu, finite_probe != 0.0f) && lane == 0) atomicExch(use_dense, 0);
     }
 
     // ---- teardown ---------------------------------------------------------------------------------------
