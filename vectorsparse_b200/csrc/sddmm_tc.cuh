@@ -155,7 +155,6 @@ __global__ void __launch_bounds__(kThreads) sddmm_tc_kernel(const SddmmParams p,
             tc::tc_fence_after_sync();
             uint32_t r[8];
             tc::tmem_ld_x8(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(e.accslot * kAccCols), r);
-            tc::tmem_ld_wait();
             tc::tc_fence_before_sync();
             const int jj = e.jt + t;
             if (jj < e.jend) {

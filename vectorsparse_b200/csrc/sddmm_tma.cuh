@@ -320,7 +320,6 @@ sddmm_tma_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_rh
                     tc::tc_fence_after_sync();
                     uint32_t r[8];
                     tc::tmem_ld_x8(tmem_base + ((uint32_t)(warp * 32) << 16) + acc * kAccCols, r);
-                    tc::tmem_ld_wait();
                     tc::tc_fence_before_sync();
                     mbar_arrive(bar_acc_empty + 8 * acc);     // the accumulator may be overwritten from here on
                     const int jj = tj + t;                    // this thread's mask entry (t = 0..127 here)

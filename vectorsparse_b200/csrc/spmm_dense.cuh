@@ -6,23 +6,26 @@
 // x 16 MMA takes ~65 cycles, while gathering the rows a vector-row needs costs hundreds of cycles of TMA / LSU
 // issue.  Up to ~97 % sparsity it is cheaper to multiply a zero-filled dense tile of A:
 //     C[256 rows x 128 cols] += A_dense[256 x 64] * B[64 x 128]          per 64-wide block of A's columns.
-// A_dense is built in shared memory from the CVSE arrays (zero fill + one store per nonzero vector: the operand
-// is kept MN-major, rows contiguous, in the 128-byte-swizzled layout the MMA reads); B arrives by plain TMA tile loads (two 8 KiB boxes per
+// A_dense is built in shared memory from the CVSE arrays (one store per nonzero vector into a tile of zeros,
+// and one to take it out again afterwards: the operand is kept MN-major, rows contiguous, in the
+// 128-byte-swizzled layout the MMA reads); B arrives by plain TMA tile loads (two 8 KiB boxes per
 // stage, no gather); the products with the zeros are free.  The result is the same sum in another order, except
 // when B holds Inf / NaN in rows no nonzero names (0 x Inf = NaN): the epilogue therefore watches for
 // non-finite sums and, if it sees one, clears the flag that keeps the gather kernel behind it from running.
 //
-// Plan.  A small kernel first buckets the nonzero vectors by (128-row group, 64-column block): `blk_offsets`
+// Plan.  A small kernel first buckets the nonzero vectors by (128-row group, 32-column block): `blk_offsets`
 // [row groups][column blocks + 1] and `blk_entries` (vector index, vector-row within the group, column within
 // the block).  The plan depends on the structure only and is shared by every matrix of a batch.
 //
 // Organisation: one persistent CTA per SM.  Work items are (batch, 128-column tile of B, 256-row tile of A),
 // consecutive CTAs taking consecutive row tiles of the same B so that it stays in L2.  A stage is one 64-wide
-// block of A's columns: 32 KiB of A (two 128-row MMA operands) + 16 KiB of B, four stages in a ring.
+// block of A's columns: 32 KiB of A (two 128-row MMA operands, ring of three) + 16 KiB of B (ring of six: its
+// loads are what has latency to hide).
 //   warps 0-7    epilogue: TMEM -> registers -> swizzled shared-memory boxes -> TMA stores of whole rows
-//   warps 8-15   fill: two warps per ring slot, each owning 128 rows of the A tile; the first of them also
-//                issues the stage's B loads
-//   warps 16-17  one MMA-issuing thread per 128-row half of the tile
+//   warps 8-19   fill: four warps per A slot, one per plan bucket (128 rows x 32 columns) of the stage
+//   warp 20      one thread issuing the B loads, up to six stages ahead
+//   warp 21      L2 prefetch of the next item's part of B
+//   warps 22-23  one MMA-issuing thread per 128-row half of the tile
 // Accumulators: 2 halves x 128 columns, double buffered (all 512 TMEM columns), so the epilogue of one item
 // overlaps the MMAs of the next.  Every wait is bounded; a wait that runs out raises the CTA's abort flag, all
 // roles fall through to the end, a status bit is set and tensor memory is freed.
@@ -38,16 +41,20 @@ namespace densespmm {
 constexpr int kTileM = 256;                              // rows of A per work item: two MMA operands of 128 rows
 constexpr int kTileN = 128;                              // columns of B per work item (MMA N)
 constexpr int kBlockK = 64;                              // columns of A (rows of B) per stage
-constexpr int kGroupRows = 128;                          // rows per plan bucket = rows one fill warp owns = one MMA operand
-constexpr int kStages = 4;
+constexpr int kGroupRows = 128;                          // rows per plan bucket: one MMA operand
+constexpr int kPlanCols = 32;                            // columns per plan bucket: half a stage
+constexpr int kAStages = 3;                              // ring of densified A tiles
+constexpr int kBStages = 6;                              // ring of B tiles: deeper, their loads have the latency to hide
 constexpr int kEpiWarps = 8;                             // warps 0..7: TMEM lane quarter = warp % 4, half of the tile = warp / 4
 constexpr int kFillWarp0 = kEpiWarps;
-constexpr int kFillPerSlot = kTileM / kGroupRows;        // 2
-constexpr int kFillWarps = kStages * kFillPerSlot;       // 8: warp f fills slot f % kStages, rows 128 * (f / kStages) ..
-constexpr int kFillBatches = 4;                          // entries a fill warp keeps in flight: 4 x 32
-constexpr int kMmaWarp = kFillWarp0 + kFillWarps;        // 16, 17
+constexpr int kFillPerSlot = (kTileM / kGroupRows) * (kBlockK / kPlanCols);   // 4: one warp per plan bucket of a stage
+constexpr int kFillWarps = kAStages * kFillPerSlot;      // 12: warp f fills A slot f % kAStages, bucket f / kAStages
+constexpr int kFillBatches = 2;                          // entries a fill warp keeps in flight: 2 x 32
+constexpr int kLoadWarp = kFillWarp0 + kFillWarps;       // 20: one thread issues the B loads
+constexpr int kPrefetchWarp = kLoadWarp + 1;             // 21: asks the next item's rows of B into L2
+constexpr int kMmaWarp = kPrefetchWarp + 1;              // 22, 23
 constexpr int kMmaWarps = kTileM / 128;                  // 2
-constexpr int kThreads = (kMmaWarp + kMmaWarps) * 32;    // 576
+constexpr int kThreads = (kMmaWarp + kMmaWarps) * 32;    // 768
 constexpr int kAStageBytes = kTileM * kBlockK * 2;       // 32 KiB
 constexpr int kBSlabBytes = kBlockK * 64 * 2;            // 8 KiB: 64 rows of B x 64 columns
 constexpr int kBStageBytes = (kTileN / 64) * kBSlabBytes;  // 16 KiB
@@ -60,25 +67,27 @@ constexpr uint32_t kStatusTimeout = 64u;  // bit raised in the status word when 
 
 struct Smem {  // offsets from the 1024-byte aligned base
     static constexpr int kA = 0;
-    static constexpr int kB = kA + kStages * kAStageBytes;
-    static constexpr int kStaging = kB + kStages * kBStageBytes;   // per epilogue warp: one 32-row x 128-byte box
-    static constexpr int kBarFull = kStaging + kEpiWarps * kStoreBoxBytes;
-    static constexpr int kBarEmpty = kBarFull + kStages * 8;
-    static constexpr int kBarAccFull = kBarEmpty + kStages * 8;
+    static constexpr int kB = kA + kAStages * kAStageBytes;
+    static constexpr int kStaging = kB + kBStages * kBStageBytes;   // per epilogue warp: one 32-row x 128-byte box
+    static constexpr int kBarFull = kStaging + kEpiWarps * kStoreBoxBytes;   // one pair of barriers per B slot
+    static constexpr int kBarEmpty = kBarFull + kBStages * 8;
+    static constexpr int kBarAccFull = kBarEmpty + kBStages * 8;
     static constexpr int kBarAccEmpty = kBarAccFull + 2 * 8;
     static constexpr int kTmemHolder = kBarAccEmpty + 2 * 8;
     static constexpr int kAbort = kTmemHolder + 8;
-    static constexpr int kTotal = kAbort + 8;
+    static constexpr int kLoaderProgress = kAbort + 8;      // stages whose B loads have been issued
+    static constexpr int kTotal = kLoaderProgress + 8;
 };
 constexpr int kSmemBytes = Smem::kTotal + 1024;  // + slack for the manual 1024-byte alignment
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
-static_assert(kFillWarps % kStages == 0, "each ring slot needs fixed owner warps");
+static_assert(kFillWarps % kAStages == 0, "each ring slot needs fixed owner warps");
+static_assert(kBStages == 2 * kAStages, "the stage barriers are shared: an A slot is reused every other turn of the B ring");
 
 // ---- plan -------------------------------------------------------------------------------------------------
 // One CTA per 128-row group (128 / V vector-rows, whose nonzero vectors are contiguous in the CVSE arrays).
-// blk_offsets[g * (k_blocks + 1) + kb] .. [.. + kb + 1] delimit the entries of group g in column block kb;
-// entry = (vector index j, (vector-row within the group << 6) | column within the block).  Columns outside
-// [0, K) are dropped (the gather kernels read zeros for them).
+// blk_offsets[g * (plan_blocks + 1) + c] .. [.. + c + 1] delimit the entries of group g in the 32-column block
+// c; entry = (vector index j, (vector-row within the group << 6) | column within the 64-column stage).  Columns
+// outside [0, K) are dropped (the gather kernels read zeros for them).
 //
 // The kernel also takes the decision between the densifying and the gather kernels, because the number of
 // nonzero vectors is only known here: dense when the density reaches `threshold` and the entries fit the
@@ -86,7 +95,7 @@ static_assert(kFillWarps % kStages == 0, "each ring slot needs fixed owner warps
 // kernels enqueued behind this one, and nothing is planned when the answer is no.
 __global__ void __launch_bounds__(kPlanThreads)
 dense_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__restrict__ col_indices, int m_vec, int K,
-                  int rows_per_group, int k_blocks, int32_t *__restrict__ blk_offsets, uint2 *__restrict__ blk_entries,
+                  int rows_per_group, int plan_blocks, int32_t *__restrict__ blk_offsets, uint2 *__restrict__ blk_entries,
                   int64_t entry_capacity, float threshold, int32_t *use_dense) {
     extern __shared__ int plan_sh[];
     {
@@ -96,30 +105,30 @@ dense_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__rest
         if (blockIdx.x == 0 && threadIdx.x == 0) *use_dense = dense ? 1 : 0;
         if (!dense) return;
     }
-    int *hist = plan_sh;                      // [k_blocks]
-    int *cursor = plan_sh + k_blocks;         // [k_blocks]
-    int *roff = plan_sh + 2 * k_blocks;       // [rows_per_group + 1]
+    int *hist = plan_sh;                         // [plan_blocks]
+    int *cursor = plan_sh + plan_blocks;         // [plan_blocks]
+    int *roff = plan_sh + 2 * plan_blocks;       // [rows_per_group + 1]
     const int g = blockIdx.x, t = threadIdx.x;
     const int r0 = min(m_vec, g * rows_per_group), r1 = min(m_vec, r0 + rows_per_group);
     const int nr = r1 - r0;
-    for (int i = t; i < k_blocks; i += kPlanThreads) hist[i] = 0;
+    for (int i = t; i < plan_blocks; i += kPlanThreads) hist[i] = 0;
     for (int i = t; i <= nr; i += kPlanThreads) roff[i] = __ldg(row_offsets + r0 + i);
     __syncthreads();
     const int j0 = roff[0], j1 = roff[nr];
     for (int j = j0 + t; j < j1; j += kPlanThreads) {
         const int c = __ldg(col_indices + j);
-        if ((unsigned)c < (unsigned)K) atomicAdd(hist + (c >> 6), 1);
+        if ((unsigned)c < (unsigned)K) atomicAdd(hist + c / kPlanCols, 1);
     }
     __syncthreads();
     if (t == 0) {
         int run = j0;
-        int32_t *o = blk_offsets + (int64_t)g * (k_blocks + 1);
-        for (int kb = 0; kb < k_blocks; ++kb) {
-            cursor[kb] = run;
-            o[kb] = run;
-            run += hist[kb];
+        int32_t *o = blk_offsets + (int64_t)g * (plan_blocks + 1);
+        for (int c = 0; c < plan_blocks; ++c) {
+            cursor[c] = run;
+            o[c] = run;
+            run += hist[c];
         }
-        o[k_blocks] = run;
+        o[plan_blocks] = run;
     }
     __syncthreads();
     for (int j = j0 + t; j < j1; j += kPlanThreads) {
@@ -130,8 +139,8 @@ dense_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__rest
             const int mid = (lo + hi) >> 1;
             if (roff[mid] <= j) lo = mid; else hi = mid;
         }
-        const int pos = atomicAdd(cursor + (c >> 6), 1);
-        blk_entries[pos] = make_uint2((uint32_t)j, ((uint32_t)lo << 6) | (uint32_t)(c & 63));
+        const int pos = atomicAdd(cursor + c / kPlanCols, 1);
+        blk_entries[pos] = make_uint2((uint32_t)j, ((uint32_t)lo << 6) | (uint32_t)(c & (kBlockK - 1)));
     }
 }
 
@@ -164,6 +173,42 @@ __device__ __forceinline__ Item decode_item(int64_t w, int m_tiles, int n_tiles,
     return it;
 }
 
+// The same walk without divisions, for the roles that locate a stage every few hundred cycles: position
+// (batch entry, column tile, row tile, column block) of stage g, advanced by a fixed number of stages.
+struct StageIter {
+    int b, nt, mt, kb;
+    int d_mt, d_nt, d_b;   // one step of gridDim.x work items, as digits of (b, nt, mt)
+    int m_tiles, n_tiles, k_blocks;
+    uint32_t g, total;
+    __device__ __forceinline__ void init(uint32_t g0, uint32_t total_stages, int m_tiles_, int n_tiles_, int k_blocks_) {
+        m_tiles = m_tiles_; n_tiles = n_tiles_; k_blocks = k_blocks_;
+        g = g0; total = total_stages;
+        const uint32_t G = gridDim.x;
+        d_mt = (int)(G % (uint32_t)m_tiles);
+        const uint32_t r = G / (uint32_t)m_tiles;
+        d_nt = (int)(r % (uint32_t)n_tiles);
+        d_b = (int)(r / (uint32_t)n_tiles);
+        const uint32_t i0 = g0 / (uint32_t)k_blocks;       // divisions once, here
+        kb = (int)(g0 - i0 * (uint32_t)k_blocks);
+        const int64_t w = blockIdx.x + (int64_t)i0 * G;
+        mt = (int)(w % m_tiles);
+        const int64_t rr = w / m_tiles;
+        nt = (int)(rr % n_tiles);
+        b = (int)(rr / n_tiles);
+    }
+    __device__ __forceinline__ bool valid() const { return g < total; }
+    __device__ __forceinline__ void next_item() {
+        mt += d_mt; nt += d_nt; b += d_b;
+        if (mt >= m_tiles) { mt -= m_tiles; ++nt; }
+        if (nt >= n_tiles) { nt -= n_tiles; ++b; }   // d_nt + carry < 2 n_tiles: one correction is enough
+    }
+    __device__ __forceinline__ void advance(int stages) {
+        g += (uint32_t)stages;
+        kb += stages;
+        while (kb >= k_blocks) { kb -= k_blocks; next_item(); }
+    }
+};
+
 // Drops one nonzero vector (`raw`: its V halves) into the fill warp's 128 rows of the A stage at `a_part`.
 // The operand is MN-major (rows of A contiguous) with the 128-byte swizzle: element (row m, column k) of the
 // 128 x 64 block lives at (m / 64) * 8 KiB + (k / 8) * 1 KiB + (k % 8) * 128 + (((m % 64) / 8) ^ (k % 8)) * 16 +
@@ -177,18 +222,21 @@ __device__ __forceinline__ void scatter_vector(uint8_t *a_part, uint32_t packed,
 }
 
 template <int V> struct ValueVec;   // the V fp16 values of one nonzero vector, loaded with one instruction
-template <> struct ValueVec<8> { uint4 raw; __device__ void load(const __half *p) { raw = __ldg(reinterpret_cast<const uint4 *>(p)); } };
-template <> struct ValueVec<4> { uint2 raw; __device__ void load(const __half *p) { raw = __ldg(reinterpret_cast<const uint2 *>(p)); } };
-template <> struct ValueVec<2> { uint32_t raw; __device__ void load(const __half *p) { raw = __ldg(reinterpret_cast<const uint32_t *>(p)); } };
-template <> struct ValueVec<1> { unsigned short raw; __device__ void load(const __half *p) { raw = __ldg(reinterpret_cast<const unsigned short *>(p)); } };
+template <> struct ValueVec<8> { typedef uint4 Raw; uint4 raw; __device__ void load(const __half *p) { raw = __ldg(reinterpret_cast<const uint4 *>(p)); } };
+template <> struct ValueVec<4> { typedef uint2 Raw; uint2 raw; __device__ void load(const __half *p) { raw = __ldg(reinterpret_cast<const uint2 *>(p)); } };
+template <> struct ValueVec<2> { typedef uint32_t Raw; uint32_t raw; __device__ void load(const __half *p) { raw = __ldg(reinterpret_cast<const uint32_t *>(p)); } };
+template <> struct ValueVec<1> { typedef unsigned short Raw; unsigned short raw; __device__ void load(const __half *p) { raw = __ldg(reinterpret_cast<const unsigned short *>(p)); } };
 
 // map_b: 3-D tensor map of the dense operand, dimensions {N, K, batch}, box {64, 64, 1}, 128-byte swizzle,
-// zero fill outside.  map_out: the output, dimensions {N, rows, batch}, box {128 bytes of columns, 32, 1},
+// zero fill outside.  map_b4 (used when N is a multiple of 64): the same memory as {64, K, N / 64, batch} with box
+// {64, 64, 2, 1}, i.e. both boxes of a stage in one copy (the TMA unit works through copies one after the
+// other, and two 8 KiB copies per stage were what the MMAs waited for).  map_out: the output, dimensions {N, rows, batch}, box {128 bytes of columns, 32, 1},
 // 128-byte swizzle (stores clip at the edges of the matrix).
 template <typename TOut, int V>
 __global__ void __launch_bounds__(kThreads, 1)
 spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
-                  const __grid_constant__ CUtensorMap map_out, const int32_t *__restrict__ blk_offsets,
+                  const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_b4, int use_b4,
+                  const int32_t *__restrict__ blk_offsets,
                   const uint2 *__restrict__ blk_entries, int m_tiles, int n_tiles, int k_blocks, uint32_t *status,
                   int32_t *use_dense) {
     if (*use_dense == 0) return;   // the plan kernel chose the gather kernel for this matrix
@@ -206,16 +254,19 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
     const uint32_t bar_acc_full = base + Smem::kBarAccFull;
     const uint32_t bar_acc_empty = base + Smem::kBarAccEmpty;
 
+    for (int i = t; i < kAStages * kAStageBytes / 16; i += kThreads)   // the A slots start out as zeros
+        reinterpret_cast<uint4 *>(sm + Smem::kA)[i] = make_uint4(0, 0, 0, 0);
     if (t == 0) {
-        for (int s = 0; s < kStages; ++s) {
-            tc::mbar_init(bar_full + 8 * s, kFillPerSlot);   // one arrival per fill warp (+ the bytes of B)
-            tc::mbar_init(bar_empty + 8 * s, kMmaWarps);     // one commit per MMA-issuing thread
+        for (int s = 0; s < kBStages; ++s) {
+            tc::mbar_init(bar_full + 8 * s, kFillPerSlot + 1);   // the fill warps and the loader (+ the bytes of B)
+            tc::mbar_init(bar_empty + 8 * s, kMmaWarps);         // one commit per MMA-issuing thread
         }
         for (int s = 0; s < 2; ++s) {
             tc::mbar_init(bar_acc_full + 8 * s, kMmaWarps);
             tc::mbar_init(bar_acc_empty + 8 * s, kEpiWarps * 32);
         }
         *abort_flag = 0;
+        *reinterpret_cast<volatile uint32_t *>(sm + Smem::kLoaderProgress) = 0;
         tc::fence_mbar_init();
     }
     if (warp == kMmaWarp) {
@@ -234,35 +285,40 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
     const uint32_t total_stages = my_items * (uint32_t)k_blocks;
     const int m_rows = p.m_vec * V;
 
-    if (warp >= kFillWarp0 && warp < kMmaWarp) {
+    // Stage g of this CTA (item g / k_blocks, column block g % k_blocks) uses A slot g % kAStages, B slot
+    // g % kBStages and the barrier pair of its B slot: `full` collects the four fill warps, the loader's arrival
+    // and the bytes of B; `empty` the two MMA threads' commits.  A fill warp waits for the stage kAStages before
+    // its own, so it sees every phase of the two barriers it alternates between.
+    if (warp >= kFillWarp0 && warp < kLoadWarp) {
         // =========================== fill ================================================================
         const int fw = warp - kFillWarp0;
-        const uint32_t slot = (uint32_t)(fw % kStages);
-        const int part = fw / kStages;                     // rows 128 * part .. + 127 of the tile
-        uint8_t *a_part = sm + Smem::kA + slot * kAStageBytes + part * (kGroupRows * kBlockK * 2);
-        const uint32_t bar = bar_full + 8 * slot;
+        const uint32_t a_slot = (uint32_t)(fw % kAStages);
+        const int bucket = fw / kAStages;                  // 0..3
+        const int half = bucket >> 1;                      // rows 128 * half .. + 127 of the tile
+        const int khalf = bucket & 1;                      // columns 32 * khalf .. + 31 of the stage
+        uint8_t *a_part = sm + Smem::kA + a_slot * kAStageBytes + half * (kGroupRows * kBlockK * 2);
+        const int plan_blocks = 2 * k_blocks;
 
-        // Software pipeline over this warp's stages (slot, slot + 4, ...): bucket bounds two stages ahead, the
-        // first 128 entries one stage ahead, their values before the wait for the slot.
-        struct Pos { int b, n0, tn, mt, kb; bool valid; };
-        auto locate = [&](uint32_t g) {
+        // Software pipeline over this warp's stages (a_slot, a_slot + 3, ...): bucket bounds two stages ahead,
+        // the first 64 entries one stage ahead, their values before the wait for the slot.
+        struct Pos { int b, mt, kb; bool valid; };
+        StageIter walk;
+        walk.init(a_slot, total_stages, m_tiles, n_tiles, k_blocks);
+        auto locate = [&]() {   // the walker's position, then kAStages further on
             Pos q;
-            q.valid = g < total_stages;
-            const uint32_t i = q.valid ? g / (uint32_t)k_blocks : 0u;
-            q.kb = q.valid ? (int)(g - i * (uint32_t)k_blocks) : 0;
-            const Item it = decode_item(blockIdx.x + (int64_t)i * G, m_tiles, n_tiles, p.N);
-            q.b = it.b; q.n0 = it.n0; q.tn = it.tn; q.mt = it.mt;
+            q.valid = walk.valid(); q.b = walk.b; q.mt = walk.mt; q.kb = walk.kb;
+            walk.advance(kAStages);
             return q;
         };
         auto bounds = [&](const Pos &q, int &e0, int &e1) {
             e0 = 0; e1 = 0;
             if (q.valid) {
-                const int32_t *o = blk_offsets + ((int64_t)q.mt * kFillPerSlot + part) * (k_blocks + 1) + q.kb;
+                const int32_t *o = blk_offsets + ((int64_t)q.mt * (kTileM / kGroupRows) + half) * (plan_blocks + 1) + 2 * q.kb + khalf;
                 e0 = __ldg(o);
                 e1 = __ldg(o + 1);
             }
         };
-        Pos cur = locate(slot), nxt = locate(slot + kStages);
+        Pos cur = locate(), nxt = locate();
         int c_e0, c_e1, n_e0, n_e1;
         bounds(cur, c_e0, c_e1);
         bounds(nxt, n_e0, n_e1);
@@ -272,11 +328,13 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
             const int e = c_e0 + lane + 32 * u;
             c_ent[u] = e < c_e1 ? __ldg(blk_entries + e) : make_uint2(0u, 0u);
         }
+        int p_e0 = 0, p_e1 = 0;            // the bucket this warp dropped into the slot last time
+        uint32_t p_pos[kFillBatches] = {};
         bool ok_run = true;
         VS_PROF_T0();
-        for (uint32_t g = slot; g < total_stages && ok_run; g += kStages) {
+        for (uint32_t g = a_slot; g < total_stages && ok_run; g += kAStages) {
             const __half *vals = static_cast<const __half *>(p.values) + (int64_t)cur.b * p.stride_values;
-            // values of the first 128 entries, entries of the next stage, bounds of the one after: all in flight
+            // values of the first 64 entries, entries of the next stage, bounds of the one after: all in flight
             // while this warp waits for its slot
             ValueVec<V> c_val[kFillBatches];
 #pragma unroll
@@ -288,40 +346,47 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                 const int e = n_e0 + lane + 32 * u;
                 n_ent[u] = e < n_e1 ? __ldg(blk_entries + e) : make_uint2(0u, 0u);
             }
-            const Pos nn = locate(g + 2 * kStages);
+            const Pos nn = locate();
             int nn_e0, nn_e1;
             bounds(nn, nn_e0, nn_e1);
 
-            const uint32_t use = g / kStages;
-            if (use > 0) ok_run = wait_or_abort<kSleepFill>(bar_empty + 8 * slot, (use - 1u) & 1u, abort_flag);
-            if (!ok_run) break;
-            VS_PROF_ADD(0);   // fill: prefetch issue + wait for the slot
-            if (part == 0 && lane == 0) {   // the stage's rows of B: one 64 x 64 box per 64 columns of the tile
-                const int slabs = (cur.tn + 63) >> 6;
-                tc::mbar_expect_tx_only(bar, (uint32_t)slabs * kBSlabBytes);
-                for (int s = 0; s < slabs; ++s)
-                    tc::tma_load_3d(base + Smem::kB + slot * kBStageBytes + s * kBSlabBytes, &map_b, bar, cur.n0 + 64 * s,
-                                    cur.kb * kBlockK, cur.b);
+            if (g >= (uint32_t)kAStages) {   // the stage that used this A slot before must have been multiplied
+                const uint32_t prev = g - kAStages;
+                ok_run = wait_or_abort<kSleepFill>(bar_empty + 8 * (prev % kBStages), (prev / kBStages) & 1u, abort_flag);
             }
-            // zero this warp's 16 KiB of the A stage, then drop the nonzeros in
+            if (!ok_run) break;
+            if (bucket == 0 && lane == 0) VS_TRACE(0, g);   // A slot free
+            VS_PROF_ADD(0);   // fill: prefetch issue + wait for the slot
+            // The A slots start out as zeros; a slot is brought back to zeros by overwriting exactly the vectors
+            // this warp dropped into it for the stage before (kAStages earlier), which costs a few stores
+            // instead of 8 KiB of them: shared-memory bandwidth is what bounds this kernel.
+            {
+                typename ValueVec<V>::Raw zero{};
 #pragma unroll
-            for (int i = 0; i < (kGroupRows * kBlockK * 2) / (32 * 16); ++i)
-                reinterpret_cast<uint4 *>(a_part)[i * 32 + lane] = make_uint4(0, 0, 0, 0);
+                for (int u = 0; u < kFillBatches; ++u)
+                    if (p_e0 + lane + 32 * u < p_e1) scatter_vector<V>(a_part, p_pos[u], zero);
+                for (int e = p_e0 + 32 * kFillBatches + lane; e < p_e1; e += 32)
+                    scatter_vector<V>(a_part, __ldg(blk_entries + e).y, zero);
+            }
             __syncwarp();
-            VS_PROF_ADD(1);   // fill: B loads + zero fill
+            VS_PROF_ADD(1);   // fill: clear the previous stage's vectors
 #pragma unroll
             for (int u = 0; u < kFillBatches; ++u)
-                if (c_e0 + lane + 32 * u < c_e1)
-                    scatter_vector<V>(a_part, c_ent[u].y, c_val[u].raw);
+                if (c_e0 + lane + 32 * u < c_e1) scatter_vector<V>(a_part, c_ent[u].y, c_val[u].raw);
             for (int e = c_e0 + 32 * kFillBatches + lane; e < c_e1; e += 32) {   // buckets with more entries (denser rows)
                 const uint2 ent = __ldg(blk_entries + e);
                 ValueVec<V> val;
                 val.load(vals + (int64_t)ent.x * V);
                 scatter_vector<V>(a_part, ent.y, val.raw);
             }
+            p_e0 = c_e0; p_e1 = c_e1;
+#pragma unroll
+            for (int u = 0; u < kFillBatches; ++u) p_pos[u] = c_ent[u].y;
             tc::fence_proxy_async();   // the tile was written by ordinary stores; the MMA reads through the async proxy
             __syncwarp();
-            if (lane == 0) tc::mbar_arrive(bar);
+            if (lane == 0) tc::mbar_arrive(bar_full + 8 * (g % kBStages));
+            if (bucket == 0 && lane == 0) VS_TRACE(1, g);   // A part filled
+            if (bucket > 0 && lane == 0) VS_TRACE(9 + bucket, g);
 
             cur = nxt; c_e0 = n_e0; c_e1 = n_e1;
 #pragma unroll
@@ -330,6 +395,66 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
             VS_PROF_ADD(2);   // fill: scatter, arrive
         }
         VS_PROF_FLUSH(0);
+    } else if (warp == kLoadWarp) {
+        // =========================== B loader ============================================================
+        // One thread keeps up to kBStages tiles of B in flight: one 64 x 64 box per 64 columns of the item.
+        if (lane == 0) {
+            volatile uint32_t *progress = reinterpret_cast<volatile uint32_t *>(sm + Smem::kLoaderProgress);
+            uint32_t g = 0;
+            bool ok_run = true;
+            for (uint32_t i = 0; i < my_items && ok_run; ++i) {
+                const Item it = decode_item(blockIdx.x + (int64_t)i * G, m_tiles, n_tiles, p.N);
+                const int slabs = (it.tn + 63) >> 6;
+                for (int kb = 0; kb < k_blocks && ok_run; ++kb, ++g) {
+                    const uint32_t slot = g % kBStages;
+                    if (g >= (uint32_t)kBStages)
+                        ok_run = wait_or_abort<kSleepFill>(bar_empty + 8 * slot, ((g / kBStages) - 1u) & 1u, abort_flag);
+                    if (!ok_run) break;
+                    const uint32_t bar = bar_full + 8 * slot;
+                    VS_TRACE(2, g);   // B slot free, loads issued
+                    tc::mbar_expect_tx(bar, (uint32_t)slabs * kBSlabBytes);   // arrives and arms the byte count
+                    if (use_b4 && slabs == kTileN / 64) {   // both boxes with one instruction
+#ifdef VS_EXP_SAMEB
+                        tc::tma_load_4d(base + Smem::kB + slot * kBStageBytes, &map_b4, bar, 0, 0, 0, blockIdx.x & 63);
+#else
+                        tc::tma_load_4d(base + Smem::kB + slot * kBStageBytes, &map_b4, bar, 0, kb * kBlockK, it.n0 >> 6, it.b);
+#endif
+                    } else {
+                        for (int s = 0; s < slabs; ++s)
+                            tc::tma_load_3d(base + Smem::kB + slot * kBStageBytes + s * kBSlabBytes, &map_b, bar, it.n0 + 64 * s,
+                                            kb * kBlockK, it.b);
+                    }
+                    *progress = g + 1;
+                }
+            }
+        }
+    } else if (warp == kPrefetchWarp) {
+        // =========================== L2 prefetch =========================================================
+        // First touches of B come from DRAM, a latency the ring of six stages does not cover, and prefetches
+        // through the TMA queue would hold up the loads queued behind them.  This warp asks each tile into L2
+        // with plain prefetches about one work item before the loader wants it, paced by the loader's counter.
+        volatile uint32_t *progress = reinterpret_cast<volatile uint32_t *>(sm + Smem::kLoaderProgress);
+        const __half *rhs = static_cast<const __half *>(p.rhs);
+        uint32_t g = (uint32_t)k_blocks;   // the stage being prefetched
+        bool ok_run = true;
+        for (uint32_t i = 1; i < my_items && ok_run; ++i) {
+            const Item it = decode_item(blockIdx.x + (int64_t)i * G, m_tiles, n_tiles, p.N);
+            const __half *b_tile = rhs + (int64_t)it.b * p.stride_rhs + it.n0;
+            for (int kb = 0; kb < k_blocks && ok_run; ++kb, ++g) {
+                const int32_t need = (int32_t)g - k_blocks - 2;   // at most an item and two stages ahead of the loader
+                uint32_t polls = 0;
+                while ((int32_t)*progress < need) {
+                    __nanosleep(200);
+                    if (++polls > (1u << 20) || *abort_flag) { ok_run = false; break; }
+                }
+                if (!ok_run) break;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {   // 64 rows x up to two 128-byte lines
+                    const int r = kb * kBlockK + lane * 2 + (j >> 1), c = (j & 1) * 64;
+                    if (r < p.K && it.n0 + c < p.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(b_tile + (int64_t)r * p.N + c));
+                }
+            }
+        }
     } else if (warp >= kMmaWarp) {
         // =========================== MMA issuers =========================================================
         // Thread h multiplies rows 128 h .. 128 h + 127 of the tile.  Both wait on every stage and both commit
@@ -347,16 +472,20 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                 const Item it = decode_item(blockIdx.x + (int64_t)i * G, m_tiles, n_tiles, p.N);
                 const uint32_t idesc = tc::make_idesc_f16(128, it.tn, 1, 1);   // both operands MN-major
                 const uint32_t buf = i & 1u;
+                if (h == 0) VS_TRACE(8, i);   // item start
                 if (i >= 2) ok_run = wait_or_abort<kSleepMma>(bar_acc_empty + 8 * buf, ((i >> 1) - 1u) & 1u, abort_flag);
+                if (h == 0) VS_TRACE(9, i);   // accumulator free
                 const uint32_t d = tmem_base + buf * kAccCols + (uint32_t)h * kTileN;
                 VS_PROF_ADD(3);   // mma: item decode + wait for the accumulator
                 for (int kb = 0; kb < k_blocks && ok_run; ++kb, ++g) {
-                    const uint32_t slot = g % kStages;
-                    ok_run = wait_or_abort<kSleepMma>(bar_full + 8 * slot, (g / kStages) & 1u, abort_flag);
+                    const uint32_t slot = g % kBStages;
+                    if (h == 0) VS_TRACE(3, g);   // issuer starts waiting for the stage
+                    ok_run = wait_or_abort<kSleepMma>(bar_full + 8 * slot, (g / kBStages) & 1u, abort_flag);
                     if (!ok_run) break;
+                    if (h == 0) VS_TRACE(4, g);   // stage full
                     VS_PROF_ADD(4);   // mma: wait for the stage
                     tc::tc_fence_after_sync();
-                    const uint32_t a_lo = a_lo0 + slot * (kAStageBytes >> 4), b_lo = b_lo0 + slot * (kBStageBytes >> 4);
+                    const uint32_t a_lo = a_lo0 + (g % kAStages) * (kAStageBytes >> 4), b_lo = b_lo0 + slot * (kBStageBytes >> 4);
                     const int n_k16 = min(kBlockK / 16, (p.K - kb * kBlockK + 15) >> 4);
 #pragma unroll
                     for (int kk = 0; kk < kBlockK / 16; ++kk)
@@ -364,6 +493,7 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                             tc::mma_f16_ss(d, tc::desc64(a_lo + 128 * kk, a_hi), tc::desc64(b_lo + 128 * kk, b_hi), idesc,
                                            (kb == 0 && kk == 0) ? 0u : 1u);
                     tc::mma_commit(bar_empty + 8 * slot);
+                    if (h == 0) VS_TRACE(5, g);   // MMAs and commit issued
                     VS_PROF_ADD(5);   // mma: issue
                 }
                 if (ok_run) tc::mma_commit(bar_acc_full + 8 * buf);
@@ -384,6 +514,7 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
             // warp-uniform outcome: tcgen05.ld below needs all 32 lanes
             ok_run = __all_sync(0xffffffffu, wait_or_abort<kSleepEpilogue>(bar_acc_full + 8 * buf, (i >> 1) & 1u, abort_flag));
             if (!ok_run) break;
+            if (t == 0) VS_TRACE(6, i);   // accumulator complete
             VS_PROF_ADD(6);   // epilogue: wait for the accumulator
             tc::tc_fence_after_sync();
             // Each warp moves its 32 rows, 128 bytes of columns at a time, through a 4 KiB box of shared memory
@@ -396,12 +527,11 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                 uint32_t r[kBoxCols];
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * kAccCols + (uint32_t)(half * kTileN + c0);
                 if constexpr (kBoxCols == 64) {
-                    tc::tmem_ld_x32(taddr, reinterpret_cast<uint32_t(&)[32]>(r[0]));
-                    tc::tmem_ld_x32(taddr + 32, reinterpret_cast<uint32_t(&)[32]>(r[32]));
+                    tc::tmem_ld_x64(taddr, r);
                 } else {
                     tc::tmem_ld_x32(taddr, r);
                 }
-                tc::tmem_ld_wait();
+                VS_PROF_ADD(6);
                 if (row0 < m_rows && it.n0 + c0 < p.N) {   // warp-uniform
                     // x * 0 is 0 for a finite x and NaN otherwise: one FMA per element finds a non-finite sum
                     // (every column of the box was written by the MMA: columns past N multiply zero-filled B)
@@ -409,7 +539,6 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
 #pragma unroll
                         for (int e = 0; e < kBoxCols; ++e) finite_probe = fmaf(__uint_as_float(r[e]), 0.0f, finite_probe);
                     }
-                    VS_PROF_ADD(6);
                     if (lane == 0) tc::bulk_wait_group_read<0>();   // the previous store has read the box
                     __syncwarp();
                     VS_PROF_ADD(7);
@@ -429,15 +558,18 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                     }
                     tc::fence_proxy_async();
                     __syncwarp();
+#ifndef VS_EXP_NOSTORE
                     if (lane == 0) {
                         tc::tma_store_3d(&map_out, stg_u32, it.n0 + c0, row0, it.b);
                         tc::bulk_commit_group();
                     }
+#endif
                     VS_PROF_ADD(8);
                 }
             }
             tc::tc_fence_before_sync();
             tc::mbar_arrive(bar_acc_empty + 8 * buf);   // both halves are in registers or stored: the buffer is free
+            if (t == 0) VS_TRACE(7, i);   // accumulator released
         }
         VS_PROF_FLUSH(6);
         // A zero of the densified tile times an Inf or NaN of B is a NaN that the reference, which only reads

@@ -386,7 +386,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) spmm_tc_kernel(const Spm
                 tc::tc_fence_after_sync();
                 uint32_t r[8];
                 tc::tmem_ld_x8(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kAccCols, r);
-                tc::tmem_ld_wait();
                 tc::tc_fence_before_sync();
                 mbar_arrive(bar_acc_empty + 8 * acc);     // the accumulator may be overwritten from here on
 

@@ -432,7 +432,6 @@ spmm_tma_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map, int
                 tc::tc_fence_after_sync();
                 uint32_t r[8];
                 tc::tmem_ld_x8(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kAccCols, r);
-                tc::tmem_ld_wait();
                 tc::tc_fence_before_sync();
                 mbar_arrive(bar_acc_empty + 8 * acc);     // the accumulator may be overwritten from here on
 

@@ -77,7 +77,6 @@ __global__ void __launch_bounds__(128) sandbox_kernel(const uint8_t *image, int 
     for (int c = 0; c < ncols; c += 8) {
         uint32_t r[8];
         tc::tmem_ld_x8(lane_addr + c, r);
-        tc::tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 8; ++i) out[(size_t)t * ncols + c + i] = __uint_as_float(r[i]);
     }

@@ -148,6 +148,23 @@ int make_tile_map(CUtensorMap *map, const void *ptr, bool f32, uint64_t rows, ui
     return r == CUDA_SUCCESS ? VS_OK : VS_ERR_ARG;
 }
 
+// The dense operand of a batch seen as {64 columns, rows, cols / 64 column blocks, batch}: one copy fetches
+// 64 rows of `blocks` neighbouring 64-column blocks, each block landing as its own 64 x 128-byte slab.
+// cols must be a multiple of 64.
+int make_blocked_map(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t cols, uint64_t batch, uint64_t batch_stride,
+                     uint32_t blocks) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return VS_ERR_DEVICE;
+    const cuuint64_t dims[4] = {64, rows, cols / 64, batch};
+    const cuuint64_t strides[3] = {cols * 2, 128, (batch > 1 ? batch_stride : rows * cols) * 2};
+    const cuuint32_t box[4] = {64, 64, blocks, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? VS_OK : VS_ERR_ARG;
+}
+
 // ---- SpMM dispatch ----------------------------------------------------------------------------------------
 template <typename TIn, typename TOut, int V> int launch_spmm_cc(const SpmmParams &p, cudaStream_t s) {
     constexpr int E = Chunk<TIn>::kElems;
@@ -237,15 +254,16 @@ template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStre
     const int k_blocks = (p.K + densespmm::kBlockK - 1) / densespmm::kBlockK;
     const int m_tiles = (p.m_vec * V + densespmm::kTileM - 1) / densespmm::kTileM;
     const int n_tiles = (p.N + densespmm::kTileN - 1) / densespmm::kTileN;
-    const int groups = m_tiles * densespmm::kFillPerSlot;
+    const int groups = m_tiles * (densespmm::kTileM / densespmm::kGroupRows);
+    const int plan_blocks = k_blocks * (densespmm::kBlockK / densespmm::kPlanCols);
     const int rows_per_group = densespmm::kGroupRows / V;
     // entries are addressed like the nonzero vectors: at most one per (vector-row, column), and never more than
     // fit between two matrices of a batch
     int64_t capacity = (int64_t)p.m_vec * p.K;
     if (p.batch > 1 && p.stride_values > 0 && p.stride_values / V < capacity) capacity = p.stride_values / V;
-    const int64_t offsets_bytes = (((int64_t)groups * (k_blocks + 1) * 4) + 15) & ~15ll;
+    const int64_t offsets_bytes = (((int64_t)groups * (plan_blocks + 1) * 4) + 15) & ~15ll;
     const int64_t plan_bytes = 16 + offsets_bytes + capacity * 8;
-    const size_t plan_smem = (size_t)(2 * k_blocks + rows_per_group + 1) * 4;
+    const size_t plan_smem = (size_t)(2 * plan_blocks + rows_per_group + 1) * 4;
     const bool dense_ok = mode != SpmmMode::kGather && p.K > 0 && p.m_vec > 0 && p.N % 8 == 0 && plan_bytes <= kMaxPlanBytes &&
                           plan_smem <= 40 * 1024 && (p.batch == 1 || (p.stride_rhs * 2) % 16 == 0) &&
                           (p.batch == 1 || (p.stride_out * sizeof(TOut)) % 16 == 0) && aligned16(p.rhs) && aligned16(p.out);
@@ -257,6 +275,9 @@ template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStre
         make_tile_map(&map_out, p.out, kOutF32, (uint64_t)p.m_vec * V, (uint64_t)p.N, (uint64_t)p.batch,
                       (uint64_t)p.stride_out, 128 / sizeof(TOut), 32) != VS_OK)
         return launch_spmm_gather<TOut, V>(p, s, d, nullptr);
+    CUtensorMap map_b4 = map;
+    const int use_b4 = (p.N % 64 == 0 && make_blocked_map(&map_b4, p.rhs, (uint64_t)p.K, (uint64_t)p.N, (uint64_t)p.batch,
+                                                          (uint64_t)p.stride_rhs, densespmm::kTileN / 64) == VS_OK) ? 1 : 0;
     auto kernel = densespmm::spmm_dense_kernel<TOut, V>;
     rc = set_smem(kernel, densespmm::kSmemBytes);
     if (rc != VS_OK) return rc;
@@ -268,11 +289,11 @@ template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStre
     uint2 *blk_entries = reinterpret_cast<uint2 *>(plan + 16 + offsets_bytes);
     const float threshold = mode == SpmmMode::kDense ? 0.0f : kDenseDensityPerV * V;
     densespmm::dense_plan_kernel<<<groups, densespmm::kPlanThreads, plan_smem, s>>>(
-        p.row_offsets, p.col_indices, p.m_vec, p.K, rows_per_group, k_blocks, blk_offsets, blk_entries, capacity, threshold,
+        p.row_offsets, p.col_indices, p.m_vec, p.K, rows_per_group, plan_blocks, blk_offsets, blk_entries, capacity, threshold,
         flag);
     const int64_t items = (int64_t)p.batch * n_tiles * m_tiles;
     const unsigned grid = (unsigned)(items < d->sm_count ? items : d->sm_count);   // one persistent CTA per SM
-    kernel<<<grid, densespmm::kThreads, densespmm::kSmemBytes, s>>>(p, map, map_out, blk_offsets, blk_entries, m_tiles,
+    kernel<<<grid, densespmm::kThreads, densespmm::kSmemBytes, s>>>(p, map, map_out, map_b4, use_b4, blk_offsets, blk_entries, m_tiles,
                                                                     n_tiles, k_blocks, d->status, flag);
     rc = (int)cudaGetLastError();
     if (rc == VS_OK) rc = launch_spmm_gather<TOut, V>(p, s, d, flag);
@@ -706,9 +727,9 @@ VS_EXPORT int vs_debug_prof(unsigned long long *out16) {
 #endif
 
 #ifdef VS_TC_PROFILE
-VS_EXPORT int vs_debug_trace(long long *out_12x2048) {
+VS_EXPORT int vs_debug_trace(long long *out_16x2048) {
     VS_CUDA_TRY(cudaDeviceSynchronize());
-    VS_CUDA_TRY(cudaMemcpyFromSymbol(out_12x2048, vs::g_trace, sizeof(long long) * 12 * 2048));
+    VS_CUDA_TRY(cudaMemcpyFromSymbol(out_16x2048, vs::g_trace, sizeof(long long) * 16 * 2048));
     return VS_OK;
 }
 #endif
