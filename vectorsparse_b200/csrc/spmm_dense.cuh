@@ -19,13 +19,12 @@
 //
 // Organisation: one persistent CTA per SM.  Work items are (batch, 128-column tile of B, 256-row tile of A),
 // consecutive CTAs taking consecutive row tiles of the same B so that it stays in L2.  A stage is one 64-wide
-// block of A's columns: 32 KiB of A (two 128-row MMA operands, ring of three) + 16 KiB of B (ring of six: its
-// loads are what has latency to hide).
+// block of A's columns: 32 KiB of A (two 128-row MMA operands) + 16 KiB of B, four of each in a ring.
 //   warps 0-7    epilogue: TMEM -> registers -> swizzled shared-memory boxes -> TMA stores of whole rows
-//   warps 8-19   fill: four warps per A slot, one per plan bucket (128 rows x 32 columns) of the stage
-//   warp 20      one thread issuing the B loads, up to six stages ahead
-//   warp 21      L2 prefetch of the next item's part of B
-//   warps 22-23  one MMA-issuing thread per 128-row half of the tile
+//   warps 8-23   fill: four warps per A slot, one per plan bucket (128 rows x 32 columns) of the stage
+//   warp 24      one thread issuing the B loads, up to four stages ahead
+//   warp 25      L2 prefetch of the next item's part of B
+//   warps 26-27  one MMA-issuing thread per 128-row half of the tile
 // Accumulators: 2 halves x 128 columns, double buffered (all 512 TMEM columns), so the epilogue of one item
 // overlaps the MMAs of the next.  Every wait is bounded; a wait that runs out raises the CTA's abort flag, all
 // roles fall through to the end, a status bit is set and tensor memory is freed.
@@ -43,24 +42,31 @@ constexpr int kTileN = 128;                              // columns of B per wor
 constexpr int kBlockK = 64;                              // columns of A (rows of B) per stage
 constexpr int kGroupRows = 128;                          // rows per plan bucket: one MMA operand
 constexpr int kPlanCols = 32;                            // columns per plan bucket: half a stage
-constexpr int kAStages = 3;                              // ring of densified A tiles
-constexpr int kBStages = 6;                              // ring of B tiles: deeper, their loads have the latency to hide
+constexpr int kAStages = 4;                              // ring of densified A tiles
+constexpr int kBStages = 4;                              // ring of B tiles: deeper, their loads have the latency to hide
 constexpr int kEpiWarps = 8;                             // warps 0..7: TMEM lane quarter = warp % 4, half of the tile = warp / 4
 constexpr int kFillWarp0 = kEpiWarps;
 constexpr int kFillPerSlot = (kTileM / kGroupRows) * (kBlockK / kPlanCols);   // 4: one warp per plan bucket of a stage
-constexpr int kFillWarps = kAStages * kFillPerSlot;      // 12: warp f fills A slot f % kAStages, bucket f / kAStages
+constexpr int kFillWarps = kAStages * kFillPerSlot;      // 16: warp f fills A slot f % kAStages, bucket f / kAStages
 constexpr int kFillBatches = 2;                          // entries a fill warp keeps in flight: 2 x 32
-constexpr int kLoadWarp = kFillWarp0 + kFillWarps;       // 20: one thread issues the B loads
-constexpr int kPrefetchWarp = kLoadWarp + 1;             // 21: asks the next item's rows of B into L2
-constexpr int kMmaWarp = kPrefetchWarp + 1;              // 22, 23
-constexpr int kMmaWarps = kTileM / 128;                  // 2
-constexpr int kThreads = (kMmaWarp + kMmaWarps) * 32;    // 768
+constexpr int kLoadWarp = kFillWarp0 + kFillWarps;       // 24: one thread issues the B loads
+constexpr int kPrefetchWarp = kLoadWarp + 1;             // 25: asks the next item's rows of B into L2
+constexpr int kMmaWarp = kPrefetchWarp + 1;              // 26, 27
+constexpr int kHalves = kTileM / 128;                    // 2 MMA operands of 128 rows
+#ifndef VS_DENSE_KSPLIT
+#define VS_DENSE_KSPLIT 1
+#endif
+constexpr int kKSplit = VS_DENSE_KSPLIT;                               // issuing threads per half (each takes 4 / kKSplit K steps of a stage)
+constexpr int kMmaWarps = kKSplit * kHalves;
+constexpr bool kZeroedAcc = kKSplit > 1;                 // accumulators handed back zeroed: MMA order free between threads
+constexpr int kThreads = (kMmaWarp + kMmaWarps) * 32;    // 896
 constexpr int kAStageBytes = kTileM * kBlockK * 2;       // 32 KiB
 constexpr int kBSlabBytes = kBlockK * 64 * 2;            // 8 KiB: 64 rows of B x 64 columns
 constexpr int kBStageBytes = (kTileN / 64) * kBSlabBytes;  // 16 KiB
-constexpr int kAccCols = kMmaWarps * kTileN;             // 256 TMEM columns per accumulator buffer
+constexpr int kAccCols = kHalves * kTileN;               // 256 TMEM columns per accumulator buffer
 constexpr int kTmemCols = 2 * kAccCols;                  // 512
-constexpr int kStoreBoxBytes = 32 * 128;                 // output box of one epilogue warp: 32 rows x 128 bytes
+constexpr int kStoreCols = 32;                           // output box of one epilogue warp: 32 rows x 32 columns
+constexpr int kStoreBoxBytes = 32 * 128;                 // staging per epilogue warp: two fp16 boxes or one fp32 box
 constexpr int kPlanThreads = 256;
 
 constexpr uint32_t kStatusTimeout = 64u;  // bit raised in the status word when a bounded wait ran out
@@ -81,7 +87,8 @@ struct Smem {  // offsets from the 1024-byte aligned base
 constexpr int kSmemBytes = Smem::kTotal + 1024;  // + slack for the manual 1024-byte alignment
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 static_assert(kFillWarps % kAStages == 0, "each ring slot needs fixed owner warps");
-static_assert(kBStages == 2 * kAStages, "the stage barriers are shared: an A slot is reused every other turn of the B ring");
+static_assert(kBStages == kAStages || kBStages == 2 * kAStages,
+              "the stage barriers are shared: a fill warp must see every phase of the barriers it waits on");
 
 // ---- plan -------------------------------------------------------------------------------------------------
 // One CTA per 128-row group (128 / V vector-rows, whose nonzero vectors are contiguous in the CVSE arrays).
@@ -156,7 +163,10 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
     *abort_flag = 1;
     return false;
 }
-constexpr int kSleepFill = 100, kSleepMma = 0, kSleepEpilogue = 100;
+#ifndef VS_DENSE_SLEEP
+#define VS_DENSE_SLEEP 32
+#endif
+constexpr int kSleepFill = VS_DENSE_SLEEP, kSleepMma = 0, kSleepEpilogue = VS_DENSE_SLEEP;
 
 // Work item w of the launch -> (batch entry, column tile, row tile).
 struct Item {
@@ -230,8 +240,8 @@ template <> struct ValueVec<1> { typedef unsigned short Raw; unsigned short raw;
 // map_b: 3-D tensor map of the dense operand, dimensions {N, K, batch}, box {64, 64, 1}, 128-byte swizzle,
 // zero fill outside.  map_b4 (used when N is a multiple of 64): the same memory as {64, K, N / 64, batch} with box
 // {64, 64, 2, 1}, i.e. both boxes of a stage in one copy (the TMA unit works through copies one after the
-// other, and two 8 KiB copies per stage were what the MMAs waited for).  map_out: the output, dimensions {N, rows, batch}, box {128 bytes of columns, 32, 1},
-// 128-byte swizzle (stores clip at the edges of the matrix).
+// other, and two 8 KiB copies per stage were what the MMAs waited for).  map_out: the output, dimensions {N, rows, batch}, box {32, 32, 1}, swizzle span =
+// the 64 (fp16) or 128 (fp32) bytes of a box row (stores clip at the edges of the matrix).
 template <typename TOut, int V>
 __global__ void __launch_bounds__(kThreads, 1)
 spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
@@ -414,11 +424,7 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                     VS_TRACE(2, g);   // B slot free, loads issued
                     tc::mbar_expect_tx(bar, (uint32_t)slabs * kBSlabBytes);   // arrives and arms the byte count
                     if (use_b4 && slabs == kTileN / 64) {   // both boxes with one instruction
-#ifdef VS_EXP_SAMEB
-                        tc::tma_load_4d(base + Smem::kB + slot * kBStageBytes, &map_b4, bar, 0, 0, 0, blockIdx.x & 63);
-#else
                         tc::tma_load_4d(base + Smem::kB + slot * kBStageBytes, &map_b4, bar, 0, kb * kBlockK, it.n0 >> 6, it.b);
-#endif
                     } else {
                         for (int s = 0; s < slabs; ++s)
                             tc::tma_load_3d(base + Smem::kB + slot * kBStageBytes + s * kBSlabBytes, &map_b, bar, it.n0 + 64 * s,
@@ -457,43 +463,51 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
         }
     } else if (warp >= kMmaWarp) {
         // =========================== MMA issuers =========================================================
-        // Thread h multiplies rows 128 h .. 128 h + 127 of the tile.  Both wait on every stage and both commit
-        // to its `empty` barrier, so each has seen every earlier use of a slot complete.
+        // Thread (h, j) multiplies rows 128 h .. 128 h + 127 of the tile for its share j of every stage's K
+        // steps.  With one thread per half (the shipped configuration) the first MMA of an item overwrites the
+        // accumulator.  With more (VS_DENSE_KSPLIT = 2) every MMA accumulates onto accumulators the epilogue
+        // hands back zeroed, because the order in which the threads' MMAs reach the pipe is then free; it also
+        // varies from run to run, and with it the last bits of the sums.  All threads wait on every stage and
+        // commit to its `empty` barrier, so each has seen every earlier use of a slot complete.
         if (lane == 0) {
-            const int h = warp - kMmaWarp;
-            const uint32_t a_lo0 = tc::smem_desc_lo(base + Smem::kA + h * (128 * kBlockK * 2), 8192);   // 64-row atoms 8 KiB apart
+            constexpr int kSteps = (kBlockK / 16) / kKSplit;   // K steps of a stage per thread
+            const int h = (warp - kMmaWarp) / kKSplit, j = (warp - kMmaWarp) % kKSplit;
+            const uint32_t a_lo0 = tc::smem_desc_lo(base + Smem::kA + h * (128 * kBlockK * 2), 8192) + 128u * kSteps * j;   // 64-row atoms 8 KiB apart
             const uint32_t a_hi = tc::smem_desc_hi(1024, (uint32_t)tc::kSwizzle128B);
-            const uint32_t b_lo0 = tc::smem_desc_lo(base + Smem::kB, kBSlabBytes);
+            const uint32_t b_lo0 = tc::smem_desc_lo(base + Smem::kB, kBSlabBytes) + 128u * kSteps * j;   // this thread's first K step
             const uint32_t b_hi = tc::smem_desc_hi(1024, (uint32_t)tc::kSwizzle128B);
-            uint32_t g = 0;
+            uint32_t a_slot = 0, b_slot = 0, b_parity = 0;
             bool ok_run = true;
             VS_PROF_T0();
             for (uint32_t i = 0; i < my_items && ok_run; ++i) {
                 const Item it = decode_item(blockIdx.x + (int64_t)i * G, m_tiles, n_tiles, p.N);
                 const uint32_t idesc = tc::make_idesc_f16(128, it.tn, 1, 1);   // both operands MN-major
                 const uint32_t buf = i & 1u;
-                if (h == 0) VS_TRACE(8, i);   // item start
-                if (i >= 2) ok_run = wait_or_abort<kSleepMma>(bar_acc_empty + 8 * buf, ((i >> 1) - 1u) & 1u, abort_flag);
-                if (h == 0) VS_TRACE(9, i);   // accumulator free
+                if (warp == kMmaWarp) VS_TRACE(8, i);   // item start
+                ok_run = wait_or_abort<kSleepMma>(bar_acc_empty + 8 * buf, (i >> 1) & 1u, abort_flag);   // zeroed and free
+                if (warp == kMmaWarp) VS_TRACE(9, i);   // accumulator free
+                tc::tc_fence_after_sync();
                 const uint32_t d = tmem_base + buf * kAccCols + (uint32_t)h * kTileN;
                 VS_PROF_ADD(3);   // mma: item decode + wait for the accumulator
-                for (int kb = 0; kb < k_blocks && ok_run; ++kb, ++g) {
-                    const uint32_t slot = g % kBStages;
-                    if (h == 0) VS_TRACE(3, g);   // issuer starts waiting for the stage
-                    ok_run = wait_or_abort<kSleepMma>(bar_full + 8 * slot, (g / kBStages) & 1u, abort_flag);
+                int k_left = p.K - 16 * kSteps * j;   // columns of A from this thread's first K step on
+                for (int kb = 0; kb < k_blocks && ok_run; ++kb, k_left -= kBlockK) {
+                    if (warp == kMmaWarp) VS_TRACE(3, i * k_blocks + kb);   // issuer starts waiting for the stage
+                    ok_run = wait_or_abort<kSleepMma>(bar_full + 8 * b_slot, b_parity, abort_flag);
                     if (!ok_run) break;
-                    if (h == 0) VS_TRACE(4, g);   // stage full
+                    if (warp == kMmaWarp) VS_TRACE(4, i * k_blocks + kb);   // stage full
                     VS_PROF_ADD(4);   // mma: wait for the stage
                     tc::tc_fence_after_sync();
-                    const uint32_t a_lo = a_lo0 + (g % kAStages) * (kAStageBytes >> 4), b_lo = b_lo0 + slot * (kBStageBytes >> 4);
-                    const int n_k16 = min(kBlockK / 16, (p.K - kb * kBlockK + 15) >> 4);
+                    const uint32_t a_lo = a_lo0 + a_slot * (kAStageBytes >> 4), b_lo = b_lo0 + b_slot * (kBStageBytes >> 4);
+                    // 16 columns of A = 16 rows of B = 2 KiB further on in either operand
 #pragma unroll
-                    for (int kk = 0; kk < kBlockK / 16; ++kk)
-                        if (kk < n_k16)   // 16 columns of A = 16 rows of B = 2 KiB further on in either operand
+                    for (int kk = 0; kk < kSteps; ++kk)
+                        if (k_left > 16 * kk)
                             tc::mma_f16_ss(d, tc::desc64(a_lo + 128 * kk, a_hi), tc::desc64(b_lo + 128 * kk, b_hi), idesc,
-                                           (kb == 0 && kk == 0) ? 0u : 1u);
-                    tc::mma_commit(bar_empty + 8 * slot);
-                    if (h == 0) VS_TRACE(5, g);   // MMAs and commit issued
+                                           (kZeroedAcc || kb > 0 || kk > 0) ? 1u : 0u);
+                    tc::mma_commit(bar_empty + 8 * b_slot);
+                    if (warp == kMmaWarp) VS_TRACE(5, i * k_blocks + kb);   // MMAs and commit issued
+                    if (++a_slot == (uint32_t)kAStages) a_slot = 0;
+                    if (++b_slot == (uint32_t)kBStages) { b_slot = 0; b_parity ^= 1u; }
                     VS_PROF_ADD(5);   // mma: issue
                 }
                 if (ok_run) tc::mma_commit(bar_acc_full + 8 * buf);
@@ -502,11 +516,33 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
         }
     } else {
         // =========================== epilogue ============================================================
+        // Warp (quarter, half) owns rows 128 half + 32 quarter .. + 31 of every tile: TMEM lanes 32 quarter ..
+        // of accumulator columns 128 half ..  It moves them out 32 columns at a time: TMEM -> registers -> a box
+        // of shared memory whose 16-byte
+        // chunks are XOR-swizzled by row, so that the row-per-thread writes spread over the banks -> one TMA
+        // store of 32 whole row segments.  fp16 boxes are 2 KiB and alternate between two buffers.
+        constexpr int kBoxBytes = 32 * kStoreCols * (int)sizeof(TOut);       // 2 KiB (fp16) or 4 KiB (fp32)
+        constexpr int kBoxes = kStoreBoxBytes / kBoxBytes;                   // 2 or 1 buffers
+        constexpr int kRowBytes = kStoreCols * (int)sizeof(TOut);            // 64 or 128: also the swizzle span
+        constexpr int kChunks = kRowBytes / 16;                              // 4 or 8 chunks per row
         bool ok_run = true;
-        float finite_probe = 0.0f;
-        const int quarter = warp & 3, half = warp >> 2;   // TMEM lanes 32 * quarter .. + 31; rows 128 * half .. of the tile
+        float finite_probe[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const int quarter = warp & 3, half = warp >> 2;
         uint8_t *stg = sm + Smem::kStaging + warp * kStoreBoxBytes;
         const uint32_t stg_u32 = base + Smem::kStaging + warp * kStoreBoxBytes;
+        const uint32_t lane_taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * kTileN);
+        // the swizzle of a 16-byte chunk index: address bits 4.. XOR address bits 7..
+        const int swz = (kRowBytes == 128) ? (lane & 7) : ((lane >> 1) & 3);
+        uint32_t box_count = 0;
+        // both accumulator buffers start out free (and zeroed, if the MMAs rely on that)
+        if (kZeroedAcc) {
+            for (int c0 = 0; c0 < 2 * kAccCols; c0 += kAccCols)
+                for (int c = 0; c < kTileN; c += 32) tc::tmem_st_zero_x32(lane_taddr + (uint32_t)(c0 + c));
+            tc::tmem_st_wait();
+        }
+        tc::tc_fence_before_sync();
+        tc::mbar_arrive(bar_acc_empty);
+        tc::mbar_arrive(bar_acc_empty + 8);
         VS_PROF_T0();
         for (uint32_t i = 0; i < my_items && ok_run; ++i) {
             const Item it = decode_item(blockIdx.x + (int64_t)i * G, m_tiles, n_tiles, p.N);
@@ -517,34 +553,27 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
             if (t == 0) VS_TRACE(6, i);   // accumulator complete
             VS_PROF_ADD(6);   // epilogue: wait for the accumulator
             tc::tc_fence_after_sync();
-            // Each warp moves its 32 rows, 128 bytes of columns at a time, through a 4 KiB box of shared memory
-            // (the 16-byte chunks XOR-swizzled by row so that the row-per-thread writes spread over the banks)
-            // and lets TMA write them out as whole rows; the box is refilled once the previous store has read it.
-            constexpr int kBoxCols = 128 / (int)sizeof(TOut);   // 64 fp16 or 32 fp32 columns
             const int row0 = it.mt * kTileM + half * 128 + quarter * 32;   // first row of this warp's boxes
 #pragma unroll 1
-            for (int c0 = 0; c0 < it.tn; c0 += kBoxCols) {
-                uint32_t r[kBoxCols];
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * kAccCols + (uint32_t)(half * kTileN + c0);
-                if constexpr (kBoxCols == 64) {
-                    tc::tmem_ld_x64(taddr, r);
-                } else {
-                    tc::tmem_ld_x32(taddr, r);
-                }
-                VS_PROF_ADD(6);
+            for (int c0 = 0; c0 < it.tn; c0 += kStoreCols) {
+                uint32_t r[kStoreCols];
+                const uint32_t taddr = lane_taddr + buf * kAccCols + (uint32_t)c0;
+                tc::tmem_ld_x32(taddr, r);
+                if (kZeroedAcc) tc::tmem_st_zero_x32(taddr);
+                VS_PROF_ADD(7);
                 if (row0 < m_rows && it.n0 + c0 < p.N) {   // warp-uniform
                     // x * 0 is 0 for a finite x and NaN otherwise: one FMA per element finds a non-finite sum
                     // (every column of the box was written by the MMA: columns past N multiply zero-filled B)
                     if (row0 + lane < m_rows) {
 #pragma unroll
-                        for (int e = 0; e < kBoxCols; ++e) finite_probe = fmaf(__uint_as_float(r[e]), 0.0f, finite_probe);
+                        for (int e = 0; e < kStoreCols; ++e) finite_probe[e & 3] = fmaf(__uint_as_float(r[e]), 0.0f, finite_probe[e & 3]);
                     }
-                    if (lane == 0) tc::bulk_wait_group_read<0>();   // the previous store has read the box
+                    const uint32_t box = kBoxes == 2 ? (box_count & 1u) : 0u;
+                    if (lane == 0) tc::bulk_wait_group_read<kBoxes - 1>();   // the store that used this box before has read it
                     __syncwarp();
-                    VS_PROF_ADD(7);
-                    uint8_t *dst = stg + lane * 128;
+                    uint8_t *dst = stg + box * kBoxBytes + lane * kRowBytes;
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {   // eight 16-byte chunks per row
+                    for (int u = 0; u < kChunks; ++u) {
                         uint4 v;
                         if constexpr (sizeof(TOut) == 2) {
                             __half2 *hh = reinterpret_cast<__half2 *>(&v);
@@ -554,21 +583,21 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                         } else {
                             v = make_uint4(r[4 * u], r[4 * u + 1], r[4 * u + 2], r[4 * u + 3]);
                         }
-                        *reinterpret_cast<uint4 *>(dst + ((u ^ (lane & 7)) << 4)) = v;
+                        *reinterpret_cast<uint4 *>(dst + ((u ^ swz) << 4)) = v;
                     }
                     tc::fence_proxy_async();
                     __syncwarp();
-#ifndef VS_EXP_NOSTORE
                     if (lane == 0) {
-                        tc::tma_store_3d(&map_out, stg_u32, it.n0 + c0, row0, it.b);
+                        tc::tma_store_3d(&map_out, stg_u32 + box * kBoxBytes, it.n0 + c0, row0, it.b);
                         tc::bulk_commit_group();
                     }
-#endif
+                    ++box_count;
                     VS_PROF_ADD(8);
                 }
             }
+            if (kZeroedAcc) tc::tmem_st_wait();
             tc::tc_fence_before_sync();
-            tc::mbar_arrive(bar_acc_empty + 8 * buf);   // both halves are in registers or stored: the buffer is free
+            tc::mbar_arrive(bar_acc_empty + 8 * buf);   // read out (and zeroed): the buffer is free
             if (t == 0) VS_TRACE(7, i);   // accumulator released
         }
         VS_PROF_FLUSH(6);
@@ -576,7 +605,8 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
         // the rows of B its nonzeros name, would not produce.  Any non-finite sum hands the call to the gather
         // kernel enqueued behind this one, which then overwrites the output.
         if (lane == 0) tc::bulk_wait_group<0>();   // every store of this warp has reached global memory
-        if (__any_sync(0xffffffffu, finite_probe != 0.0f) && lane == 0) atomicExch(use_dense, 0);
+        const float probe = (finite_probe[0] + finite_probe[1]) + (finite_probe[2] + finite_probe[3]);
+        if (__any_sync(0xffffffffu, probe != 0.0f) && lane == 0) atomicExch(use_dense, 0);
     }
 
     // ---- teardown ---------------------------------------------------------------------------------------

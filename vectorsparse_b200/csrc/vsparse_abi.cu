@@ -131,8 +131,8 @@ int make_gather_map(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t c
 }
 
 // Tensor map of a batch of row-major matrices, dimensions {cols, rows, batch}, for tile loads / stores of
-// box_cols x box_rows elements with the 128-byte swizzle (box_cols * element size = 128); loads read zeros
-// outside the matrix, stores are clipped there.
+// box_cols x box_rows elements, swizzled over the bytes of a box row (128 or 64); loads read zeros outside the
+// matrix, stores are clipped there.
 int make_tile_map(CUtensorMap *map, const void *ptr, bool f32, uint64_t rows, uint64_t cols, uint64_t batch,
                   uint64_t batch_stride, uint32_t box_cols, uint32_t box_rows) {
     EncodeTiledFn fn = encode_tiled_fn();
@@ -142,8 +142,9 @@ int make_tile_map(CUtensorMap *map, const void *ptr, bool f32, uint64_t rows, ui
     const cuuint64_t strides[2] = {cols * es, (batch > 1 ? batch_stride : rows * cols) * es};
     const cuuint32_t box[3] = {box_cols, box_rows, 1};
     const cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+    const CUtensorMapSwizzle swizzle = box_cols * es == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+    CUresult r = fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(ptr), dims,
+                    strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? VS_OK : VS_ERR_ARG;
 }
@@ -273,7 +274,7 @@ template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStre
     CUtensorMap map, map_out;
     if (make_tile_map(&map, p.rhs, false, (uint64_t)p.K, (uint64_t)p.N, (uint64_t)p.batch, (uint64_t)p.stride_rhs, 64, 64) != VS_OK ||
         make_tile_map(&map_out, p.out, kOutF32, (uint64_t)p.m_vec * V, (uint64_t)p.N, (uint64_t)p.batch,
-                      (uint64_t)p.stride_out, 128 / sizeof(TOut), 32) != VS_OK)
+                      (uint64_t)p.stride_out, densespmm::kStoreCols, 32) != VS_OK)
         return launch_spmm_gather<TOut, V>(p, s, d, nullptr);
     CUtensorMap map_b4 = map;
     const int use_b4 = (p.N % 64 == 0 && make_blocked_map(&map_b4, p.rhs, (uint64_t)p.K, (uint64_t)p.N, (uint64_t)p.batch,
