@@ -182,9 +182,11 @@ def test_rejected_arguments_raise():
 
 
 @pytest.mark.parametrize("V", [2, 8])
-def test_software_gather_kernel_for_strides_tma_cannot_address(V):
-    """A batch stride of B that is not a multiple of the dense width cannot be described by one tensor map: the
-    cp.async tensor-core kernel takes over.  Same tolerance; the padding between entries must stay untouched."""
+def test_software_gather_kernel_for_strides_tma_cannot_address(V, monkeypatch):
+    """A batch stride of B that is not a multiple of the dense width cannot be described by the row-gather tensor
+    map: among the gather kernels the cp.async one takes over.  Same tolerance; the padding between entries must
+    stay untouched.  (The densifying kernel, which would otherwise take this density, is switched off.)"""
+    monkeypatch.setenv("VSPARSE_B200_SPMM", "gather")
     N, K, batch = 128, 160, 3
     a = problem(cvse.GEN_BETA, 91 + V, 48, K, V, 0.6)
     vals = cvse.fill_random((a.nnz_vec * V,), np.float16, cvse.DIST_NORMAL, 1, 0.5)
