@@ -219,6 +219,23 @@ struct StageIter {
     }
 };
 
+// The items of this CTA one after the other (blockIdx.x, + gridDim.x, ...), again without divisions per step.
+struct ItemIter {
+    StageIter w;
+    int N;
+    __device__ __forceinline__ void init(int m_tiles, int n_tiles, int N_) {
+        w.init(0u, 0xffffffffu, m_tiles, n_tiles, 1);
+        N = N_;
+    }
+    __device__ __forceinline__ Item get() const {
+        Item it;
+        it.b = w.b; it.mt = w.mt; it.n0 = w.nt * kTileN;
+        it.tn = min(kTileN, (N - it.n0 + 63) & ~63);
+        return it;
+    }
+    __device__ __forceinline__ void next() { w.next_item(); }
+};
+
 // Drops one nonzero vector (`raw`: its V halves) into the fill warp's 128 rows of the A stage at `a_part`.
 // The operand is MN-major (rows of A contiguous) with the 128-byte swizzle: element (row m, column k) of the
 // 128 x 64 block lives at (m / 64) * 8 KiB + (k / 8) * 1 KiB + (k % 8) * 128 + (((m % 64) / 8) ^ (k % 8)) * 16 +
@@ -412,8 +429,10 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
             volatile uint32_t *progress = reinterpret_cast<volatile uint32_t *>(sm + Smem::kLoaderProgress);
             uint32_t g = 0;
             bool ok_run = true;
-            for (uint32_t i = 0; i < my_items && ok_run; ++i) {
-                const Item it = decode_item(blockIdx.x + (int64_t)i * G, m_tiles, n_tiles, p.N);
+            ItemIter items;
+            items.init(m_tiles, n_tiles, p.N);
+            for (uint32_t i = 0; i < my_items && ok_run; ++i, items.next()) {
+                const Item it = items.get();
                 const int slabs = (it.tn + 63) >> 6;
                 for (int kb = 0; kb < k_blocks && ok_run; ++kb, ++g) {
                     const uint32_t slot = g % kBStages;
@@ -443,8 +462,11 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
         const __half *rhs = static_cast<const __half *>(p.rhs);
         uint32_t g = (uint32_t)k_blocks;   // the stage being prefetched
         bool ok_run = true;
+        ItemIter items;
+        items.init(m_tiles, n_tiles, p.N);
         for (uint32_t i = 1; i < my_items && ok_run; ++i) {
-            const Item it = decode_item(blockIdx.x + (int64_t)i * G, m_tiles, n_tiles, p.N);
+            items.next();
+            const Item it = items.get();
             const __half *b_tile = rhs + (int64_t)it.b * p.stride_rhs + it.n0;
             for (int kb = 0; kb < k_blocks && ok_run; ++kb, ++g) {
                 const int32_t need = (int32_t)g - k_blocks - 2;   // at most an item and two stages ahead of the loader
@@ -479,8 +501,11 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
             uint32_t a_slot = 0, b_slot = 0, b_parity = 0;
             bool ok_run = true;
             VS_PROF_T0();
-            for (uint32_t i = 0; i < my_items && ok_run; ++i) {
-                const Item it = decode_item(blockIdx.x + (int64_t)i * G, m_tiles, n_tiles, p.N);
+            ItemIter items;
+            items.init(m_tiles, n_tiles, p.N);
+            bool ready = false;   // whether the next stage was already seen full
+            for (uint32_t i = 0; i < my_items && ok_run; ++i, items.next()) {
+                const Item it = items.get();
                 const uint32_t idesc = tc::make_idesc_f16(128, it.tn, 1, 1);   // both operands MN-major
                 const uint32_t buf = i & 1u;
                 if (warp == kMmaWarp) VS_TRACE(8, i);   // item start
@@ -492,7 +517,7 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                 int k_left = p.K - 16 * kSteps * j;   // columns of A from this thread's first K step on
                 for (int kb = 0; kb < k_blocks && ok_run; ++kb, k_left -= kBlockK) {
                     if (warp == kMmaWarp) VS_TRACE(3, i * k_blocks + kb);   // issuer starts waiting for the stage
-                    ok_run = wait_or_abort<kSleepMma>(bar_full + 8 * b_slot, b_parity, abort_flag);
+                    if (!ready) ok_run = wait_or_abort<kSleepMma>(bar_full + 8 * b_slot, b_parity, abort_flag);
                     if (!ok_run) break;
                     if (warp == kMmaWarp) VS_TRACE(4, i * k_blocks + kb);   // stage full
                     VS_PROF_ADD(4);   // mma: wait for the stage
@@ -508,6 +533,9 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                     if (warp == kMmaWarp) VS_TRACE(5, i * k_blocks + kb);   // MMAs and commit issued
                     if (++a_slot == (uint32_t)kAStages) a_slot = 0;
                     if (++b_slot == (uint32_t)kBStages) { b_slot = 0; b_parity ^= 1u; }
+                    // one look at the next stage's barrier (this CTA's stages follow one another across items):
+                    // its latency passes while the MMAs above are handed to the pipe
+                    ready = (kb + 1 < k_blocks || i + 1 < my_items) && tc::mbar_try_wait(bar_full + 8 * b_slot, b_parity);
                     VS_PROF_ADD(5);   // mma: issue
                 }
                 if (ok_run) tc::mma_commit(bar_acc_full + 8 * buf);
@@ -544,8 +572,10 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
         tc::mbar_arrive(bar_acc_empty);
         tc::mbar_arrive(bar_acc_empty + 8);
         VS_PROF_T0();
-        for (uint32_t i = 0; i < my_items && ok_run; ++i) {
-            const Item it = decode_item(blockIdx.x + (int64_t)i * G, m_tiles, n_tiles, p.N);
+        ItemIter items;
+        items.init(m_tiles, n_tiles, p.N);
+        for (uint32_t i = 0; i < my_items && ok_run; ++i, items.next()) {
+            const Item it = items.get();
             const uint32_t buf = i & 1u;
             // warp-uniform outcome: tcgen05.ld below needs all 32 lanes
             ok_run = __all_sync(0xffffffffu, wait_or_abort<kSleepEpilogue>(bar_acc_full + 8 * buf, (i >> 1) & 1u, abort_flag));
