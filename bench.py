@@ -50,9 +50,22 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from an ncu capture of this
 # command (profiles/ holds the summary it comes from); None until one has been taken for the workload.
 NCU_TRAFFIC_BYTES = {
-    "spmm_v8_s90": 339.8e6,    # profiles/spmm_tma_kernel__spmm_v8_s90.md
+    "spmm_v8_s90": 334.8e6,    # profiles/spmm_dense_kernel__spmm_v8_s90.md
     "sddmm_v8_s90": 380.2e6,   # profiles/sddmm_tma_kernel__sddmm_v8_s90.md
 }
+
+
+def kernels_per_step(w):
+    """Names of the library's kernels one step launches (the count is what `gpu_launches` reports)."""
+    tensor = w.get("path") != 1
+    if w["op"] == "spmm" and tensor:
+        if os.environ.get("VSPARSE_B200_SPMM") == "gather":
+            return ["spmm_tma_kernel"]
+        return ["dense_plan_kernel", "spmm_dense_kernel",
+                "spmm_tma_kernel (returns at once unless the plan kernel chose it)"]
+    if w["op"] == "spmm":
+        return ["spmm_cc_kernel"]
+    return ["sddmm_tma_kernel"] if tensor else ["sddmm_cc_kernel"]
 
 
 def measured_peaks():
@@ -280,7 +293,8 @@ def run_ours(args):
                          "algorithmic_bytes_per_launch": alg_bytes},
             "e2e": {"value": flops * e2e_steps * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
-            "gpu_launches": args.steps,
+            "gpu_launches": args.steps * len(kernels_per_step(w)),
+            "kernels_per_step": kernels_per_step(w),
             "single_launch_latency_us": lat_us,
             "clocks": clocks,
         }

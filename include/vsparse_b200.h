@@ -63,6 +63,16 @@ const char *vs_version(void);
  * vec_length: {2,4,8} on the tensor path, {1,2,4,8} on the CUDA-core path, else VS_ERR_VEC_LENGTH.
  * k (dense width): tensor path needs k % 64 == 0 (as the reference, src/wmma_spmm.cu:327,396); CUDA-core path
  * needs k % 8 == 0 for fp16 and k % 4 == 0 for fp32.  values, rhs, out must be 16-byte aligned.
+ *
+ * Tensor path: two formulations, chosen on the device by the density of the matrix (the signature carries no
+ * nonzero count).  From a density of 0.003 * vec_length upwards, zero-filled 256 x 64 tiles of the sparse
+ * matrix are multiplied with whole tiles of rhs; below it, and whenever that kernel produced a non-finite sum
+ * (0 * Inf from a row of rhs that no nonzero names), one row of rhs is gathered per nonzero vector as in the
+ * reference.  A column index may appear only once per vector-row (as in any CVSE built from a mask).
+ * Environment variable VSPARSE_B200_SPMM = "dense" | "gather" forces one formulation.  The first tensor-path
+ * call on a stream allocates a plan scratch buffer with cudaMallocAsync on that stream (8 bytes per nonzero
+ * vector, bounded by m_vec * n and by 512 MB; reused and grown by later calls on the stream, never freed): make
+ * that call outside stream capture.  Everything else about the call is asynchronous and allocation-free.
  * ---------------------------------------------------------------------------------------------------- */
 int vs_spmm(int path, int in_dtype, int out_dtype, int m_vec, int vec_length, int k, int n,
             const int32_t *row_indices, const int32_t *row_offsets, const int32_t *col_indices,

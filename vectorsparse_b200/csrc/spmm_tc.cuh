@@ -8,9 +8,9 @@
 // a gathered row of B is contiguous along the 128 columns (MMA-M), a value vector is contiguous along V
 // (MMA-N).  The accumulator lives in tensor memory, 16 fp32 columns per work item.
 //
-// Organisation.  One persistent CTA per SM, warp-specialised, no CTA-wide barrier inside a phase:
+// Organisation.  Two persistent CTAs per SM, warp-specialised, no CTA-wide barrier inside a phase:
 //   * 10 producer warps, each owning ONE slot of the shared-memory ring and therefore every 10th stage (a stage
-//     is up to 64 nonzero vectors of one vector-row = up to four K=16 MMAs).  A warp gathers its whole stage:
+//     is up to 32 nonzero vectors of one vector-row = one or two K=16 MMAs).  A warp gathers its whole stage:
 //     cp.async 16-byte chunks of B rows straight into the 128-byte-swizzled operand layout (zero-filled past
 //     the end of a row) and signals the slot's `full` mbarrier with cp.async.mbarrier.arrive, i.e. when the
 //     copies have landed.  Ten stages are therefore being gathered concurrently, and the bookkeeping of a stage
@@ -18,11 +18,11 @@
 //     gathers stage n, so a gather never waits on an index load.
 //   * 1 MMA thread: waits for `full` in ring order, issues the MMAs of the stage and commits them to the slot's
 //     `empty` mbarrier (slot reuse) and, at the end of a row, to `acc_full`.
-//   * 2 x 4 epilogue warps (even / odd work items): wait for `acc_full`, tcgen05.ld their 32 lanes, release the
+//   * 4 epilogue warps: wait for `acc_full`, tcgen05.ld their 32 lanes, release the
 //     accumulator (`acc_empty`), transpose through a warp-private staging tile, write C with 16-byte stores.
 // Work items are (batch, column tile, vector-row in row_indices order), dealt round-robin to the CTAs so that
 // the descending-length order the row swizzle produces becomes a longest-first schedule; each CTA decodes its
-// next 256 items in bulk ("phase") so that no role ever chases row_indices -> row_offsets per item.
+// next 128 items in bulk ("phase") so that no role ever chases row_indices -> row_offsets per item.
 // Every wait is bounded; a wait that runs out raises the CTA's abort flag, all roles leave through the phase
 // barrier, a status bit is set and tensor memory is freed.
 #pragma once
