@@ -217,20 +217,49 @@ def run_ours(args):
     assert ops.device_status() == 0, "a kernel gave up on a bounded wait"
 
     # ---- end-to-end leg: host buffers, copies inside the timed region --------------------------------------
-    def e2e_step():
-        da = h_a.to(dev, non_blocking=True)
-        db = h_b.to(dev, non_blocking=True)
-        launch(da, db, d_out)
-        h_out.copy_(d_out, non_blocking=True)
+    # Every step copies its inputs from pinned host memory, runs the public API call and copies the result back.
+    # The three stages run on three streams over two sets of device buffers, so that step s+1's upload and step
+    # s-1's download overlap step s's kernels (PCIe is full duplex); the time is that of the whole sequence.
+    e2e_steps = 0 if args.kernel_only else max(4, min(args.steps, 10))
+    if e2e_steps:
+        s_in, s_run, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+        bufs = [(torch.empty_like(d_a), torch.empty_like(d_b), torch.empty_like(d_out)) for _ in range(2)]
+        ev_in = [torch.cuda.Event() for _ in range(2)]
+        ev_run = [torch.cuda.Event() for _ in range(2)]
+        ev_out = [torch.cuda.Event() for _ in range(2)]
 
-    e2e_steps = 0 if args.kernel_only else max(2, min(args.steps, 5))
-    for _ in range(2 if e2e_steps else 0):
-        e2e_step()
+    def e2e_sequence(n):
+        for st in (s_in, s_run, s_out):
+            st.wait_stream(torch.cuda.current_stream())
+        for s in range(n):
+            i = s & 1
+            da, db, dout = bufs[i]
+            with torch.cuda.stream(s_in):
+                if s >= 2:
+                    s_in.wait_event(ev_run[i])     # step s-2 has consumed this set of inputs
+                da.copy_(h_a, non_blocking=True)
+                db.copy_(h_b, non_blocking=True)
+                ev_in[i].record(s_in)
+            with torch.cuda.stream(s_run):
+                s_run.wait_event(ev_in[i])
+                if s >= 2:
+                    s_run.wait_event(ev_out[i])    # step s-2's result has left this output buffer
+                launch(da, db, dout)
+                ev_run[i].record(s_run)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_run[i])
+                h_out.copy_(dout, non_blocking=True)
+                ev_out[i].record(s_out)
+        for st in (s_in, s_run, s_out):
+            torch.cuda.current_stream().wait_stream(st)
+
+    if e2e_steps:
+        e2e_sequence(2)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
+    if e2e_steps:
+        e2e_sequence(e2e_steps)
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1) if e2e_steps else float("nan")
