@@ -11,6 +11,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
+#include <algorithm>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -23,6 +24,7 @@
 #include "spmm_dense.cuh"
 #include "sddmm_tc.cuh"
 #include "sddmm_tma.cuh"
+#include "sddmm_dense.cuh"
 #include "tc_selftest.cuh"
 
 #define VS_EXPORT extern "C" __attribute__((visibility("default")))
@@ -343,10 +345,7 @@ template <typename TOut, int V> int launch_sddmm_tc_cpasync(const SddmmParams &p
 
 // TMA row gather: lhs and rhs of all batch entries must each be addressable as one matrix of k-wide rows, i.e.
 // their batch strides are multiples of k (or zero / a single entry).
-template <typename TOut, int V> int launch_sddmm_tc(const SddmmParams &p, cudaStream_t s) {
-    DeviceInfo *d;
-    int rc = device_info(&d);
-    if (rc != VS_OK) return rc;
+template <typename TOut, int V> int launch_sddmm_gather(const SddmmParams &p, cudaStream_t s, DeviceInfo *d) {
     static const bool force_cpasync = []() {
         const char *e = std::getenv("VSPARSE_B200_GATHER");
         return e && !std::strcmp(e, "cpasync");
@@ -364,13 +363,69 @@ template <typename TOut, int V> int launch_sddmm_tc(const SddmmParams &p, cudaSt
         make_gather_map(&map_l, p.lhs, (uint64_t)rows_l, (uint64_t)p.k) != VS_OK)
         return launch_sddmm_tc_cpasync<TOut, V>(p, s, d);
     auto kernel = tmasddmm::sddmm_tma_kernel<TOut, V>;
-    rc = set_smem(kernel, tmasddmm::kSmemBytes);
+    int rc = set_smem(kernel, tmasddmm::kSmemBytes);
     if (rc != VS_OK) return rc;
     const int64_t items = (int64_t)p.batch * p.m_vec;
     const int64_t cap = (int64_t)tmasddmm::kCtasPerSm * d->sm_count;
     const unsigned grid = (unsigned)(items < cap ? items : cap);
     kernel<<<grid, tmasddmm::kThreads, tmasddmm::kSmemBytes, s>>>(p, map_r, map_l, (int)rpb_r, (int)rows_r, (int)rpb_l,
                                                                   (int)rows_l, d->status);
+    return (int)cudaGetLastError();
+}
+
+// Which tensor-core SDDMM runs: dense 256 x 128 tiles of lhs . rhs^T sampled at the mask cost the same whatever
+// the sparsity but at least an epilogue pass per tile; the gather kernel is proportional to the mask entries.
+// The number of entries is an argument here, so the choice is made on the host (cycles per SM, measured):
+// ~7 per mask entry and 64 contraction elements for the gather kernel; per tile, ~800 per 64 contraction
+// elements (operand traffic through L2 included) and not less than ~2500 (the sampling pass) for the dense one.
+// VSPARSE_B200_SDDMM = "dense" | "gather" (read at every call) forces one.
+bool sddmm_use_dense(const SddmmParams &p, int V) {
+    const char *e = std::getenv("VSPARSE_B200_SDDMM");
+    if (e && !std::strcmp(e, "dense")) return true;
+    if (e && !std::strcmp(e, "gather")) return false;
+    const double density = (double)p.nnz_vec / ((double)p.m_vec * (double)p.n);
+    const double entries_per_tile = (double)(densesddmm::kTileM / V) * densesddmm::kTileN * density;
+    const double k_blocks = (double)(p.k / densesddmm::kBlockK);
+    const double gather = entries_per_tile * k_blocks * 7.0;
+    const double dense = std::max(k_blocks * 800.0, 2500.0);
+    return dense * 1.25 < gather;
+}
+
+template <typename TOut, int V> int launch_sddmm_tc(const SddmmParams &p, cudaStream_t s) {
+    DeviceInfo *d;
+    int rc = device_info(&d);
+    if (rc != VS_OK) return rc;
+    const int chunks = (p.n + densesddmm::kChunk - 1) / densesddmm::kChunk;
+    const int64_t offsets_bytes = (((int64_t)p.m_vec * (chunks + 1) * 4) + 15) & ~15ll;
+    const int64_t plan_bytes = offsets_bytes + (int64_t)p.nnz_vec * 8;
+    const size_t plan_smem = (size_t)2 * chunks * 4;
+    const bool dense_ok = p.n > 0 && p.m_vec > 0 && p.nnz_vec > 0 && p.k >= densesddmm::kBlockK && plan_bytes <= kMaxPlanBytes &&
+                          plan_smem <= 40 * 1024 && aligned16(p.lhs) && aligned16(p.rhs) &&
+                          (p.batch == 1 || ((p.stride_lhs * 2) % 16 == 0 && (p.stride_rhs * 2) % 16 == 0)) &&
+                          sddmm_use_dense(p, V);
+    if (!dense_ok) return launch_sddmm_gather<TOut, V>(p, s, d);
+    CUtensorMap map_l, map_r;
+    if (make_tile_map(&map_l, p.lhs, false, (uint64_t)p.m_vec * V, (uint64_t)p.k, (uint64_t)p.batch, (uint64_t)p.stride_lhs, 64,
+                      densesddmm::kTileM) != VS_OK ||
+        make_tile_map(&map_r, p.rhs, false, (uint64_t)p.n, (uint64_t)p.k, (uint64_t)p.batch, (uint64_t)p.stride_rhs, 64,
+                      densesddmm::kTileN) != VS_OK)
+        return launch_sddmm_gather<TOut, V>(p, s, d);
+    auto kernel = densesddmm::sddmm_dense_kernel<TOut, V>;
+    rc = set_smem(kernel, densesddmm::kSmemBytes);
+    if (rc != VS_OK) return rc;
+    uint8_t *plan = nullptr;
+    if (stream_scratch(d, s, (size_t)plan_bytes, reinterpret_cast<void **>(&plan)) != VS_OK)
+        return launch_sddmm_gather<TOut, V>(p, s, d);
+    int32_t *chunk_offsets = reinterpret_cast<int32_t *>(plan);
+    uint2 *chunk_entries = reinterpret_cast<uint2 *>(plan + offsets_bytes);
+    densesddmm::sddmm_plan_kernel<<<p.m_vec, densesddmm::kPlanThreads, plan_smem, s>>>(p.row_offsets, p.col_indices, p.n, chunks,
+                                                                                   chunk_offsets, chunk_entries);
+    const int m_tiles = (p.m_vec * V + densesddmm::kTileM - 1) / densesddmm::kTileM;
+    const int n_tiles = (p.n + densesddmm::kTileN - 1) / densesddmm::kTileN;
+    const int64_t items = (int64_t)p.batch * m_tiles * n_tiles;
+    const unsigned grid = (unsigned)(items < d->sm_count ? items : d->sm_count);   // one persistent CTA per SM
+    kernel<<<grid, densesddmm::kThreads, densesddmm::kSmemBytes, s>>>(p, map_l, map_r, chunk_offsets, chunk_entries, m_tiles,
+                                                                      n_tiles, chunks, d->status);
     return (int)cudaGetLastError();
 }
 
