@@ -55,7 +55,7 @@ NCU_TRAFFIC_BYTES = {
 }
 
 
-def kernels_per_step(w):
+def kernels_per_step(w, a=None):
     """Names of the library's kernels one step launches (the count is what `gpu_launches` reports)."""
     tensor = w.get("path") != 1
     if w["op"] == "spmm" and tensor:
@@ -65,7 +65,11 @@ def kernels_per_step(w):
                 "spmm_tma_kernel (returns at once unless the plan kernel chose it)"]
     if w["op"] == "spmm":
         return ["spmm_cc_kernel"]
-    return ["sddmm_tma_kernel"] if tensor else ["sddmm_cc_kernel"]
+    if not tensor:
+        return ["sddmm_cc_kernel"]
+    from vectorsparse_b200 import _lib
+    dense = a is not None and _lib.lib().vs_sddmm_formulation(a.m_vec, w["N"], w["K"], a.nnz_vec, w["V"]) == 1
+    return ["sddmm_plan_kernel", "sddmm_dense_kernel"] if dense else ["sddmm_tma_kernel"]
 
 
 def measured_peaks():
@@ -322,8 +326,8 @@ def run_ours(args):
                          "algorithmic_bytes_per_launch": alg_bytes},
             "e2e": {"value": flops * e2e_steps * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
-            "gpu_launches": args.steps * len(kernels_per_step(w)),
-            "kernels_per_step": kernels_per_step(w),
+            "gpu_launches": args.steps * len(kernels_per_step(w, a)),
+            "kernels_per_step": kernels_per_step(w, a),
             "single_launch_latency_us": lat_us,
             "clocks": clocks,
         }

@@ -102,6 +102,12 @@ int vs_spmm_batched(int path, int in_dtype, int out_dtype, int m_vec, int vec_le
  * algorithm: 0..3 accepted on the tensor path and all computed by the same kernel — in the reference they are
  * implementation variants of one function, and variant 3 returns deliberately wrong values
  * (src/wmma_sddmm.cu:769-771); here it returns correct ones.  Other values: VS_ERR_ARG.
+ *
+ * Tensor path: two formulations, chosen on the host from nonzeros_vec, the shape and k.  Dense 256 x 128 tiles
+ * of lhs . rhs^T sampled at the mask (denser masks, k >= 128), or one gathered row of rhs per mask entry as in
+ * the reference.  Environment variable VSPARSE_B200_SDDMM = "dense" | "gather" forces one.  The dense
+ * formulation keeps a plan scratch buffer per calling stream exactly as the tensor-path SpMM does (see vs_spmm);
+ * with it, a mask entry whose column lies outside [0, n) is skipped instead of written as zero.
  * ---------------------------------------------------------------------------------------------------- */
 int vs_sddmm(int path, int in_dtype, int out_dtype, int m_vec, int k, int n, int nonzeros_vec,
              const int32_t *row_indices, const int32_t *row_offsets, const int32_t *col_indices,
@@ -178,6 +184,11 @@ int vs_sddmm_host(int path, int in_dtype, int out_dtype, int m_vec, int k, int n
  * device), optionally clearing it.  0 = no kernel ever gave up.
  * ---------------------------------------------------------------------------------------------------- */
 int vs_device_status(int clear, uint32_t *status);
+
+/* Which tensor-path SDDMM formulation vs_sddmm / vs_sddmm_batched would run for this problem: 1 = dense tiles
+ * sampled at the mask, 0 = row gather (environment override included).  Diagnostic, no counterpart in the
+ * reference; lets a benchmark name the kernels it measures.  Needs no device. */
+int vs_sddmm_formulation(int m_vec, int k, int n, int nonzeros_vec, int vec_length);
 
 /* ------------------------------------------------------------------------------------------------------
  * Tensor-core encoding self-test (diagnostic; no counterpart in the reference).  Copies `image_bytes` of a

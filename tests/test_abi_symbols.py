@@ -100,3 +100,18 @@ def test_host_forms_validate_structure_first():
     pv = lambda a: a.ctypes.data_as(C.c_void_p)
     rc = L.vs_spmm_host(_lib.VS_PATH_CUDA_CORE, _lib.VS_F32, _lib.VS_F32, 2, 1, 4, 4, pv(ro), pv(ro), pv(ci), pv(z), pv(z), pv(z))
     assert rc == -6
+
+
+def test_sddmm_formulation_choice(monkeypatch):
+    """Host-side choice between the dense and the gather tensor-core SDDMM: needs no device."""
+    f = _lib.lib().vs_sddmm_formulation
+    monkeypatch.delenv("VSPARSE_B200_SDDMM", raising=False)
+    assert f(256, 256, 512, 12685, 8) == 1        # 90 % sparse, k = 256: dense tiles
+    assert f(256, 256, 512, 600, 8) == 0          # 99.5 % sparse: gather
+    assert f(512, 64, 4096, 209920, 8) == 0       # attention, head dimension 64: the sampling pass would dominate
+    assert f(256, 256, 512, 12685, 1) == 0        # no tensor path at V = 1
+    assert f(0, 256, 512, 0, 8) == 0
+    monkeypatch.setenv("VSPARSE_B200_SDDMM", "dense")
+    assert f(512, 64, 4096, 209920, 8) == 1
+    monkeypatch.setenv("VSPARSE_B200_SDDMM", "gather")
+    assert f(256, 256, 512, 12685, 8) == 0

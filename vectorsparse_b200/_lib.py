@@ -44,6 +44,7 @@ SIGNATURES = {
     "vs_spmm_host": (_i, [_i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "vs_sddmm_host": (_i, [_i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
     "vs_device_status": (_i, [_i, C.POINTER(C.c_uint32)]),
+    "vs_sddmm_formulation": (_i, [_i, _i, _i, _i, _i]),
     "vs_selftest_mma": (_i, [_vp, _i, _vp, _i, C.c_uint32, _i, _f, _vp, _vp]),
     "vs_selftest_gather4": (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _vp]),
     "vs_cvse_validate": (_i, [_i, _i, _i, _vp, _vp]),

@@ -17,8 +17,8 @@
 //   warps 0-7   epilogue: warp (quarter, half) owns 32 rows of the tile.  Per 32 columns: TMEM -> registers ->
 //               a swizzled 32 x 32 fp32 box of shared memory (private to the warp), then every lane walks the
 //               entries of ITS vector-row in that chunk and stores lhs-row x entry values; the V lanes of a
-//               vector-row write V consecutive outputs.  Offsets and the first entries of every chunk are
-//               loaded before the wait for the accumulator.
+//               vector-row write V consecutive outputs.  The bounds of its entries are loaded one item ahead,
+//               the first eight entries of a chunk one chunk ahead, further entries eight at a time.
 //   warp 8      one thread issuing the loads: 32 KiB of lhs and 16 KiB of rhs per stage, four stages in a ring
 //   warps 9-10  one MMA-issuing thread per 128-row half of the tile
 // Accumulators: 2 halves x 128 columns, double buffered (all 512 TMEM columns).  Every wait is bounded; a wait
@@ -48,7 +48,7 @@ constexpr int kBStageBytes = kTileN * kBlockK * 2;       // 16 KiB
 constexpr int kAccCols = kHalves * kTileN;               // 256 TMEM columns per accumulator buffer
 constexpr int kTmemCols = 2 * kAccCols;                  // 512
 constexpr int kBoxBytes = 32 * kChunk * 4;               // 4 KiB: 32 rows x 32 fp32 columns per epilogue warp
-constexpr int kAhead = 4;                                // entries per chunk a lane loads before it needs them
+constexpr int kAhead = 8;                                // entries of a chunk a lane loads one chunk ahead
 constexpr int kPlanThreads = 128;
 
 constexpr uint32_t kStatusTimeout = 128u;  // bit raised in the status word when a bounded wait ran out
@@ -201,17 +201,21 @@ sddmm_dense_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_
             it.init(m_tiles, n_tiles);
             uint32_t slot = 0, use = 0;
             bool ok_run = true;
+            VS_PROF_T0();
             for (uint32_t i = 0; i < my_items && ok_run; ++i, it.next()) {
                 for (int kb = 0; kb < k_blocks && ok_run; ++kb) {
                     if (use > 0) ok_run = wait_or_abort<kSleepLoad>(bar_empty + 8 * slot, (use - 1u) & 1u, abort_flag);
                     if (!ok_run) break;
+                    VS_PROF_ADD(0);   // loader: wait for a free slot
                     const uint32_t bar = bar_full + 8 * slot;
                     tc::mbar_expect_tx(bar, (uint32_t)(kAStageBytes + kBStageBytes));   // arrives and arms the byte count
                     tc::tma_load_3d(base + Smem::kA + slot * kAStageBytes, &map_lhs, bar, kb * kBlockK, it.mt * kTileM, it.b);
                     tc::tma_load_3d(base + Smem::kB + slot * kBStageBytes, &map_rhs, bar, kb * kBlockK, it.nt * kTileN, it.b);
                     if (++slot == (uint32_t)kStages) { slot = 0; ++use; }
+                    VS_PROF_ADD(1);   // loader: issue
                 }
             }
+            VS_PROF_FLUSH(0);
         }
     } else if (warp >= kMmaWarp) {
         // =========================== MMA issuers =========================================================
@@ -226,6 +230,7 @@ sddmm_dense_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_
             it.init(m_tiles, n_tiles);
             uint32_t slot = 0, parity = 0;
             bool ok_run = true, ready = false;
+            VS_PROF_T0();
             for (uint32_t i = 0; i < my_items && ok_run; ++i, it.next()) {
                 const int tn = min(kTileN, (p.n - it.nt * kTileN + 15) & ~15);
                 const uint32_t idesc = tc::make_idesc_f16(128, tn, 0, 0);   // both operands K-major
@@ -233,9 +238,11 @@ sddmm_dense_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_
                 if (i >= 2) ok_run = wait_or_abort<kSleepMma>(bar_acc_empty + 8 * buf, ((i >> 1) - 1u) & 1u, abort_flag);
                 tc::tc_fence_after_sync();
                 const uint32_t d = tmem_base + buf * kAccCols + (uint32_t)h * kTileN;
+                VS_PROF_ADD(3);   // mma: wait for the accumulator
                 for (int kb = 0; kb < k_blocks && ok_run; ++kb) {
                     if (!ready) ok_run = wait_or_abort<kSleepMma>(bar_full + 8 * slot, parity, abort_flag);
                     if (!ok_run) break;
+                    VS_PROF_ADD(4);   // mma: wait for the stage
                     tc::tc_fence_after_sync();
                     const uint32_t a_lo = a_lo0 + slot * (kAStageBytes >> 4), b_lo = b_lo0 + slot * (kBStageBytes >> 4);
 #pragma unroll
@@ -246,9 +253,11 @@ sddmm_dense_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_
                     if (++slot == (uint32_t)kStages) { slot = 0; parity ^= 1u; }
                     // one look at the next stage's barrier while the MMAs above are handed to the pipe
                     ready = (kb + 1 < k_blocks || i + 1 < my_items) && tc::mbar_try_wait(bar_full + 8 * slot, parity);
+                    VS_PROF_ADD(5);   // mma: issue (+ look ahead)
                 }
                 if (ok_run) tc::mma_commit(bar_acc_full + 8 * buf);
             }
+            VS_PROF_FLUSH(3);
         }
     } else {
         // =========================== epilogue ============================================================
@@ -257,67 +266,94 @@ sddmm_dense_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_
         const uint32_t lane_taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * kTileN);
         const uint8_t *my_row = stg + lane * 128;          // this lane's row of the box; 16-byte chunks XOR (lane & 7)
         constexpr int kChunksPerTile = kTileN / kChunk;    // 4
+        // What a lane has to know ahead of time: the bounds of its vector-row's entries in the tile's four chunks
+        // (loaded one ITEM ahead) and the first kAhead entries of the next chunk it will sample (loaded one CHUNK
+        // ahead): the two dependent global loads never sit between the accumulator and the stores.
+        auto load_bounds = [&](const ItemIter &w, bool valid, int (&off)[kChunksPerTile + 1]) {
+            const int iv = (w.mt * kTileM + half * 128 + quarter * 32 + lane) / V;
+            const int c0 = (w.nt * kTileN) / kChunk;
+            const bool live = valid && iv < p.m_vec;
+            const int32_t *o = chunk_offsets + (int64_t)(live ? iv : 0) * (chunks + 1) + c0;
+#pragma unroll
+            for (int c = 0; c <= kChunksPerTile; ++c) off[c] = (live && c0 + c <= chunks) ? __ldg(o + c) : 0;
+#pragma unroll
+            for (int c = 0; c < kChunksPerTile; ++c)
+                if (!(live && c0 + c < chunks)) off[c + 1] = off[c];   // no such chunk: empty range
+        };
+        auto load_entries = [&](int lo, int hi, uint2 (&e)[kAhead]) {
+#pragma unroll
+            for (int a = 0; a < kAhead; ++a) e[a] = lo + a < hi ? __ldg(chunk_entries + lo + a) : make_uint2(0u, 0u);
+        };
         ItemIter it;
         it.init(m_tiles, n_tiles);
+        int off[kChunksPerTile + 1], off_next[kChunksPerTile + 1];
+        uint2 ent[kAhead];
+        load_bounds(it, my_items > 0, off);
+        load_entries(off[0], off[1], ent);
         bool ok_run = true;
-        for (uint32_t i = 0; i < my_items && ok_run; ++i, it.next()) {
+        VS_PROF_T0();
+        for (uint32_t i = 0; i < my_items && ok_run; ++i) {
             const uint32_t buf = i & 1u;
-            const int row = it.mt * kTileM + half * 128 + quarter * 32 + lane;   // this lane's row of lhs
-            const int iv = row / V, v = row % V;                                 // its vector-row and place in it
-            const int n0 = it.nt * kTileN;
-            const int tn = min(kTileN, (p.n - n0 + 15) & ~15);
-            // bounds of this vector-row's entries in the tile's four chunks, and the first entries of each:
-            // in flight while the MMAs of the item run
-            int off[kChunksPerTile + 1];
-            uint2 ent[kChunksPerTile][kAhead];
-            {
-                const int c0 = n0 / kChunk;
-                const int32_t *o = chunk_offsets + (int64_t)iv * (chunks + 1) + c0;
-#pragma unroll
-                for (int c = 0; c <= kChunksPerTile; ++c) off[c] = (iv < p.m_vec && c0 + c <= chunks) ? __ldg(o + c) : 0;
-#pragma unroll
-                for (int c = 0; c < kChunksPerTile; ++c) {
-                    if (!(iv < p.m_vec && c0 + c < chunks)) off[c + 1] = off[c];   // no such chunk: empty range
-#pragma unroll
-                    for (int a = 0; a < kAhead; ++a)
-                        ent[c][a] = off[c] + a < off[c + 1] ? __ldg(chunk_entries + off[c] + a) : make_uint2(0u, 0u);
-                }
-            }
+            const int v = (it.mt * kTileM + half * 128 + quarter * 32 + lane) % V;   // this lane's place in its vector-row
+            const int tn = min(kTileN, (p.n - it.nt * kTileN + 15) & ~15);
             TOut *out = static_cast<TOut *>(p.out) + (int64_t)it.b * p.stride_out + v;
+            it.next();
+            load_bounds(it, i + 1 < my_items, off_next);
             // warp-uniform outcome: tcgen05.ld below needs all 32 lanes
             ok_run = __all_sync(0xffffffffu, wait_or_abort<kSleepEpilogue>(bar_acc_full + 8 * buf, (i >> 1) & 1u, abort_flag));
             if (!ok_run) break;
+            VS_PROF_ADD(6);   // epilogue: bounds of the next item issued + wait for the accumulator
             tc::tc_fence_after_sync();
 #pragma unroll
             for (int c = 0; c < kChunksPerTile; ++c) {
+                uint2 ent_next[kAhead];   // the chunk after this one: same item, or the first of the next item
+                if (c + 1 < kChunksPerTile) load_entries(off[c + 1], off[c + 2], ent_next);
+                else load_entries(off_next[0], off_next[1], ent_next);
                 if (c * kChunk < tn) {   // warp-uniform
                     uint32_t r[kChunk];
-                    __syncwarp();        // together again, and every lane is done reading the previous chunk's box
+                    __syncwarp();        // together again for the aligned load
                     tc::tmem_ld_x32(lane_taddr + buf * kAccCols + (uint32_t)(c * kChunk), r);
+                    if ((c + 1) * kChunk >= tn) {   // the last column this warp needs is in registers
+                        tc::tc_fence_before_sync();
+                        tc::mbar_arrive(bar_acc_empty + 8 * buf);
+                    }
+                    VS_PROF_ADD(7);   // epilogue: TMEM load
+                    // The lane's 32 columns go to its row of the box and come back one entry at a time (no
+                    // dynamic register indexing); no lane reads another lane's row, so nothing is synchronised.
 #pragma unroll
                     for (int u = 0; u < 8; ++u)
                         *reinterpret_cast<uint4 *>(stg + lane * 128 + ((u ^ (lane & 7)) << 4)) =
                             make_uint4(r[4 * u], r[4 * u + 1], r[4 * u + 2], r[4 * u + 3]);
-                    __syncwarp();
-                    // a lane only reads its own row, but the box keeps register pressure and dynamic indexing out
 #pragma unroll
                     for (int a = 0; a < kAhead; ++a) {
                         if (off[c] + a < off[c + 1]) {
-                            const uint32_t cl = ent[c][a].y;
+                            const uint32_t cl = ent[a].y;
                             const float x = *reinterpret_cast<const float *>(my_row + (((cl >> 2) ^ (uint32_t)(lane & 7)) << 4) + (cl & 3u) * 4);
-                            store_scalar(out + (int64_t)ent[c][a].x * V, x);
+                            store_scalar(out + (int64_t)ent[a].x * V, x);
                         }
                     }
-                    for (int e = off[c] + kAhead; e < off[c + 1]; ++e) {   // denser rows
-                        const uint2 en = __ldg(chunk_entries + e);
-                        const float x = *reinterpret_cast<const float *>(my_row + (((en.y >> 2) ^ (uint32_t)(lane & 7)) << 4) + (en.y & 3u) * 4);
-                        store_scalar(out + (int64_t)en.x * V, x);
+                    // denser rows: the remaining entries eight at a time, so that their loads overlap
+                    for (int e = off[c] + kAhead; e < off[c + 1]; e += 8) {
+                        uint2 en[8];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) en[u] = e + u < off[c + 1] ? __ldg(chunk_entries + e + u) : make_uint2(0u, 0u);
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            if (e + u < off[c + 1]) {
+                                const float x = *reinterpret_cast<const float *>(my_row + (((en[u].y >> 2) ^ (uint32_t)(lane & 7)) << 4) + (en[u].y & 3u) * 4);
+                                store_scalar(out + (int64_t)en[u].x * V, x);
+                            }
+                        }
                     }
+                    VS_PROF_ADD(8);   // epilogue: box + sampling
                 }
+#pragma unroll
+                for (int a = 0; a < kAhead; ++a) ent[a] = ent_next[a];
             }
-            tc::tc_fence_before_sync();
-            tc::mbar_arrive(bar_acc_empty + 8 * buf);   // every column this warp needs has been read
+#pragma unroll
+            for (int c = 0; c <= kChunksPerTile; ++c) off[c] = off_next[c];
         }
+        VS_PROF_FLUSH(6);
     }
 
     // ---- teardown ---------------------------------------------------------------------------------------

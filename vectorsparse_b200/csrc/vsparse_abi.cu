@@ -743,6 +743,14 @@ VS_EXPORT int vs_sddmm_host(int path, int in_dtype, int out_dtype, int m_vec, in
     return VS_OK;
 }
 
+VS_EXPORT int vs_sddmm_formulation(int m_vec, int k, int n, int nonzeros_vec, int vec_length) {
+    if (m_vec <= 0 || n <= 0 || k < densesddmm::kBlockK || nonzeros_vec <= 0 || !(vec_length == 2 || vec_length == 4 || vec_length == 8))
+        return 0;
+    SddmmParams p{};
+    p.m_vec = m_vec; p.k = k; p.n = n; p.nnz_vec = nonzeros_vec;
+    return sddmm_use_dense(p, vec_length) ? 1 : 0;
+}
+
 VS_EXPORT int vs_device_status(int clear, uint32_t *status) {
     if (!status) return VS_ERR_NULL;
     DeviceInfo *d;
