@@ -51,7 +51,7 @@ WORKLOADS = {
 # command (profiles/ holds the summary it comes from); None until one has been taken for the workload.
 NCU_TRAFFIC_BYTES = {
     "spmm_v8_s90": 334.8e6,    # profiles/spmm_dense_kernel__spmm_v8_s90.md
-    "sddmm_v8_s90": 380.2e6,   # profiles/sddmm_tma_kernel__sddmm_v8_s90.md
+    "sddmm_v8_s90": 380.5e6,   # profiles/sddmm_dense_kernel__sddmm_v8_s90.md
 }
 
 
