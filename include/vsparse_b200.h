@@ -64,9 +64,10 @@ const char *vs_version(void);
  * k (dense width): tensor path needs k % 64 == 0 (as the reference, src/wmma_spmm.cu:327,396); CUDA-core path
  * needs k % 8 == 0 for fp16 and k % 4 == 0 for fp32.  values, rhs, out must be 16-byte aligned.
  *
- * Tensor path: two formulations, chosen on the device by the density of the matrix (the signature carries no
- * nonzero count).  From a density of 0.003 * vec_length upwards, zero-filled 256 x 64 tiles of the sparse
- * matrix are multiplied with whole tiles of rhs; below it, and whenever that kernel produced a non-finite sum
+ * Tensor path: two formulations, chosen on the device (the signature carries no nonzero count) by comparing
+ * their measured costs: zero-filled 256 x 64 tiles of the sparse matrix multiplied with whole tiles of rhs cost
+ * the same whatever the tiles hold; where that is more than a per-row overhead plus a cost per nonzero vector
+ * (wide, very sparse matrices), and whenever the dense kernel produced a non-finite sum
  * (0 * Inf from a row of rhs that no nonzero names), one row of rhs is gathered per nonzero vector as in the
  * reference.  A column index may appear only once per vector-row (as in any CVSE built from a mask).
  * Environment variable VSPARSE_B200_SPMM = "dense" | "gather" forces one formulation.  The first tensor-path

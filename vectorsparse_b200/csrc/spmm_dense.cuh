@@ -97,18 +97,22 @@ static_assert(kBStages == kAStages || kBStages == 2 * kAStages,
 // outside [0, K) are dropped (the gather kernels read zeros for them).
 //
 // The kernel also takes the decision between the densifying and the gather kernels, because the number of
-// nonzero vectors is only known here: dense when the density reaches `threshold` and the entries fit the
-// scratch (`entry_capacity`).  Every CTA computes the same answer; CTA 0 publishes it in *use_dense for the two
-// kernels enqueued behind this one, and nothing is planned when the answer is no.
+// nonzero vectors is only known here.  Costs in cycles of one SM per 128 columns of B, fitted to measurements
+// (2048 x 512, V = 2/4/8, 90-99 % sparse): the dense kernel ~1100 per stage (256 rows x 64 columns of A) whatever
+// they hold; the gather kernel ~370 per vector-row plus ~4.7 per nonzero vector.  Dense when cheaper (or forced)
+// and the entries fit the scratch (`entry_capacity`).  Every CTA computes the same answer; CTA 0 publishes it
+// in *use_dense for the two kernels enqueued behind this one, and nothing is planned when the answer is no.
 __global__ void __launch_bounds__(kPlanThreads)
 dense_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__restrict__ col_indices, int m_vec, int K,
                   int rows_per_group, int plan_blocks, int32_t *__restrict__ blk_offsets, uint2 *__restrict__ blk_entries,
-                  int64_t entry_capacity, float threshold, int32_t *use_dense) {
+                  int64_t entry_capacity, int force_dense, int32_t *use_dense) {
     extern __shared__ int plan_sh[];
     {
         const int64_t nnz = __ldg(row_offsets + m_vec);
-        const float density = (float)nnz / ((float)m_vec * (float)K);
-        const bool dense = nnz <= entry_capacity && density >= threshold;
+        const float stages = (float)(gridDim.x / (kTileM / kGroupRows)) * (float)(plan_blocks / (kBlockK / kPlanCols));
+        const float dense_cost = stages * 1100.0f;
+        const float gather_cost = (float)m_vec * 370.0f + 4.7f * (float)nnz;
+        const bool dense = nnz <= entry_capacity && (force_dense || dense_cost < gather_cost);
         if (blockIdx.x == 0 && threadIdx.x == 0) *use_dense = dense ? 1 : 0;
         if (!dense) return;
     }

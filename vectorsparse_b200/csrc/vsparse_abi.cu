@@ -235,7 +235,7 @@ int launch_spmm_gather(const SpmmParams &p, cudaStream_t s, DeviceInfo *d, const
 // Which tensor-core SpMM runs.  The densifying kernel multiplies zero-filled 256 x 64 tiles of A, the gather
 // kernels fetch one row of B per nonzero vector: the first costs the same whatever the sparsity, the second is
 // proportional to the nonzeros.  The number of nonzeros is only known on the device (the reference signature
-// does not pass it), so the choice is made there: the plan kernel compares the density with a threshold and
+// does not pass it), so the choice is made there: the plan kernel compares the two costs (see there) and
 // leaves a flag that one of the two kernels, both enqueued, finds set against it and returns at once.  The
 // densifying kernel clears the flag again if it produced a non-finite sum, so that the gather kernel redoes the
 // call with the reference's semantics for Inf / NaN in rows of B that no nonzero names.
@@ -247,7 +247,6 @@ SpmmMode spmm_mode() {   // read at every call, so that a test can switch kernel
     return SpmmMode::kAuto;
 }
 constexpr int64_t kMaxPlanBytes = 512ll << 20;
-constexpr float kDenseDensityPerV = 0.003f;   // dense from this density on, per element of the vector length
 
 template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStream_t s) {
     DeviceInfo *d;
@@ -290,9 +289,9 @@ template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStre
     int32_t *flag = reinterpret_cast<int32_t *>(plan);
     int32_t *blk_offsets = reinterpret_cast<int32_t *>(plan + 16);
     uint2 *blk_entries = reinterpret_cast<uint2 *>(plan + 16 + offsets_bytes);
-    const float threshold = mode == SpmmMode::kDense ? 0.0f : kDenseDensityPerV * V;
+    const int force_dense = mode == SpmmMode::kDense ? 1 : 0;
     densespmm::dense_plan_kernel<<<groups, densespmm::kPlanThreads, plan_smem, s>>>(
-        p.row_offsets, p.col_indices, p.m_vec, p.K, rows_per_group, plan_blocks, blk_offsets, blk_entries, capacity, threshold,
+        p.row_offsets, p.col_indices, p.m_vec, p.K, rows_per_group, plan_blocks, blk_offsets, blk_entries, capacity, force_dense,
         flag);
     const int64_t items = (int64_t)p.batch * n_tiles * m_tiles;
     const unsigned grid = (unsigned)(items < d->sm_count ? items : d->sm_count);   // one persistent CTA per SM
