@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the column-vector sparse SpMM hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|dense-library] [--workload NAME]
 
 Default workload `spmm_v8_s90`: the tensor-core SpMM (wmmaSpmm entry point) on the pruned ResNet-50 layer shape
 the target is quoted on — A 2048 x 512 in CVSE with V = 8 at 90 % sparsity (Beta(2,2)-skewed rows), fp16 values
@@ -16,6 +16,9 @@ Metric: effective TFLOP/s = 2 * nnz * N / time, nnz = nnz_vec * V, summed over a
 the launch, D2H of C, all inside the timed region.
 `--impl reference`: the reference's own CPU path (its sequential host loop) timed on this box's host cores on a
 bounded sample of the same stream.
+`--impl dense-library`: context only, one GPU, SpMM workloads: the sparse matrices expanded to dense fp16 once,
+outside the timed region, and multiplied by the vendor library's batched GEMM (torch.bmm); answers "what would
+ignoring the sparsity cost on this part".  Not a product path and not part of any other number.
 """
 from __future__ import annotations
 
@@ -418,12 +421,51 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_dense_library(args):
+    """The densified problem through the library's batched GEMM: a comparator, not a product path."""
+    import torch
+
+    from vectorsparse_b200 import cvse
+    w = WORKLOADS[args.workload]
+    assert w["op"] == "spmm" and w.get("dtype") != "f32", "dense-library comparator: fp16 SpMM workloads only"
+    dev = "cuda:0"
+    a = build_problem(w)
+    inst, V, M, K, N = w["inst"], w["V"], w["M"], w["K"], w["N"]
+    flops, alg_bytes = algorithmic(w, a)
+    vals = torch.from_numpy(cvse.fill_random((inst, a.nnz_vec * V), np.float16, cvse.DIST_NORMAL, 100, 0.02)).to(dev)
+    B = torch.from_numpy(cvse.fill_random((inst, K, N), np.float16, cvse.DIST_NORMAL, 101, 1.0)).to(dev)
+    # dense A[inst, M, K]: values[j*V+v] -> row (row of j)*V+v, column col_indices[j]
+    row_of = np.repeat(np.arange(a.m_vec), np.diff(a.row_offsets)).astype(np.int64)
+    rows = torch.from_numpy((row_of[:, None] * V + np.arange(V)[None, :]).reshape(-1)).to(dev)
+    cols = torch.from_numpy(np.repeat(a.col_indices.astype(np.int64), V)).to(dev)
+    A = torch.zeros((inst, M, K), dtype=torch.float16, device=dev)
+    A[:, rows, cols] = vals
+    C = torch.empty((inst, M, N), dtype=torch.float16, device=dev)
+    for _ in range(max(args.warmup, 3)):
+        torch.bmm(A, B, out=C)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        torch.bmm(A, B, out=C)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({
+        "impl": "dense-library", "metric": "SpMM effective TFLOP/s (2*nnz*N)", "value": flops / (ms * 1e-3) / 1e12,
+        "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+        "higher_is_better": True, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
+        "dense_tflops": 2.0 * inst * M * K * N / (ms * 1e-3) / 1e12,
+        "config": {"workload": args.workload, "note": "A expanded to dense outside the timed region; torch.bmm (cuBLAS)"},
+    }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "dense-library"])
     ap.add_argument("--workload", default="spmm_v8_s90", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--kernel-only", action="store_true",
@@ -431,6 +473,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "dense-library":
+        run_dense_library(args)
     else:
         run_ours(args)
 
