@@ -49,6 +49,7 @@ constexpr int kFillWarp0 = kEpiWarps;
 constexpr int kFillPerSlot = (kTileM / kGroupRows) * (kBlockK / kPlanCols);   // 4: one warp per plan bucket of a stage
 constexpr int kFillWarps = kAStages * kFillPerSlot;      // 16: warp f fills A slot f % kAStages, bucket f / kAStages
 constexpr int kFillBatches = 2;                          // entries a fill warp keeps in flight: 2 x 32
+constexpr int kOverflowBatches = 4;                      // batches of 32 loaded together beyond those
 constexpr int kLoadWarp = kFillWarp0 + kFillWarps;       // 24: one thread issues the B loads
 constexpr int kPrefetchWarp = kLoadWarp + 1;             // 25: asks the next item's rows of B into L2
 constexpr int kMmaWarp = kPrefetchWarp + 1;              // 26, 27
@@ -396,19 +397,38 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
 #pragma unroll
                 for (int u = 0; u < kFillBatches; ++u)
                     if (p_e0 + lane + 32 * u < p_e1) scatter_vector<V>(a_part, p_pos[u], zero);
-                for (int e = p_e0 + 32 * kFillBatches + lane; e < p_e1; e += 32)
-                    scatter_vector<V>(a_part, __ldg(blk_entries + e).y, zero);
+                for (int e0 = p_e0 + 32 * kFillBatches; e0 < p_e1; e0 += 32 * kOverflowBatches) {   // denser buckets
+                    uint32_t pos[kOverflowBatches];
+#pragma unroll
+                    for (int u = 0; u < kOverflowBatches; ++u) {
+                        const int e = e0 + 32 * u + lane;
+                        pos[u] = e < p_e1 ? __ldg(blk_entries + e).y : 0u;
+                    }
+#pragma unroll
+                    for (int u = 0; u < kOverflowBatches; ++u)
+                        if (e0 + 32 * u + lane < p_e1) scatter_vector<V>(a_part, pos[u], zero);
+                }
             }
             __syncwarp();
             VS_PROF_ADD(1);   // fill: clear the previous stage's vectors
 #pragma unroll
             for (int u = 0; u < kFillBatches; ++u)
                 if (c_e0 + lane + 32 * u < c_e1) scatter_vector<V>(a_part, c_ent[u].y, c_val[u].raw);
-            for (int e = c_e0 + 32 * kFillBatches + lane; e < c_e1; e += 32) {   // buckets with more entries (denser rows)
-                const uint2 ent = __ldg(blk_entries + e);
-                ValueVec<V> val;
-                val.load(vals + (int64_t)ent.x * V);
-                scatter_vector<V>(a_part, ent.y, val.raw);
+            // buckets with more entries (denser rows): several batches of loads in flight at a time
+            for (int e0 = c_e0 + 32 * kFillBatches; e0 < c_e1; e0 += 32 * kOverflowBatches) {
+                uint2 en[kOverflowBatches];
+                ValueVec<V> val[kOverflowBatches];
+#pragma unroll
+                for (int u = 0; u < kOverflowBatches; ++u) {
+                    const int e = e0 + 32 * u + lane;
+                    en[u] = e < c_e1 ? __ldg(blk_entries + e) : make_uint2(0u, 0u);
+                }
+#pragma unroll
+                for (int u = 0; u < kOverflowBatches; ++u)
+                    if (e0 + 32 * u + lane < c_e1) val[u].load(vals + (int64_t)en[u].x * V);
+#pragma unroll
+                for (int u = 0; u < kOverflowBatches; ++u)
+                    if (e0 + 32 * u + lane < c_e1) scatter_vector<V>(a_part, en[u].y, val[u].raw);
             }
             p_e0 = c_e0; p_e1 = c_e1;
 #pragma unroll
