@@ -15,7 +15,7 @@
 //
 // Organisation: one persistent CTA per SM, work items (batch, 256-row tile of lhs, 128-row tile of rhs).
 //   warps 0-7   epilogue: warp (quarter, half) owns 32 rows of the tile.  Per 32 columns: TMEM -> registers ->
-//               a swizzled 32 x 32 fp32 box of shared memory (private to the warp), then every lane walks the
+//               its row of a swizzled 32 x 32 box of shared memory (already in the output type), then every lane walks the
 //               entries of ITS vector-row in that chunk and stores lhs-row x entry values; the V lanes of a
 //               vector-row write V consecutive outputs.  The bounds of its entries are loaded one item ahead,
 //               the first eight entries of a chunk one chunk ahead, further entries eight at a time.
@@ -47,7 +47,7 @@ constexpr int kAStageBytes = kTileM * kBlockK * 2;       // 32 KiB
 constexpr int kBStageBytes = kTileN * kBlockK * 2;       // 16 KiB
 constexpr int kAccCols = kHalves * kTileN;               // 256 TMEM columns per accumulator buffer
 constexpr int kTmemCols = 2 * kAccCols;                  // 512
-constexpr int kBoxBytes = 32 * kChunk * 4;               // 4 KiB: 32 rows x 32 fp32 columns per epilogue warp
+constexpr int kBoxBytes = 32 * kChunk * 4;               // 4 KiB per epilogue warp: 32 rows x 32 columns, fp32 at most
 constexpr int kAhead = 8;                                // entries of a chunk a lane loads one chunk ahead
 constexpr int kPlanThreads = 128;
 
@@ -264,7 +264,32 @@ sddmm_dense_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_
         const int quarter = warp & 3, half = warp >> 2;   // TMEM lanes 32 quarter ..; rows 128 half .. of the tile
         uint8_t *stg = sm + Smem::kStaging + warp * kBoxBytes;
         const uint32_t lane_taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * kTileN);
-        const uint8_t *my_row = stg + lane * 128;          // this lane's row of the box; 16-byte chunks XOR (lane & 7)
+        // This lane's row of the box holds its 32 accumulator columns already in the output type (64 or 128
+        // bytes); the 16-byte chunks of a row are XOR-swizzled with address bits 7.. so that the row-per-lane
+        // stores spread over the banks.
+        constexpr int kElem = (int)sizeof(TOut);
+        constexpr int kRowBytes = kChunk * kElem;
+        constexpr int kPerChunk = 16 / kElem;
+        const uint32_t swz = kRowBytes == 128 ? (uint32_t)(lane & 7) : (uint32_t)((lane >> 1) & 3);
+        uint8_t *my_row = stg + lane * kRowBytes;
+        auto box_write = [&](const uint32_t (&r)[kChunk]) {
+#pragma unroll
+            for (int u = 0; u < kRowBytes / 16; ++u) {
+                uint4 v;
+                if constexpr (kElem == 2) {
+                    __half2 *hh = reinterpret_cast<__half2 *>(&v);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        hh[e] = __floats2half2_rn(__uint_as_float(r[8 * u + 2 * e]), __uint_as_float(r[8 * u + 2 * e + 1]));
+                } else {
+                    v = make_uint4(r[4 * u], r[4 * u + 1], r[4 * u + 2], r[4 * u + 3]);
+                }
+                *reinterpret_cast<uint4 *>(my_row + (((uint32_t)u ^ swz) << 4)) = v;
+            }
+        };
+        auto box_read = [&](uint32_t cl) -> TOut {
+            return *reinterpret_cast<const TOut *>(my_row + (((cl / kPerChunk) ^ swz) << 4) + (cl % kPerChunk) * kElem);
+        };
         constexpr int kChunksPerTile = kTileN / kChunk;    // 4
         // What a lane has to know ahead of time: the bounds of its vector-row's entries in the tile's four chunks
         // (loaded one ITEM ahead) and the first kAhead entries of the next chunk it will sample (loaded one CHUNK
@@ -320,16 +345,11 @@ sddmm_dense_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_
                     VS_PROF_ADD(7);   // epilogue: TMEM load
                     // The lane's 32 columns go to its row of the box and come back one entry at a time (no
                     // dynamic register indexing); no lane reads another lane's row, so nothing is synchronised.
-#pragma unroll
-                    for (int u = 0; u < 8; ++u)
-                        *reinterpret_cast<uint4 *>(stg + lane * 128 + ((u ^ (lane & 7)) << 4)) =
-                            make_uint4(r[4 * u], r[4 * u + 1], r[4 * u + 2], r[4 * u + 3]);
+                    box_write(r);
 #pragma unroll
                     for (int a = 0; a < kAhead; ++a) {
                         if (off[c] + a < off[c + 1]) {
-                            const uint32_t cl = ent[a].y;
-                            const float x = *reinterpret_cast<const float *>(my_row + (((cl >> 2) ^ (uint32_t)(lane & 7)) << 4) + (cl & 3u) * 4);
-                            store_scalar(out + (int64_t)ent[a].x * V, x);
+                            out[(int64_t)ent[a].x * V] = box_read(ent[a].y);
                         }
                     }
                     // denser rows: the remaining entries eight at a time, so that their loads overlap
@@ -340,8 +360,7 @@ sddmm_dense_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_
 #pragma unroll
                         for (int u = 0; u < 8; ++u) {
                             if (e + u < off[c + 1]) {
-                                const float x = *reinterpret_cast<const float *>(my_row + (((en[u].y >> 2) ^ (uint32_t)(lane & 7)) << 4) + (en[u].y & 3u) * 4);
-                                store_scalar(out + (int64_t)en[u].x * V, x);
+                                out[(int64_t)en[u].x * V] = box_read(en[u].y);
                             }
                         }
                     }
