@@ -153,7 +153,8 @@ int vs_attention_cvse(int path, int m_vec, int vec_length, int n, int d, int non
  * until the process exits.  Same arguments and results as vs_attention_cvse, minus `workspace`.
  *
  *  - Larger requests are refused with VS_ERR_SHAPE and a message on stderr; nothing is launched.
- *  - The call itself, and everything it calls, uses no cudaMalloc, cudaFree or allocating library routine.
+ *  - The call itself, and everything it calls, uses no cudaMalloc, cudaFree or allocating library routine: its
+ *    SDDMM and SpMM steps always run the row-gather kernels, never the formulations that keep plan scratch.
  *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
  *    current).  Make that first call outside any stream capture.
  *  - All calls on a device share the one array, and it keeps what the last call left in it.  Nothing in it has

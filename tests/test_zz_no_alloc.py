@@ -39,7 +39,11 @@ def attention_pair(path, seed, heads, n, band, sparsity):
 
 
 @pytest.mark.parametrize("path", [VS_PATH_TENSOR, VS_PATH_CUDA_CORE])
-def test_two_calls_in_a_row_match_the_workspace_form(path):
+def test_two_calls_in_a_row_match_the_workspace_form(path, monkeypatch):
+    # The no-allocation form always runs the row-gather tensor kernels (the dense formulations keep plan scratch);
+    # the workspace form is pinned to the same ones here, so that the comparison can be bit for bit.
+    monkeypatch.setenv("VSPARSE_B200_SPMM", "gather")
+    monkeypatch.setenv("VSPARSE_B200_SDDMM", "gather")
     want, got = attention_pair(path, seed=31, heads=3, n=512, band=64, sparsity=0.8)
     assert not torch.isnan(got).any()
     assert torch.equal(got, want)          # same kernels in the same order: the results are bit-identical
@@ -47,6 +51,15 @@ def test_two_calls_in_a_row_match_the_workspace_form(path):
     want2, got2 = attention_pair(path, seed=77, heads=2, n=256, band=32, sparsity=0.7)
     assert not torch.isnan(got2).any()
     assert torch.equal(got2, want2)
+
+
+def test_matches_the_default_formulations_within_tolerance(monkeypatch):
+    """Left to choose, the workspace form may run the dense formulations: same values up to fp16 rounding."""
+    monkeypatch.delenv("VSPARSE_B200_SPMM", raising=False)
+    monkeypatch.delenv("VSPARSE_B200_SDDMM", raising=False)
+    want, got = attention_pair(VS_PATH_TENSOR, seed=5, heads=2, n=512, band=64, sparsity=0.8)
+    assert not torch.isnan(got).any()
+    assert torch.allclose(got.float(), want.float(), rtol=0, atol=2e-2)
 
 
 def test_requests_beyond_the_built_in_scratch_are_refused():

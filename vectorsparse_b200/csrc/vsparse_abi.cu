@@ -70,6 +70,15 @@ int device_info(DeviceInfo **out) {
     return VS_OK;
 }
 
+// Set for the duration of an entry point that promises not to allocate: the tensor-core formulations that need
+// plan scratch are skipped on this thread, the gather kernels (which need none) take the call.
+thread_local bool t_no_scratch = false;
+struct NoScratchScope {
+    bool saved;
+    NoScratchScope() : saved(t_no_scratch) { t_no_scratch = true; }
+    ~NoScratchScope() { t_no_scratch = saved; }
+};
+
 // Scratch of at least `bytes` for work enqueued on `stream`.  Grows by stream-ordered allocation (the old buffer
 // is released behind the work already enqueued); in the steady state this makes no CUDA call.  Buffers live
 // until the process ends.
@@ -266,7 +275,7 @@ template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStre
     const int64_t offsets_bytes = (((int64_t)groups * (plan_blocks + 1) * 4) + 15) & ~15ll;
     const int64_t plan_bytes = 16 + offsets_bytes + capacity * 8;
     const size_t plan_smem = (size_t)(2 * plan_blocks + rows_per_group + 1) * 4;
-    const bool dense_ok = mode != SpmmMode::kGather && p.K > 0 && p.m_vec > 0 && p.N % 8 == 0 && plan_bytes <= kMaxPlanBytes &&
+    const bool dense_ok = !t_no_scratch && mode != SpmmMode::kGather && p.K > 0 && p.m_vec > 0 && p.N % 8 == 0 && plan_bytes <= kMaxPlanBytes &&
                           plan_smem <= 40 * 1024 && (p.batch == 1 || (p.stride_rhs * 2) % 16 == 0) &&
                           (p.batch == 1 || (p.stride_out * sizeof(TOut)) % 16 == 0) && aligned16(p.rhs) && aligned16(p.out);
     if (!dense_ok) return launch_spmm_gather<TOut, V>(p, s, d, nullptr);
@@ -398,7 +407,7 @@ template <typename TOut, int V> int launch_sddmm_tc(const SddmmParams &p, cudaSt
     const int64_t offsets_bytes = (((int64_t)p.m_vec * (chunks + 1) * 4) + 15) & ~15ll;
     const int64_t plan_bytes = offsets_bytes + (int64_t)p.nnz_vec * 8;
     const size_t plan_smem = (size_t)2 * chunks * 4;
-    const bool dense_ok = p.n > 0 && p.m_vec > 0 && p.nnz_vec > 0 && p.k >= densesddmm::kBlockK && plan_bytes <= kMaxPlanBytes &&
+    const bool dense_ok = !t_no_scratch && p.n > 0 && p.m_vec > 0 && p.nnz_vec > 0 && p.k >= densesddmm::kBlockK && plan_bytes <= kMaxPlanBytes &&
                           plan_smem <= 40 * 1024 && aligned16(p.lhs) && aligned16(p.rhs) &&
                           (p.batch == 1 || ((p.stride_lhs * 2) % 16 == 0 && (p.stride_rhs * 2) % 16 == 0)) &&
                           sddmm_use_dense(p, V);
@@ -643,6 +652,7 @@ VS_EXPORT int vs_attention_cvse_static(int path, int m_vec, int vec_length, int 
     void *scratch = nullptr;
     int rc = attention_scratch(&scratch);
     if (rc != VS_OK) return rc;
+    NoScratchScope no_allocation;   // SDDMM and SpMM below: the formulations without plan scratch
     return vs_attention_cvse(path, m_vec, vec_length, n, d, nonzeros_vec, row_indices, row_offsets, col_indices, q, kmat,
                              vmat, out, scratch, scale, batch, stream);
 }
