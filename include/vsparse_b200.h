@@ -187,6 +187,27 @@ int vs_sddmm_host(int path, int in_dtype, int out_dtype, int m_vec, int k, int n
  * ---------------------------------------------------------------------------------------------------- */
 int vs_device_status(int clear, uint32_t *status);
 
+/* ------------------------------------------------------------------------------------------------------
+ * Plan scratch in the caller's hands (no counterpart in the reference, whose kernels keep no workspace:
+ * src/wmma_spmm.cu:317-350).  The dense formulations of the tensor path bucket the nonzeros once per call and
+ * need device memory for that.  By default the library keeps one buffer per calling stream (see vs_spmm).  A
+ * caller that plans its own device memory can instead hand over a buffer:
+ *
+ *   vs_spmm_workspace_bytes / vs_sddmm_workspace_bytes   bytes the dense formulation needs for such a call
+ *                                                        (0: it is never used for this problem); no device needed
+ *   vs_set_workspace(ptr, bytes)                         from now on the tensor-path calls made by THIS host
+ *                                                        thread put their plan in [ptr, ptr + bytes) when it
+ *                                                        fits and run the row-gather formulation when it does
+ *                                                        not: with a workspace set the library never allocates.
+ *                                                        (NULL, 0) returns to the library's own buffers.
+ *
+ * ptr must be 16-byte aligned device memory and stay valid until the work enqueued with it has completed; calls
+ * that may overlap on the GPU (different streams) need different workspaces.
+ * ---------------------------------------------------------------------------------------------------- */
+int64_t vs_spmm_workspace_bytes(int m_vec, int vec_length, int n, int batch, int64_t stride_values);
+int64_t vs_sddmm_workspace_bytes(int m_vec, int n, int nonzeros_vec);
+int vs_set_workspace(void *workspace, int64_t bytes);
+
 /* Which tensor-path SDDMM formulation vs_sddmm / vs_sddmm_batched would run for this problem: 1 = dense tiles
  * sampled at the mask, 0 = row gather (environment override included).  Diagnostic, no counterpart in the
  * reference; lets a benchmark name the kernels it measures.  Needs no device. */

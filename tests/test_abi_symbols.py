@@ -115,3 +115,21 @@ def test_sddmm_formulation_choice(monkeypatch):
     assert f(512, 64, 4096, 209920, 8) == 1
     monkeypatch.setenv("VSPARSE_B200_SDDMM", "gather")
     assert f(256, 256, 512, 12685, 8) == 0
+
+
+def test_workspace_queries_and_setter():
+    """Sizing a caller-owned plan scratch and handing it over need no device."""
+    L = _lib.lib()
+    b1 = L.vs_spmm_workspace_bytes(256, 8, 512, 1, 0)
+    assert b1 >= 256 * 512 * 8                      # one entry per possible (vector-row, column)
+    b256 = L.vs_spmm_workspace_bytes(256, 8, 512, 256, 12685 * 8)
+    assert 12685 * 8 <= b256 < b1                   # a batch stride bounds the number of nonzero vectors
+    assert L.vs_spmm_workspace_bytes(256, 1, 512, 1, 0) == 0      # no tensor path at V = 1
+    assert L.vs_spmm_workspace_bytes(1 << 20, 8, 1 << 20, 1, 0) == 0   # beyond the 512 MB cap: gather kernels
+    assert L.vs_sddmm_workspace_bytes(256, 512, 12685) >= 12685 * 8
+    assert L.vs_sddmm_workspace_bytes(0, 512, 12685) == 0
+    assert L.vs_set_workspace(None, 0) == 0
+    assert L.vs_set_workspace(None, 64) == -8       # a size without a buffer
+    assert L.vs_set_workspace(C.c_void_p(0x1008), 64) == -5      # not 16-byte aligned
+    assert L.vs_set_workspace(C.c_void_p(0x1000), -1) == -8
+    assert L.vs_set_workspace(None, 0) == 0

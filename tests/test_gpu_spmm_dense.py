@@ -131,3 +131,28 @@ def test_batched_strides_streams_and_growing_scratch(monkeypatch):
         for b in range(batch):
             want = spmm_oracle(a, N, vals[b, :a.nnz_vec * V], B[b, :a.n * N].reshape(a.n, N))
             assert_close(host[b, :a.m * N].reshape(a.m, N), want, f"batched m_vec={a.m_vec} entry {b}")
+
+
+def test_caller_owned_workspace(monkeypatch):
+    """With a workspace set the plan goes into the caller's buffer and the library allocates nothing; a buffer that
+    is too small sends the call to the gather kernels instead.  Same results either way."""
+    monkeypatch.setenv("VSPARSE_B200_SPMM", "dense")
+    V, N = 8, 128
+    a = problem(cvse.GEN_BETA, 17, 64, 320, V, 0.8)
+    vals, B = spmm_inputs(a, N, np.float16, 4, sigma=0.5)
+    want = spmm_oracle(a, N, vals, B)
+    need = _lib.lib().vs_spmm_workspace_bytes(a.m_vec, V, a.n, 1, 0)
+    assert need > 0
+    poison = 0xA5
+    for size in (need, 64):
+        ws = torch.full((size + 256,), poison, dtype=torch.uint8, device=DEV)
+        ops.set_workspace(ws[:size])
+        try:
+            got = run(a, N, vals, B, torch.float32, "dense", monkeypatch)
+        finally:
+            ops.set_workspace(None)
+        assert_close(got, want, f"caller workspace of {size} bytes")
+        tail = ws[size:].cpu().numpy()
+        assert np.all(tail == poison), "wrote past the end of the caller's workspace"
+        used = bool((ws[:size].cpu().numpy() != poison).any())
+        assert used == (size == need), "the plan must live in the caller's buffer exactly when it fits"

@@ -79,10 +79,20 @@ struct NoScratchScope {
     ~NoScratchScope() { t_no_scratch = saved; }
 };
 
+// A workspace handed over by the caller (vs_set_workspace) for the calls of this host thread.
+thread_local bool t_ws_set = false;
+thread_local void *t_ws_ptr = nullptr;
+thread_local int64_t t_ws_bytes = 0;
+
 // Scratch of at least `bytes` for work enqueued on `stream`.  Grows by stream-ordered allocation (the old buffer
 // is released behind the work already enqueued); in the steady state this makes no CUDA call.  Buffers live
 // until the process ends.
 int stream_scratch(DeviceInfo *d, cudaStream_t stream, size_t bytes, void **out) {
+    if (t_ws_set) {   // the caller's buffer or nothing: never allocate behind a caller that manages memory itself
+        if ((int64_t)bytes > t_ws_bytes) return VS_ERR_SHAPE;
+        *out = t_ws_ptr;
+        return VS_OK;
+    }
     std::lock_guard<std::mutex> lock(g_devices_mutex);
     Scratch &sc = d->scratch[stream];
     if (sc.bytes < bytes) {
@@ -257,6 +267,29 @@ SpmmMode spmm_mode() {   // read at every call, so that a test can switch kernel
 }
 constexpr int64_t kMaxPlanBytes = 512ll << 20;
 
+// Bytes of plan scratch the densifying SpMM needs: a flag word, the bucket offsets, 8 bytes per possible entry.
+int64_t spmm_plan_bytes(int m_vec, int V, int K, int batch, int64_t stride_values, int64_t *capacity_out, int64_t *offsets_out) {
+    const int k_blocks = (K + densespmm::kBlockK - 1) / densespmm::kBlockK;
+    const int m_tiles = (int)(((int64_t)m_vec * V + densespmm::kTileM - 1) / densespmm::kTileM);
+    const int groups = m_tiles * (densespmm::kTileM / densespmm::kGroupRows);
+    const int plan_blocks = k_blocks * (densespmm::kBlockK / densespmm::kPlanCols);
+    // entries are addressed like the nonzero vectors: at most one per (vector-row, column), and never more than
+    // fit between two matrices of a batch
+    int64_t capacity = (int64_t)m_vec * K;
+    if (batch > 1 && stride_values > 0 && stride_values / V < capacity) capacity = stride_values / V;
+    const int64_t offsets_bytes = (((int64_t)groups * (plan_blocks + 1) * 4) + 15) & ~15ll;
+    if (capacity_out) *capacity_out = capacity;
+    if (offsets_out) *offsets_out = offsets_bytes;
+    return 16 + offsets_bytes + capacity * 8;
+}
+// The same for the dense SDDMM: per-row chunk offsets and 8 bytes per mask entry.
+int64_t sddmm_plan_bytes(int m_vec, int n, int nnz_vec, int64_t *offsets_out) {
+    const int chunks = (n + densesddmm::kChunk - 1) / densesddmm::kChunk;
+    const int64_t offsets_bytes = (((int64_t)m_vec * (chunks + 1) * 4) + 15) & ~15ll;
+    if (offsets_out) *offsets_out = offsets_bytes;
+    return offsets_bytes + (int64_t)nnz_vec * 8;
+}
+
 template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStream_t s) {
     DeviceInfo *d;
     int rc = device_info(&d);
@@ -268,12 +301,8 @@ template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStre
     const int groups = m_tiles * (densespmm::kTileM / densespmm::kGroupRows);
     const int plan_blocks = k_blocks * (densespmm::kBlockK / densespmm::kPlanCols);
     const int rows_per_group = densespmm::kGroupRows / V;
-    // entries are addressed like the nonzero vectors: at most one per (vector-row, column), and never more than
-    // fit between two matrices of a batch
-    int64_t capacity = (int64_t)p.m_vec * p.K;
-    if (p.batch > 1 && p.stride_values > 0 && p.stride_values / V < capacity) capacity = p.stride_values / V;
-    const int64_t offsets_bytes = (((int64_t)groups * (plan_blocks + 1) * 4) + 15) & ~15ll;
-    const int64_t plan_bytes = 16 + offsets_bytes + capacity * 8;
+    int64_t capacity = 0, offsets_bytes = 0;
+    const int64_t plan_bytes = spmm_plan_bytes(p.m_vec, V, p.K, p.batch, p.stride_values, &capacity, &offsets_bytes);
     const size_t plan_smem = (size_t)(2 * plan_blocks + rows_per_group + 1) * 4;
     const bool dense_ok = !t_no_scratch && mode != SpmmMode::kGather && p.K > 0 && p.m_vec > 0 && p.N % 8 == 0 && plan_bytes <= kMaxPlanBytes &&
                           plan_smem <= 40 * 1024 && (p.batch == 1 || (p.stride_rhs * 2) % 16 == 0) &&
@@ -404,8 +433,8 @@ template <typename TOut, int V> int launch_sddmm_tc(const SddmmParams &p, cudaSt
     int rc = device_info(&d);
     if (rc != VS_OK) return rc;
     const int chunks = (p.n + densesddmm::kChunk - 1) / densesddmm::kChunk;
-    const int64_t offsets_bytes = (((int64_t)p.m_vec * (chunks + 1) * 4) + 15) & ~15ll;
-    const int64_t plan_bytes = offsets_bytes + (int64_t)p.nnz_vec * 8;
+    int64_t offsets_bytes = 0;
+    const int64_t plan_bytes = sddmm_plan_bytes(p.m_vec, p.n, p.nnz_vec, &offsets_bytes);
     const size_t plan_smem = (size_t)2 * chunks * 4;
     const bool dense_ok = !t_no_scratch && p.n > 0 && p.m_vec > 0 && p.nnz_vec > 0 && p.k >= densesddmm::kBlockK && plan_bytes <= kMaxPlanBytes &&
                           plan_smem <= 40 * 1024 && aligned16(p.lhs) && aligned16(p.rhs) &&
@@ -749,6 +778,27 @@ VS_EXPORT int vs_sddmm_host(int path, int in_dtype, int out_dtype, int m_vec, in
     if (rc != VS_OK) return rc;
     VS_CUDA_TRY(cudaDeviceSynchronize());
     if (b_out) VS_CUDA_TRY(cudaMemcpy(output_values, d_out, b_out, cudaMemcpyDeviceToHost));
+    return VS_OK;
+}
+
+VS_EXPORT int64_t vs_spmm_workspace_bytes(int m_vec, int vec_length, int n, int batch, int64_t stride_values) {
+    if (m_vec <= 0 || n <= 0 || batch < 1 || !(vec_length == 2 || vec_length == 4 || vec_length == 8)) return 0;
+    const int64_t bytes = spmm_plan_bytes(m_vec, vec_length, n, batch, stride_values, nullptr, nullptr);
+    return bytes <= kMaxPlanBytes ? bytes : 0;
+}
+
+VS_EXPORT int64_t vs_sddmm_workspace_bytes(int m_vec, int n, int nonzeros_vec) {
+    if (m_vec <= 0 || n <= 0 || nonzeros_vec <= 0) return 0;
+    const int64_t bytes = sddmm_plan_bytes(m_vec, n, nonzeros_vec, nullptr);
+    return bytes <= kMaxPlanBytes ? bytes : 0;
+}
+
+VS_EXPORT int vs_set_workspace(void *workspace, int64_t bytes) {
+    if (bytes < 0 || (workspace == nullptr && bytes != 0)) return VS_ERR_ARG;
+    if (!aligned16(workspace)) return VS_ERR_ALIGN;
+    t_ws_set = workspace != nullptr;
+    t_ws_ptr = workspace;
+    t_ws_bytes = bytes;
     return VS_OK;
 }
 

@@ -173,6 +173,15 @@ def attention_cvse(path, m_vec, vec_length, n, d, nonzeros_vec, row_indices, row
     return 0
 
 
+def set_workspace(buffer=None) -> None:
+    """Hands the tensor-path kernels a caller-owned plan scratch (a CUDA uint8 tensor) for the calls of this host
+    thread, or returns to the library's own per-stream buffers (None).  See include/vsparse_b200.h."""
+    if buffer is None:
+        _lib.check(_lib.lib().vs_set_workspace(None, 0), "vs_set_workspace")
+    else:
+        _lib.check(_lib.lib().vs_set_workspace(buffer.data_ptr(), buffer.numel() * buffer.element_size()), "vs_set_workspace")
+
+
 def device_status(clear: bool = True) -> int:
     """Status word of the current device: 0 unless a kernel gave up on a bounded wait."""
     import ctypes as C
