@@ -183,6 +183,9 @@ template <typename T, int V> struct EntryWords {  // one entry = V values of T =
     __device__ __forceinline__ static void store(T *p, const float (&f)[V]) {
         uint32_t w[kWords];
         pack(f, w);
+        store_words(p, w);
+    }
+    __device__ __forceinline__ static void store_words(T *p, const uint32_t (&w)[kWords]) {
         if constexpr (kBytes == 4) {
             *reinterpret_cast<uint32_t *>(p) = w[0];
         } else if constexpr (kBytes == 8) {
@@ -215,21 +218,59 @@ __global__ void __launch_bounds__(kCcThreads) softmax_cvse_kernel(const SoftmaxP
     if constexpr (kCache > 0) {
         if (end - beg <= 32 * kCache) {
             uint32_t cache[kCache][EW::kWords];
+            // fp16 scores with a non-negative scale: the row maxima are taken on the packed halves (the maximum
+            // commutes with the scaling) and only the V results are widened; conversions are what this kernel
+            // spends its time on
+            constexpr bool kPacked = sizeof(T) == 2 && V >= 2;
+            const bool packed_max = kPacked && p.scale >= 0.0f;
+            if (packed_max) {
+                uint32_t m2[EW::kWords];
+                const __half2 lowest = __floats2half2_rn(-INFINITY, -INFINITY);
 #pragma unroll
-            for (int c = 0; c < kCache; ++c) {
-                const int j = beg + lane + 32 * c;
-                if (j < end) {
-                    EW::load(s + (int64_t)j * V, cache[c]);
-                    float f[V];
-                    EW::unpack(cache[c], f);
+                for (int q = 0; q < EW::kWords; ++q) m2[q] = *reinterpret_cast<const uint32_t *>(&lowest);
 #pragma unroll
-                    for (int v = 0; v < V; ++v) mx[v] = fmaxf(mx[v], p.scale * f[v]);
+                for (int c = 0; c < kCache; ++c) {
+                    const int j = beg + lane + 32 * c;
+                    if (j < end) {
+                        EW::load(s + (int64_t)j * V, cache[c]);
+#pragma unroll
+                        for (int q = 0; q < EW::kWords; ++q) {
+                            const __half2 h = __hmax2(*reinterpret_cast<const __half2 *>(&m2[q]), *reinterpret_cast<const __half2 *>(&cache[c][q]));
+                            m2[q] = *reinterpret_cast<const uint32_t *>(&h);
+                        }
+                    }
                 }
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+                    for (int q = 0; q < EW::kWords; ++q) {
+                        const uint32_t other = __shfl_xor_sync(0xffffffffu, m2[q], off);
+                        const __half2 h = __hmax2(*reinterpret_cast<const __half2 *>(&m2[q]), *reinterpret_cast<const __half2 *>(&other));
+                        m2[q] = *reinterpret_cast<const uint32_t *>(&h);
+                    }
+                if constexpr (kPacked) {
+                    float f[V];
+                    EW::unpack(m2, f);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) mx[v] = p.scale * f[v];
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < kCache; ++c) {
+                    const int j = beg + lane + 32 * c;
+                    if (j < end) {
+                        EW::load(s + (int64_t)j * V, cache[c]);
+                        float f[V];
+                        EW::unpack(cache[c], f);
+#pragma unroll
+                        for (int v = 0; v < V; ++v) mx[v] = fmaxf(mx[v], p.scale * f[v]);
+                    }
+                }
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+                    for (int v = 0; v < V; ++v) mx[v] = fmaxf(mx[v], __shfl_xor_sync(0xffffffffu, mx[v], off));
             }
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1)
-#pragma unroll
-                for (int v = 0; v < V; ++v) mx[v] = fmaxf(mx[v], __shfl_xor_sync(0xffffffffu, mx[v], off));
             // exponentials are computed once (exp2 of a pre-scaled argument), kept in the cache in the element
             // type, and scaled by 1 / sum on the way out
             const float sl2 = p.scale * 1.4426950408889634f;
@@ -256,15 +297,34 @@ __global__ void __launch_bounds__(kCcThreads) softmax_cvse_kernel(const SoftmaxP
             float inv[V];
 #pragma unroll
             for (int v = 0; v < V; ++v) inv[v] = 1.0f / sum[v];
+            if constexpr (kPacked) {
+                // the cached exponentials are already fp16: scale them there (two more roundings of 2^-11,
+                // well inside the stated tolerance) instead of widening and narrowing every value again
+                uint32_t inv2[EW::kWords];
+                EW::pack(inv, inv2);
 #pragma unroll
-            for (int c = 0; c < kCache; ++c) {
-                const int j = beg + lane + 32 * c;
-                if (j < end) {
-                    float f[V];
-                    EW::unpack(cache[c], f);
+                for (int c = 0; c < kCache; ++c) {
+                    const int j = beg + lane + 32 * c;
+                    if (j < end) {
 #pragma unroll
-                    for (int v = 0; v < V; ++v) f[v] *= inv[v];
-                    EW::store(o + (int64_t)j * V, f);
+                        for (int q = 0; q < EW::kWords; ++q) {
+                            const __half2 h = __hmul2(*reinterpret_cast<const __half2 *>(&cache[c][q]), *reinterpret_cast<const __half2 *>(&inv2[q]));
+                            cache[c][q] = *reinterpret_cast<const uint32_t *>(&h);
+                        }
+                        EW::store_words(o + (int64_t)j * V, cache[c]);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < kCache; ++c) {
+                    const int j = beg + lane + 32 * c;
+                    if (j < end) {
+                        float f[V];
+                        EW::unpack(cache[c], f);
+#pragma unroll
+                        for (int v = 0; v < V; ++v) f[v] *= inv[v];
+                        EW::store(o + (int64_t)j * V, f);
+                    }
                 }
             }
             return;
