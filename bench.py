@@ -43,6 +43,8 @@ WORKLOADS = {
     "spmm_v4_s90": dict(op="spmm", M=2048, K=512, V=4, s=0.9, N=256, inst=256, kind="beta"),
     "spmm_v2_s90": dict(op="spmm", M=2048, K=512, V=2, s=0.9, N=256, inst=256, kind="beta"),
     "sddmm_v8_s90": dict(op="sddmm", M=2048, K=512, V=8, s=0.9, N=256, inst=256, kind="beta"),
+    # product with the transposed sparse matrix (vs_spmm_t): out [K x N] = A^T . rhs, rhs [M x N]
+    "spmm_t_v8_s90": dict(op="spmm_t", M=2048, K=512, V=8, s=0.9, N=256, inst=256, kind="beta"),
     "spmm_cc_v8_s90": dict(op="spmm", M=2048, K=512, V=8, s=0.9, N=256, inst=256, kind="beta", path=1),
     # fp32 CUDA-core SpMM (the cudaSpmm entry point), M = K = 4096, uniform random positions, values and B U(-1,1)
     "spmm_f32_v4_s90_n1024": dict(op="spmm", M=4096, K=4096, V=4, s=0.9, N=1024, inst=8, kind="uniform", path=1, dtype="f32"),
@@ -61,6 +63,8 @@ NCU_TRAFFIC_BYTES = {
 def kernels_per_step(w, a=None):
     """Names of the library's kernels one step launches (the count is what `gpu_launches` reports)."""
     tensor = w.get("path") != 1
+    if w["op"] == "spmm_t":
+        return ["spmm_t_kernel"]
     if w["op"] == "spmm" and tensor:
         if os.environ.get("VSPARSE_B200_SPMM") == "gather":
             return ["spmm_tma_kernel"]
@@ -144,6 +148,11 @@ def algorithmic(w, a):
         k_touched = int(np.unique(a.col_indices).size)
         per = nnz_vec * V * es + k_touched * w["N"] * es + w["M"] * w["N"] * es
         flops = 2.0 * nnz_vec * V * w["N"]
+    elif w["op"] == "spmm_t":  # rhs M x N (the rows of nonempty vector-rows), out K x N
+        rows_touched = int(np.count_nonzero(np.diff(a.row_offsets))) * V
+        per = nnz_vec * V * es + rows_touched * w["N"] * es + w["K"] * w["N"] * es
+        flops = 2.0 * nnz_vec * V * w["N"]
+        structure = nnz_vec * 8 + (w["K"] + 1) * 4   # t_rows, t_src, t_offsets
     else:  # sddmm: lhs M x k, rhs K x k, out nnz
         k = w["N"]
         n_touched = int(np.unique(a.col_indices).size)
@@ -186,6 +195,16 @@ def run_ours(args):
 
         def launch(d_a, d_b, out):
             ops.spmm_batched(path, a.m_vec, V, N, K, ri, ro, ci, d_a, d_b, out)
+    elif w["op"] == "spmm_t":
+        row = (a.nnz_vec * V + 7) // 8 * 8
+        t_off, t_rows, t_src = (torch.from_numpy(x).to(dev) for x in cvse.transpose(a))
+        h_a = torch.from_numpy(cvse.fill_random((inst, row), np.float16, cvse.DIST_NORMAL, seed, 0.02)).pin_memory()
+        h_b = torch.from_numpy(cvse.fill_random((inst, M, N), np.float16, cvse.DIST_NORMAL, seed + 1, 1.0)).pin_memory()
+        h_out = torch.empty((inst, K, N), dtype=torch.float16).pin_memory()
+        d_out = torch.empty((inst, K, N), dtype=torch.float16, device=dev)
+
+        def launch(d_a, d_b, out):
+            ops.spmm_t(a.m_vec, V, N, K, t_off, t_rows, t_src, d_a, d_b, out)
     else:
         k = N
         h_a = torch.from_numpy(cvse.fill_random((inst, M, k), np.float16, cvse.DIST_NORMAL, seed, 1.0)).pin_memory()
@@ -306,7 +325,7 @@ def run_ours(args):
         h2d = h_a.numel() * h_a.element_size() + h_b.numel() * h_b.element_size()
         d2h = h_out.numel() * h_out.element_size()
         line = {
-            "metric": "SpMM effective TFLOP/s (2*nnz*N)" if w["op"] == "spmm" else "SDDMM effective TFLOP/s (2*nnz*k)",
+            "metric": "SDDMM effective TFLOP/s (2*nnz*k)" if w["op"] == "sddmm" else "SpMM effective TFLOP/s (2*nnz*N)",
             "value": flops * args.steps * world / (total_ms * 1e-3) / 1e12,
             "unit": "TFLOP/s",
             "n_gpus": world,
@@ -320,7 +339,7 @@ def run_ours(args):
             "data": "synthetic",
             "config": {"workload": args.workload, "op": w["op"], "M": M, "K": K, "V": V, "sparsity": w["s"],
                        "dense_width_or_k": N, "nnz_vec": a.nnz_vec, "instances_per_step": inst,
-                       "path": "cuda-core" if path == VS_PATH_CUDA_CORE else "tensor (tcgen05)",
+                       "path": "cuda-core" if path == VS_PATH_CUDA_CORE or w["op"] == "spmm_t" else "tensor (tcgen05)",
                        "l2": "working set 3x L2 (distinct operands per instance), no flush needed",
                        "parallelism": f"independent streams x{world}"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
@@ -365,6 +384,14 @@ def cpu_leg(w, a, budget_s, threads=None):
             if use_ref:
                 return oracle.ref_spmm(a.m_vec, V, N, a.row_offsets, a.col_indices, x, y)
             return oracle.spmm(a.m_vec, V, N, a.row_offsets, a.col_indices, x, y, acc="f32", threads=1)
+    elif w["op"] == "spmm_t":   # no reference code for this product: the oracle's loop is the CPU path
+        use_ref = False
+        x = cvse.fill_random((a.nnz_vec * V,), np.float16, cvse.DIST_NORMAL, 1, 0.02).astype(np.float32)
+        y = cvse.fill_random((M, N), np.float16, cvse.DIST_NORMAL, 2, 1.0).astype(np.float32)
+        flops = 2.0 * a.nnz_vec * V * N
+
+        def one(_):
+            return oracle.spmm_t(a.m_vec, V, N, K, a.row_offsets, a.col_indices, x, y)
     else:
         k = N
         x = cvse.fill_random((M, k), np.float16, cvse.DIST_NORMAL, 1, 1.0)
@@ -407,13 +434,15 @@ def run_reference(args):
     base["value"] = v
     line = {
         "impl": "reference",
-        "metric": "SpMM effective TFLOP/s (2*nnz*N)" if w["op"] == "spmm" else "SDDMM effective TFLOP/s (2*nnz*k)",
+        "metric": "SDDMM effective TFLOP/s (2*nnz*k)" if w["op"] == "sddmm" else "SpMM effective TFLOP/s (2*nnz*N)",
         "value": v, "unit": "TFLOP/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": steps,
         "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
         "config": {"workload": args.workload, "op": w["op"], "M": w["M"], "K": w["K"], "V": w["V"],
                    "sparsity": w["s"], "dense_width_or_k": w["N"], "nnz_vec": a.nnz_vec,
-                   "instances_per_step": w["inst"], "path": "host loop (spmm_benchmark.cpp:66-86)"},
+                   "instances_per_step": w["inst"], "path": "host loop (spmm_benchmark.cpp:66-86)" if w["op"] == "spmm" else
+                   "host loop (include/bm_test_utils.h:171-193)" if w["op"] == "sddmm" else
+                   "host loop of the oracle (the reference has no transposed product)"},
         "cpu_baseline": base,
         "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,

@@ -90,6 +90,30 @@ int vs_spmm_batched(int path, int in_dtype, int out_dtype, int m_vec, int vec_le
                     int64_t stride_values, int64_t stride_rhs, int64_t stride_out, void *stream);
 
 /* ------------------------------------------------------------------------------------------------------
+ * SpMM with the transposed sparse matrix:  out[n x k] = A^T . rhs,  A the m_vec*V x n CVSE matrix, rhs m_vec*V x k.
+ *
+ *   out[c*k + l] = sum over the nonzero vectors (i, j) with col_indices[j] == c of
+ *                  sum_v values[j*V+v] * rhs[(i*V+v)*k + l];       every row of out written (zeros for a column
+ *                                                                   no vector names)
+ *
+ * No counterpart in the reference, whose kernels cover the forward products (src/wmma_spmm.cu,
+ * src/cuda_spmm.cu); this is the product on the other side of them in a training step of fixed-mask sparse
+ * attention (dV = P^T dO, dK = dS^T Q), kept to the conventions of vs_spmm: device pointers, caller-owned
+ * buffers, asynchronous on `stream`, nothing allocated.  `values` is the SAME array the forward operators use;
+ * only the structure is transposed, once, on the host, by vs_cvse_transpose below.
+ * (in_dtype, out_dtype): (F16,F16), (F16,F32); fp32 accumulation in the listed order (reproducible).
+ * vec_length in {1,2,4,8}; k % 8 == 0; values, rhs, out 16-byte aligned.  CUDA cores (one warp per 256 columns
+ * of an output row).  The batched form shares the structure and strides values / rhs / out as vs_spmm_batched.
+ * ---------------------------------------------------------------------------------------------------- */
+int vs_spmm_t(int in_dtype, int out_dtype, int m_vec, int vec_length, int k, int n, const int32_t *t_offsets,
+              const int32_t *t_rows, const int32_t *t_src, const void *values, const void *rhs_matrix,
+              void *output_matrix, void *stream);
+int vs_spmm_t_batched(int in_dtype, int out_dtype, int m_vec, int vec_length, int k, int n, const int32_t *t_offsets,
+                      const int32_t *t_rows, const int32_t *t_src, const void *values, const void *rhs_matrix,
+                      void *output_matrix, int batch, int64_t stride_values, int64_t stride_rhs, int64_t stride_out,
+                      void *stream);
+
+/* ------------------------------------------------------------------------------------------------------
  * SDDMM.  Replaces sddmm::wmmaSddmm (include/wmma_sddmm.cuh:7-33, path = VS_PATH_TENSOR) and
  * sddmm::cudaSddmm (include/cuda_sddmm.cuh:7-32, path = VS_PATH_CUDA_CORE; `algorithm` ignored).
  *
@@ -257,6 +281,24 @@ int vs_smtx_write(const char *path, int rows, int cols, int nnz, const int32_t *
  * count only (row_offsets is still filled).  Returns nonzeros_vec or a negative error. */
 int vs_cvse_from_dense_mask(int m_vec, int n, const uint8_t *mask, int32_t *row_offsets,
                             int32_t *col_indices);
+
+/* HOST.  Structure of A^T for vs_spmm_t: for each column c of A, t_offsets[c] .. t_offsets[c+1] delimit its
+ * nonzero vectors in t_rows (vector-row i, ascending) and t_src (index j of the vector in col_indices / values).
+ * t_offsets holds n + 1 ints, t_rows and t_src nonzeros_vec each.  The input is validated first
+ * (VS_ERR_STRUCTURE).  No counterpart in the reference. */
+int vs_cvse_transpose(int m_vec, int n, int nonzeros_vec, const int32_t *row_offsets, const int32_t *col_indices,
+                      int32_t *t_offsets, int32_t *t_rows, int32_t *t_src);
+
+/* Vector-wise magnitude pruning of a dense row-major weight [m_vec * vec_length x n] (fp32) into CVSE: every
+ * vec_length x 1 column vector is scored by the sum of its absolute values and the highest-scoring vectors are
+ * kept — scope 0: round((1 - sparsity) * m_vec * n) of them over the whole matrix; scope 1: round((1 -
+ * sparsity) * n) in every vector-row.  Ties go to the lower (vector-row, column).  Two-call protocol like the
+ * generators: col_indices == NULL fills row_offsets and returns nonzeros_vec; the second call fills col_indices
+ * (ascending within a row) and, when `values` is not NULL, the kept weights in the CVSE value layout
+ * (values[j * vec_length + v]).  The reference has no pruning step: it reads patterns pruned elsewhere (DLMC
+ * .smtx files, spmm_benchmark.cpp:21-54); this is the way in for a weight held in memory. */
+int vs_cvse_prune_dense(int m_vec, int n, int vec_length, const float *weight, double sparsity, int scope,
+                        int32_t *row_offsets, int32_t *col_indices, float *values);
 
 /* Seeded pattern generators; two-call protocol: col_indices == NULL fills row_offsets and returns nnz_vec,
  * the second call (same arguments) fills col_indices too.  Columns ascend within a row.

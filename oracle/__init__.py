@@ -98,6 +98,17 @@ def spmm(m_vec, V, N, row_offsets, col_indices, values, B, acc="f64", threads=1)
     return out
 
 
+def spmm_t(m_vec, V, N, K, row_offsets, col_indices, values, B):
+    """C[K, N] = A(CVSE)^T @ B, B [m_vec * V, N]; fp64 accumulation.  No reference counterpart (see vs_oracle.c)."""
+    ro, rop = _i32(row_offsets)
+    ci, cip = _i32(col_indices)
+    v, vp = _f32(np.asarray(values, dtype=np.float32))
+    b, bp = _f32(np.asarray(B, dtype=np.float32))
+    out = np.empty((K, N), dtype=np.float64)
+    lib().vso_spmm_t_f64(m_vec, V, N, K, rop, cip, vp, bp, out.ctypes.data_as(_F64P))
+    return out
+
+
 def sddmm(m_vec, k, V, row_offsets, col_indices, lhs, rhs, acc="f64", threads=1):
     """out[j*V+v] = <lhs[i*V+v], rhs[col[j]]>.  acc='f32' is Host_sddmm (bm_test_utils.h:171-193)."""
     ro, rop = _i32(row_offsets)

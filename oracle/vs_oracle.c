@@ -169,6 +169,24 @@ VSO_API void vso_spmm_f64(int m_vec, int V, int N, const int *row_offsets, const
     }
 }
 
+/* Transposed product, C[K x N] = A^T B with B [m_vec*V x N]: the loop of spmm_benchmark.cpp:66-86 with the roles of
+ * the row index (i*V+v) and the column index swapped.  The reference has no such operator, so this function is
+ * pinned only by its agreement with vso_spmm_f64 on an explicitly transposed matrix (tests). */
+VSO_API void vso_spmm_t_f64(int m_vec, int V, int N, int K, const int *row_offsets, const int *col_indices,
+                            const float *values, const float *B, double *C) {
+    memset(C, 0, sizeof(double) * (size_t)K * N);
+    for (int i = 0; i < m_vec; ++i) {
+        for (int j = row_offsets[i]; j < row_offsets[i + 1]; ++j) {
+            double *c = C + (size_t)col_indices[j] * N;
+            for (int v = 0; v < V; ++v) {
+                double a = (double)values[(size_t)j * V + v];
+                const float *b = B + ((size_t)i * V + v) * N;
+                for (int l = 0; l < N; ++l) c[l] += a * (double)b[l];
+            }
+        }
+    }
+}
+
 /* ---- SDDMM: out[j*V+v] = <lhs[i*V+v, :], rhs[col[j], :]>  (bm_test_utils.h:171-193) --------------- */
 
 VSO_API void vso_sddmm_f32(int m_vec, int k, int V, const int *row_offsets, const int *col_indices,

@@ -156,3 +156,19 @@ def test_caller_owned_workspace(monkeypatch):
         assert np.all(tail == poison), "wrote past the end of the caller's workspace"
         used = bool((ws[:size].cpu().numpy() != poison).any())
         assert used == (size == need), "the plan must live in the caller's buffer exactly when it fits"
+
+
+def test_duplicate_columns_in_a_vector_row_are_added(monkeypatch):
+    """The reference's generator can pad a row with a column it already holds (include/bm_test_utils.h:70-127);
+    its kernels add both values.  A dense tile has one place per (row, column), so the plan kernel reports such
+    matrices and the gather kernel takes the call."""
+    V, N = 8, 64
+    a = custom([6, 0, 9, 4], 96, V, seed=3)
+    ci = a.col_indices.copy()
+    ci[1] = ci[0]                                  # vector-row 0 names its first column twice
+    ci[a.row_offsets[2] + 5] = ci[a.row_offsets[2] + 2]
+    dup = cvse.CVSE(a.m_vec, a.n, V, a.row_offsets, ci, a.row_indices)
+    vals, B = spmm_inputs(dup, N, np.float16, 12, sigma=1.0)
+    want = spmm_oracle(dup, N, vals, B)
+    for mode in ("dense", "gather", None):
+        assert_close(run(dup, N, vals, B, torch.float32, mode, monkeypatch), want, f"duplicate columns, {mode}")

@@ -134,3 +134,45 @@ def test_dense_mask_round_trip():
     dense = a.to_dense(vals)
     assert dense.shape == (68, 33)
     assert np.array_equal((dense.reshape(17, 4, 33) != 0).all(axis=1), mask)
+
+
+@pytest.mark.parametrize("V", [1, 2, 4, 8])
+@pytest.mark.parametrize("per_row", [False, True])
+def test_prune_dense_keeps_the_heaviest_vectors(V, per_row):
+    rng = np.random.default_rng(10 + V)
+    m_vec, n, s = 12, 40, 0.8
+    w = rng.standard_normal((m_vec * V, n)).astype(np.float32)
+    a, vals = cvse.prune_dense(w, V, s, per_row=per_row)
+    a.validate()
+    score = np.abs(w.astype(np.float64)).reshape(m_vec, V, n).sum(axis=1)
+    if per_row:
+        keep = int(round((1 - s) * n))
+        assert np.all(np.diff(a.row_offsets) == keep)
+        for i in range(m_vec):
+            cols = a.col_indices[a.row_offsets[i]:a.row_offsets[i + 1]]
+            assert np.all(np.diff(cols) > 0)
+            assert set(cols) == set(np.argsort(-score[i], kind="stable")[:keep])
+    else:
+        keep = int(round((1 - s) * m_vec * n))
+        assert a.nnz_vec == keep
+        best = set(np.argsort(-score.ravel(), kind="stable")[:keep])
+        got = {i * n + int(c) for i in range(m_vec) for c in a.col_indices[a.row_offsets[i]:a.row_offsets[i + 1]]}
+        assert got == best
+    # the values are the kept weights in the CVSE layout, so the dense expansion is the masked weight
+    dense = a.to_dense(vals)
+    mask = np.repeat((a.to_dense(np.ones(a.nnz_vec * V, np.float32)) != 0), 1, axis=0)
+    assert np.array_equal(dense, np.where(mask, w, 0).astype(np.float32))
+
+
+def test_prune_dense_edges():
+    w = np.ones((8, 5), np.float32)
+    a, vals = cvse.prune_dense(w, 4, 1.0)          # everything pruned
+    assert a.nnz_vec == 0 and vals.size == 0 and np.all(a.row_offsets == 0)
+    a, vals = cvse.prune_dense(w, 4, 0.0)          # nothing pruned
+    assert a.nnz_vec == 10 and np.array_equal(a.to_dense(vals), w)
+    a, _ = cvse.prune_dense(w, 4, 0.5)             # all scores tie: the lower (vector-row, column) wins
+    assert a.nnz_vec == 5 and list(np.diff(a.row_offsets)) == [5, 0]
+    with pytest.raises(VsError):
+        cvse.prune_dense(w, 4, 1.5)
+    with pytest.raises(ValueError):
+        cvse.prune_dense(np.ones((6, 5), np.float32), 4, 0.5)

@@ -36,6 +36,8 @@ SIGNATURES = {
     "vs_version": (C.c_char_p, []),
     "vs_spmm": (_i, [_i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "vs_spmm_batched": (_i, [_i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i64, _vp]),
+    "vs_spmm_t": (_i, [_i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "vs_spmm_t_batched": (_i, [_i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i64, _vp]),
     "vs_sddmm": (_i, [_i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i]),
     "vs_sddmm_batched": (_i, [_i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i64, _i64, _i64, _vp, _i]),
     "vs_softmax_cvse": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _f, _i, _i64, _vp]),
@@ -56,6 +58,8 @@ SIGNATURES = {
     "vs_smtx_read": (_i, [C.c_char_p, _i, _i, _vp, _vp]),
     "vs_smtx_write": (_i, [C.c_char_p, _i, _i, _i, _vp, _vp]),
     "vs_cvse_from_dense_mask": (_i, [_i, _i, _vp, _vp, _vp]),
+    "vs_cvse_transpose": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "vs_cvse_prune_dense": (_i, [_i, _i, _i, _vp, C.c_double, _i, _vp, _vp, _vp]),
     "vs_cvse_generate": (_i, [_i, C.c_uint64, _i, _i, _i, C.c_double, _i, _vp, _vp]),
     "vs_fill_random": (_i, [_i, _i, C.c_uint64, C.c_double, _i64, _vp]),
 }

@@ -21,6 +21,18 @@ struct SpmmParams {
     int64_t stride_values, stride_rhs, stride_out;  // in elements
 };
 
+// Header of the plan scratch of the densifying SpMM, read by the kernels enqueued behind the plan kernel:
+// word 0 = the plan kernel chose the dense kernel; words 4 .. 4 + checks = one verdict per duplicate-checking CTA
+// of the plan kernel, set when it met the same column twice in one vector-row (the dense tile would keep one of
+// the two values, the reference adds them: such matrices go to the gather kernel).  Block-uniform result; every
+// thread of the block must call it.
+__device__ __forceinline__ bool plan_dense_chosen(const int32_t *hdr, int checks) {
+    if (*reinterpret_cast<const volatile int32_t *>(hdr) == 0) return false;
+    int dup = 0;
+    for (int i = threadIdx.x; i < checks; i += blockDim.x) dup |= hdr[4 + i];
+    return __syncthreads_or(dup) == 0;
+}
+
 struct SddmmParams {
     int m_vec;
     int k;           // contraction length

@@ -1,5 +1,5 @@
 // Host side of the CVSE format: validator, row swizzle (load balancer), .smtx reader/writer, dense-mask
-// converter and the seeded pattern / value generators.  Plain C++ on host arrays; no CUDA here.
+// converter, magnitude pruning of a dense weight and the seeded pattern / value generators.  Plain C++ on host arrays; no CUDA here.
 //
 // The reference keeps this logic inline in its drivers and in include/bm_test_utils.h:
 //   .smtx parsing               spmm_benchmark.cpp:21-54, sddmm_benchmark.cpp:172-206
@@ -199,6 +199,83 @@ VS_EXPORT int vs_cvse_from_dense_mask(int m_vec, int n, const uint8_t *mask, int
                 ++off;
             }
         if (off > INT32_MAX) return VS_ERR_SHAPE;
+        row_offsets[i + 1] = (int32_t)off;
+    }
+    return (int)off;
+}
+
+// ---- structure of the transposed matrix -----------------------------------------------------------------------
+
+VS_EXPORT int vs_cvse_transpose(int m_vec, int n, int nonzeros_vec, const int32_t *row_offsets,
+                                const int32_t *col_indices, int32_t *t_offsets, int32_t *t_rows, int32_t *t_src) {
+    if (m_vec < 0 || n < 0 || nonzeros_vec < 0) return VS_ERR_SHAPE;
+    if (!row_offsets || !t_offsets || (nonzeros_vec > 0 && (!col_indices || !t_rows || !t_src))) return VS_ERR_NULL;
+    const int rc = vs_cvse_validate(m_vec, n, nonzeros_vec, row_offsets, col_indices);
+    if (rc != VS_OK) return rc;
+    // counting sort by column; walking the vector-rows in order keeps each column's entries ascending in i
+    std::vector<int32_t> cursor((size_t)n + 1, 0);
+    for (int j = 0; j < nonzeros_vec; ++j) ++cursor[(size_t)col_indices[j] + 1];
+    t_offsets[0] = 0;
+    for (int c = 0; c < n; ++c) {
+        cursor[c + 1] += cursor[c];
+        t_offsets[c + 1] = cursor[c + 1];
+    }
+    for (int i = 0; i < m_vec; ++i)
+        for (int j = row_offsets[i]; j < row_offsets[i + 1]; ++j) {
+            const int32_t at = cursor[col_indices[j]]++;
+            t_rows[at] = i;
+            t_src[at] = j;
+        }
+    return VS_OK;
+}
+
+// ---- magnitude pruning of a dense weight ----------------------------------------------------------------------
+
+VS_EXPORT int vs_cvse_prune_dense(int m_vec, int n, int vec_length, const float *weight, double sparsity, int scope,
+                                  int32_t *row_offsets, int32_t *col_indices, float *values) {
+    if (m_vec < 0 || n < 0) return VS_ERR_SHAPE;
+    if (!weight || !row_offsets) return VS_ERR_NULL;
+    if (!(sparsity >= 0.0 && sparsity <= 1.0) || (scope != 0 && scope != 1)) return VS_ERR_ARG;
+    if (vec_length != 1 && vec_length != 2 && vec_length != 4 && vec_length != 8) return VS_ERR_VEC_LENGTH;
+    const int V = vec_length;
+    const int64_t slots = (int64_t)m_vec * n;
+    if (slots > INT32_MAX) return VS_ERR_SHAPE;
+    std::vector<double> score((size_t)slots);
+    for (int i = 0; i < m_vec; ++i)
+        for (int c = 0; c < n; ++c) {
+            double s = 0.0;
+            for (int v = 0; v < V; ++v) s += std::fabs((double)weight[((size_t)i * V + v) * n + c]);
+            score[(size_t)i * n + c] = s;
+        }
+    std::vector<uint8_t> keep((size_t)slots, 0);
+    std::vector<int32_t> order;
+    // the `want` best slots of [lo, hi): by score descending, ties by ascending slot number
+    auto mark_best = [&](int64_t lo, int64_t hi, int64_t want) {
+        order.resize((size_t)(hi - lo));
+        std::iota(order.begin(), order.end(), (int32_t)lo);
+        want = std::min<int64_t>(want, hi - lo);
+        auto better = [&](int32_t a, int32_t b) { return score[a] != score[b] ? score[a] > score[b] : a < b; };
+        std::partial_sort(order.begin(), order.begin() + want, order.end(), better);
+        for (int64_t q = 0; q < want; ++q) keep[order[q]] = 1;
+    };
+    if (scope == 0) {
+        mark_best(0, slots, (int64_t)std::llround((1.0 - sparsity) * (double)slots));
+    } else {
+        const int64_t per_row = (int64_t)std::llround((1.0 - sparsity) * (double)n);
+        for (int i = 0; i < m_vec; ++i) mark_best((int64_t)i * n, (int64_t)(i + 1) * n, per_row);
+    }
+    int64_t off = 0;
+    row_offsets[0] = 0;
+    for (int i = 0; i < m_vec; ++i) {
+        for (int c = 0; c < n; ++c) {
+            if (!keep[(size_t)i * n + c]) continue;
+            if (col_indices) {
+                col_indices[off] = c;
+                if (values)
+                    for (int v = 0; v < V; ++v) values[off * V + v] = weight[((size_t)i * V + v) * n + c];
+            }
+            ++off;
+        }
         row_offsets[i + 1] = (int32_t)off;
     }
     return (int)off;

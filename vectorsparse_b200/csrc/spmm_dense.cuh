@@ -69,6 +69,8 @@ constexpr int kTmemCols = 2 * kAccCols;                  // 512
 constexpr int kStoreCols = 32;                           // output box of one epilogue warp: 32 rows x 32 columns
 constexpr int kStoreBoxBytes = 32 * 128;                 // staging per epilogue warp: two fp16 boxes or one fp32 box
 constexpr int kPlanThreads = 256;
+constexpr int kPlanWarps = kPlanThreads / 32;
+constexpr int kMaxCheckCtas = 256;                       // CTAs of the plan kernel that look for repeated columns
 
 constexpr uint32_t kStatusTimeout = 64u;  // bit raised in the status word when a bounded wait ran out
 
@@ -92,10 +94,16 @@ static_assert(kBStages == kAStages || kBStages == 2 * kAStages,
               "the stage barriers are shared: a fill warp must see every phase of the barriers it waits on");
 
 // ---- plan -------------------------------------------------------------------------------------------------
-// One CTA per 128-row group (128 / V vector-rows, whose nonzero vectors are contiguous in the CVSE arrays).
-// blk_offsets[g * (plan_blocks + 1) + c] .. [.. + c + 1] delimit the entries of group g in the 32-column block
-// c; entry = (vector index j, (vector-row within the group << 6) | column within the 64-column stage).  Columns
-// outside [0, K) are dropped (the gather kernels read zeros for them).
+// CTAs 0 .. groups-1: one per 128-row group (128 / V vector-rows, whose nonzero vectors are contiguous in the
+// CVSE arrays).  blk_offsets[g * (plan_blocks + 1) + c] .. [.. + c + 1] delimit the entries of group g in the
+// 32-column block c; entry = (vector index j, (vector-row within the group << 6) | column within the 64-column
+// stage).  Columns outside [0, K) are dropped (the gather kernels read zeros for them).
+//
+// CTAs groups .. gridDim.x-1 look for a column that appears twice in one vector-row (the reference's generator
+// pads rows that way, include/bm_test_utils.h:110-124): a dense tile has one place per (row, column), the
+// reference's kernels add both values, so such a matrix must go to the gather kernel.  A warp takes a vector-row
+// at a time and marks its columns in a bitmap of its own in shared memory; each of these CTAs writes its verdict
+// to its own word behind *use_dense (use_dense[4 + i]), so nothing has to be cleared between calls.
 //
 // The kernel also takes the decision between the densifying and the gather kernels, because the number of
 // nonzero vectors is only known here.  Costs in cycles of one SM per 128 columns of B, fitted to measurements
@@ -105,17 +113,39 @@ static_assert(kBStages == kAStages || kBStages == 2 * kAStages,
 // in *use_dense for the two kernels enqueued behind this one, and nothing is planned when the answer is no.
 __global__ void __launch_bounds__(kPlanThreads)
 dense_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__restrict__ col_indices, int m_vec, int K,
-                  int rows_per_group, int plan_blocks, int32_t *__restrict__ blk_offsets, uint2 *__restrict__ blk_entries,
-                  int64_t entry_capacity, int force_dense, int32_t *use_dense) {
+                  int groups, int rows_per_group, int plan_blocks, int32_t *__restrict__ blk_offsets,
+                  uint2 *__restrict__ blk_entries, int64_t entry_capacity, int force_dense, int32_t *use_dense) {
     extern __shared__ int plan_sh[];
     {
         const int64_t nnz = __ldg(row_offsets + m_vec);
-        const float stages = (float)(gridDim.x / (kTileM / kGroupRows)) * (float)(plan_blocks / (kBlockK / kPlanCols));
+        const float stages = (float)(groups / (kTileM / kGroupRows)) * (float)(plan_blocks / (kBlockK / kPlanCols));
         const float dense_cost = stages * 1100.0f;
         const float gather_cost = (float)m_vec * 370.0f + 4.7f * (float)nnz;
         const bool dense = nnz <= entry_capacity && (force_dense || dense_cost < gather_cost);
         if (blockIdx.x == 0 && threadIdx.x == 0) *use_dense = dense ? 1 : 0;
         if (!dense) return;
+    }
+    if ((int)blockIdx.x >= groups) {
+        const int check = blockIdx.x - groups, checks = gridDim.x - groups;
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        unsigned *seen = reinterpret_cast<unsigned *>(plan_sh) + warp * plan_blocks;   // one bit per column of the row in hand
+        int twice = 0;
+        for (int r = check * kPlanWarps + warp; r < m_vec; r += checks * kPlanWarps) {
+            const int e0 = __ldg(row_offsets + r), e1 = __ldg(row_offsets + r + 1);
+            if (e1 - e0 < 2) continue;
+            for (int i = lane; i < plan_blocks; i += 32) seen[i] = 0u;
+            __syncwarp();
+            for (int e = e0 + lane; e < e1; e += 32) {
+                const int c = __ldg(col_indices + e);
+                if ((unsigned)c >= (unsigned)K) continue;
+                const unsigned bit = 1u << (c & 31);
+                if (atomicOr(seen + (c >> 5), bit) & bit) twice = 1;   // of two lanes with one column, the later sees the earlier's bit
+            }
+            __syncwarp();
+        }
+        twice = __syncthreads_or(twice);
+        if (threadIdx.x == 0) use_dense[4 + check] = twice;
+        return;
     }
     int *hist = plan_sh;                         // [plan_blocks]
     int *cursor = plan_sh + plan_blocks;         // [plan_blocks]
@@ -270,8 +300,11 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_b4, int use_b4,
                   const int32_t *__restrict__ blk_offsets,
                   const uint2 *__restrict__ blk_entries, int m_tiles, int n_tiles, int k_blocks, uint32_t *status,
-                  int32_t *use_dense) {
-    if (*use_dense == 0) return;   // the plan kernel chose the gather kernel for this matrix
+                  int32_t *use_dense, int plan_checks) {
+    // Not chosen (the gather kernel behind this one takes the call): the CTA still sets itself up and tears itself
+    // down, with no work items in between.  (An early return that depends on a barrier's result made the compiler
+    // treat the rest of the kernel as possibly divergent: 17 % slower.)
+    const bool chosen = plan_dense_chosen(use_dense, plan_checks);
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = tc::smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -311,7 +344,7 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
     tc::tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(sm + Smem::kTmemHolder);
 
-    const int64_t total_items = (int64_t)p.batch * n_tiles * m_tiles;
+    const int64_t total_items = chosen ? (int64_t)p.batch * n_tiles * m_tiles : 0;
     const int64_t G = gridDim.x;
     const uint32_t my_items = (total_items > blockIdx.x) ? (uint32_t)((total_items - blockIdx.x + G - 1) / G) : 0u;
     const uint32_t total_stages = my_items * (uint32_t)k_blocks;

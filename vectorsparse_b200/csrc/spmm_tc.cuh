@@ -131,8 +131,8 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
 }
 
 template <typename TOut, int V>
-__global__ void __launch_bounds__(kThreads, kCtasPerSm) spmm_tc_kernel(const SpmmParams p, uint32_t *status, const int32_t *skip_flag) {
-    if (skip_flag && *skip_flag) return;   // another kernel has taken this call (decided on the device)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) spmm_tc_kernel(const SpmmParams p, uint32_t *status, const int32_t *plan_hdr, int plan_checks) {
+    if (plan_hdr && plan_dense_chosen(plan_hdr, plan_checks)) return;   // the dense kernel has taken this call (decided on the device)
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = tc::smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;

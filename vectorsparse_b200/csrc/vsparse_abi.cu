@@ -22,6 +22,7 @@
 #include "spmm_tc.cuh"
 #include "spmm_tma.cuh"
 #include "spmm_dense.cuh"
+#include "spmm_t.cuh"
 #include "sddmm_tc.cuh"
 #include "sddmm_tma.cuh"
 #include "sddmm_dense.cuh"
@@ -210,7 +211,7 @@ template <typename TIn, typename TOut> int spmm_cc_by_v(int V, const SpmmParams 
 
 // Software (cp.async) gather: works for any batch stride.
 template <typename TOut, int V>
-int launch_spmm_tc_cpasync(const SpmmParams &p, cudaStream_t s, DeviceInfo *d, const int32_t *skip_flag = nullptr) {
+int launch_spmm_tc_cpasync(const SpmmParams &p, cudaStream_t s, DeviceInfo *d, const int32_t *plan_hdr = nullptr, int plan_checks = 0) {
     auto kernel = tcspmm::spmm_tc_kernel<TOut, V>;
     int rc = set_smem(kernel, tcspmm::kSmemBytes);
     if (rc != VS_OK) return rc;
@@ -218,15 +219,15 @@ int launch_spmm_tc_cpasync(const SpmmParams &p, cudaStream_t s, DeviceInfo *d, c
     const int64_t items = (int64_t)p.batch * n_tiles * p.m_vec;
     const int64_t cap = (int64_t)tcspmm::kCtasPerSm * d->sm_count;  // persistent CTAs
     const unsigned grid = (unsigned)(items < cap ? items : cap);
-    kernel<<<grid, tcspmm::kThreads, tcspmm::kSmemBytes, s>>>(p, d->status, skip_flag);
+    kernel<<<grid, tcspmm::kThreads, tcspmm::kSmemBytes, s>>>(p, d->status, plan_hdr, plan_checks);
     return (int)cudaGetLastError();
 }
 
 // TMA row gather: the dense operand of all batch entries must be addressable as one matrix of N-wide rows,
-// i.e. the batch stride is a multiple of N (or zero / a single entry).  With `skip_flag` the kernel returns at
-// once when the word it points to is non-zero (the densifying kernel has taken the call).
+// i.e. the batch stride is a multiple of N (or zero / a single entry).  With `plan_hdr` the kernel returns at
+// once when that plan header says that the densifying kernel has taken the call.
 template <typename TOut, int V>
-int launch_spmm_gather(const SpmmParams &p, cudaStream_t s, DeviceInfo *d, const int32_t *skip_flag) {
+int launch_spmm_gather(const SpmmParams &p, cudaStream_t s, DeviceInfo *d, const int32_t *plan_hdr, int plan_checks) {
     static const bool force_cpasync = []() {
         const char *e = std::getenv("VSPARSE_B200_GATHER");
         return e && !std::strcmp(e, "cpasync");
@@ -235,10 +236,10 @@ int launch_spmm_gather(const SpmmParams &p, cudaStream_t s, DeviceInfo *d, const
     const int64_t rows_per_batch = one ? 0 : p.stride_rhs / p.N;
     const int64_t total_rows = (one ? 0 : (int64_t)(p.batch - 1) * rows_per_batch) + p.K;
     const bool tma_ok = !force_cpasync && p.K > 0 && (one || p.stride_rhs % p.N == 0) && total_rows < 0x7fffffffll;
-    if (!tma_ok) return launch_spmm_tc_cpasync<TOut, V>(p, s, d, skip_flag);
+    if (!tma_ok) return launch_spmm_tc_cpasync<TOut, V>(p, s, d, plan_hdr, plan_checks);
     CUtensorMap map;
     int rc = make_gather_map(&map, p.rhs, (uint64_t)total_rows, (uint64_t)p.N);
-    if (rc != VS_OK) return launch_spmm_tc_cpasync<TOut, V>(p, s, d, skip_flag);
+    if (rc != VS_OK) return launch_spmm_tc_cpasync<TOut, V>(p, s, d, plan_hdr, plan_checks);
     auto kernel = tmaspmm::spmm_tma_kernel<TOut, V>;
     rc = set_smem(kernel, tmaspmm::kSmemBytes);
     if (rc != VS_OK) return rc;
@@ -247,7 +248,7 @@ int launch_spmm_gather(const SpmmParams &p, cudaStream_t s, DeviceInfo *d, const
     const int64_t cap = (int64_t)tmaspmm::kCtasPerSm * d->sm_count;  // persistent CTAs
     const unsigned grid = (unsigned)(items < cap ? items : cap);
     kernel<<<grid, tmaspmm::kThreads, tmaspmm::kSmemBytes, s>>>(p, map, (int)rows_per_batch, (int)total_rows, d->status,
-                                                                skip_flag);
+                                                                plan_hdr, plan_checks);
     return (int)cudaGetLastError();
 }
 
@@ -267,7 +268,13 @@ SpmmMode spmm_mode() {   // read at every call, so that a test can switch kernel
 }
 constexpr int64_t kMaxPlanBytes = 512ll << 20;
 
-// Bytes of plan scratch the densifying SpMM needs: a flag word, the bucket offsets, 8 bytes per possible entry.
+// Bytes of plan scratch the densifying SpMM needs: the header (verdict + one word per duplicate-checking CTA of
+// the plan kernel), the bucket offsets, 8 bytes per possible entry.
+inline int spmm_plan_checks(int m_vec) {   // duplicate-checking CTAs: a vector-row per warp, a few rows each at most
+    const int want = (m_vec + densespmm::kPlanWarps - 1) / densespmm::kPlanWarps;
+    return want < densespmm::kMaxCheckCtas ? want : densespmm::kMaxCheckCtas;
+}
+inline int64_t spmm_plan_header_bytes(int checks) { return ((int64_t)(4 + checks) * 4 + 15) & ~15ll; }
 int64_t spmm_plan_bytes(int m_vec, int V, int K, int batch, int64_t stride_values, int64_t *capacity_out, int64_t *offsets_out) {
     const int k_blocks = (K + densespmm::kBlockK - 1) / densespmm::kBlockK;
     const int m_tiles = (int)(((int64_t)m_vec * V + densespmm::kTileM - 1) / densespmm::kTileM);
@@ -280,7 +287,7 @@ int64_t spmm_plan_bytes(int m_vec, int V, int K, int batch, int64_t stride_value
     const int64_t offsets_bytes = (((int64_t)groups * (plan_blocks + 1) * 4) + 15) & ~15ll;
     if (capacity_out) *capacity_out = capacity;
     if (offsets_out) *offsets_out = offsets_bytes;
-    return 16 + offsets_bytes + capacity * 8;
+    return spmm_plan_header_bytes(spmm_plan_checks(m_vec)) + offsets_bytes + capacity * 8;
 }
 // The same for the dense SDDMM: per-row chunk offsets and 8 bytes per mask entry.
 int64_t sddmm_plan_bytes(int m_vec, int n, int nnz_vec, int64_t *offsets_out) {
@@ -303,18 +310,20 @@ template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStre
     const int rows_per_group = densespmm::kGroupRows / V;
     int64_t capacity = 0, offsets_bytes = 0;
     const int64_t plan_bytes = spmm_plan_bytes(p.m_vec, V, p.K, p.batch, p.stride_values, &capacity, &offsets_bytes);
-    const size_t plan_smem = (size_t)(2 * plan_blocks + rows_per_group + 1) * 4;
+    const int checks = spmm_plan_checks(p.m_vec);
+    const size_t plan_words = (size_t)(2 * plan_blocks + rows_per_group + 1), check_words = (size_t)densespmm::kPlanWarps * plan_blocks;
+    const size_t plan_smem = (plan_words > check_words ? plan_words : check_words) * 4;
     const bool dense_ok = !t_no_scratch && mode != SpmmMode::kGather && p.K > 0 && p.m_vec > 0 && p.N % 8 == 0 && plan_bytes <= kMaxPlanBytes &&
                           plan_smem <= 40 * 1024 && (p.batch == 1 || (p.stride_rhs * 2) % 16 == 0) &&
                           (p.batch == 1 || (p.stride_out * sizeof(TOut)) % 16 == 0) && aligned16(p.rhs) && aligned16(p.out);
-    if (!dense_ok) return launch_spmm_gather<TOut, V>(p, s, d, nullptr);
+    if (!dense_ok) return launch_spmm_gather<TOut, V>(p, s, d, nullptr, 0);
 
     constexpr bool kOutF32 = sizeof(TOut) == 4;
     CUtensorMap map, map_out;
     if (make_tile_map(&map, p.rhs, false, (uint64_t)p.K, (uint64_t)p.N, (uint64_t)p.batch, (uint64_t)p.stride_rhs, 64, 64) != VS_OK ||
         make_tile_map(&map_out, p.out, kOutF32, (uint64_t)p.m_vec * V, (uint64_t)p.N, (uint64_t)p.batch,
                       (uint64_t)p.stride_out, densespmm::kStoreCols, 32) != VS_OK)
-        return launch_spmm_gather<TOut, V>(p, s, d, nullptr);
+        return launch_spmm_gather<TOut, V>(p, s, d, nullptr, 0);
     CUtensorMap map_b4 = map;
     const int use_b4 = (p.N % 64 == 0 && make_blocked_map(&map_b4, p.rhs, (uint64_t)p.K, (uint64_t)p.N, (uint64_t)p.batch,
                                                           (uint64_t)p.stride_rhs, densespmm::kTileN / 64) == VS_OK) ? 1 : 0;
@@ -323,20 +332,21 @@ template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStre
     if (rc != VS_OK) return rc;
     uint8_t *plan = nullptr;
     if (stream_scratch(d, s, (size_t)plan_bytes, reinterpret_cast<void **>(&plan)) != VS_OK)
-        return launch_spmm_gather<TOut, V>(p, s, d, nullptr);
+        return launch_spmm_gather<TOut, V>(p, s, d, nullptr, 0);
     int32_t *flag = reinterpret_cast<int32_t *>(plan);
-    int32_t *blk_offsets = reinterpret_cast<int32_t *>(plan + 16);
-    uint2 *blk_entries = reinterpret_cast<uint2 *>(plan + 16 + offsets_bytes);
+    const int64_t header_bytes = spmm_plan_header_bytes(checks);
+    int32_t *blk_offsets = reinterpret_cast<int32_t *>(plan + header_bytes);
+    uint2 *blk_entries = reinterpret_cast<uint2 *>(plan + header_bytes + offsets_bytes);
     const int force_dense = mode == SpmmMode::kDense ? 1 : 0;
-    densespmm::dense_plan_kernel<<<groups, densespmm::kPlanThreads, plan_smem, s>>>(
-        p.row_offsets, p.col_indices, p.m_vec, p.K, rows_per_group, plan_blocks, blk_offsets, blk_entries, capacity, force_dense,
-        flag);
+    densespmm::dense_plan_kernel<<<groups + checks, densespmm::kPlanThreads, plan_smem, s>>>(
+        p.row_offsets, p.col_indices, p.m_vec, p.K, groups, rows_per_group, plan_blocks, blk_offsets, blk_entries, capacity,
+        force_dense, flag);
     const int64_t items = (int64_t)p.batch * n_tiles * m_tiles;
     const unsigned grid = (unsigned)(items < d->sm_count ? items : d->sm_count);   // one persistent CTA per SM
     kernel<<<grid, densespmm::kThreads, densespmm::kSmemBytes, s>>>(p, map, map_out, map_b4, use_b4, blk_offsets, blk_entries, m_tiles,
-                                                                    n_tiles, k_blocks, d->status, flag);
+                                                                    n_tiles, k_blocks, d->status, flag, checks);
     rc = (int)cudaGetLastError();
-    if (rc == VS_OK) rc = launch_spmm_gather<TOut, V>(p, s, d, flag);
+    if (rc == VS_OK) rc = launch_spmm_gather<TOut, V>(p, s, d, flag, checks);
     return rc;
 }
 
@@ -535,6 +545,62 @@ VS_EXPORT int vs_spmm(int path, int in_dtype, int out_dtype, int m_vec, int vec_
                       const void *values, const void *rhs_matrix, void *output_matrix, void *stream) {
     return vs_spmm_batched(path, in_dtype, out_dtype, m_vec, vec_length, k, n, row_indices, row_offsets,
                            col_indices, values, rhs_matrix, output_matrix, 1, 0, 0, 0, stream);
+}
+
+// ---- SpMM with the transposed sparse matrix ------------------------------------------------------------------
+namespace {
+template <typename TOut, int V> int launch_spmm_t(const spmmt::Params &p, cudaStream_t s) {
+    DeviceInfo *d;
+    int rc = device_info(&d);
+    if (rc != VS_OK) return rc;
+    const int row_groups = (p.n + spmmt::kWarps - 1) / spmmt::kWarps;
+    const int chunks = (p.N + spmmt::kChunk - 1) / spmmt::kChunk;
+    const int64_t items = (int64_t)p.batch * chunks * row_groups;
+    const int64_t cap = (int64_t)d->sm_count * 64;   // a few waves of 128-thread CTAs; the rest by grid stride
+    const unsigned grid = (unsigned)(items < cap ? items : cap);
+    spmmt::spmm_t_kernel<TOut, V><<<grid, spmmt::kThreads, 0, s>>>(p, items, row_groups, chunks);
+    return (int)cudaGetLastError();
+}
+template <typename TOut> int spmm_t_by_v(int V, const spmmt::Params &p, cudaStream_t s) {
+    switch (V) {
+        case 1: return launch_spmm_t<TOut, 1>(p, s);
+        case 2: return launch_spmm_t<TOut, 2>(p, s);
+        case 4: return launch_spmm_t<TOut, 4>(p, s);
+        case 8: return launch_spmm_t<TOut, 8>(p, s);
+    }
+    return VS_ERR_VEC_LENGTH;
+}
+}  // namespace
+
+VS_EXPORT int vs_spmm_t_batched(int in_dtype, int out_dtype, int m_vec, int vec_length, int k, int n,
+                                const int32_t *t_offsets, const int32_t *t_rows, const int32_t *t_src,
+                                const void *values, const void *rhs_matrix, void *output_matrix, int batch,
+                                int64_t stride_values, int64_t stride_rhs, int64_t stride_out, void *stream) {
+    if (!valid_v(vec_length)) return VS_ERR_VEC_LENGTH;
+    if (!(in_dtype == VS_F16 && (out_dtype == VS_F16 || out_dtype == VS_F32))) return VS_ERR_DTYPE;
+    if (m_vec < 0 || k < 0 || n < 0 || k % 8 != 0) return VS_ERR_SHAPE;
+    if ((int64_t)m_vec * vec_length > 0x7fffffffll) return VS_ERR_SHAPE;
+    if (batch < 1 || batch > kMaxBatch) return VS_ERR_ARG;
+    if (n == 0 || k == 0) return VS_OK;
+    if (!t_offsets || !t_rows || !t_src || !values || !rhs_matrix || !output_matrix) return VS_ERR_NULL;
+    if (!aligned16(values) || !aligned16(rhs_matrix) || !aligned16(output_matrix)) return VS_ERR_ALIGN;
+    if (!stride_ok(stride_values, in_dtype) || !stride_ok(stride_rhs, in_dtype) || !stride_ok(stride_out, out_dtype))
+        return VS_ERR_ALIGN;
+    if (batch > 1 && stride_out == 0) return VS_ERR_ARG;
+    spmmt::Params p;
+    p.n = n; p.N = k; p.batch = batch;
+    p.t_offsets = t_offsets; p.t_rows = t_rows; p.t_src = t_src;
+    p.values = static_cast<const __half *>(values); p.rhs = static_cast<const __half *>(rhs_matrix); p.out = output_matrix;
+    p.stride_values = stride_values; p.stride_rhs = stride_rhs; p.stride_out = stride_out;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return out_dtype == VS_F16 ? spmm_t_by_v<__half>(vec_length, p, s) : spmm_t_by_v<float>(vec_length, p, s);
+}
+
+VS_EXPORT int vs_spmm_t(int in_dtype, int out_dtype, int m_vec, int vec_length, int k, int n, const int32_t *t_offsets,
+                        const int32_t *t_rows, const int32_t *t_src, const void *values, const void *rhs_matrix,
+                        void *output_matrix, void *stream) {
+    return vs_spmm_t_batched(in_dtype, out_dtype, m_vec, vec_length, k, n, t_offsets, t_rows, t_src, values, rhs_matrix,
+                             output_matrix, 1, 0, 0, 0, stream);
 }
 
 VS_EXPORT int vs_sddmm_batched(int path, int in_dtype, int out_dtype, int m_vec, int k, int n, int nonzeros_vec,

@@ -105,6 +105,37 @@ def from_dense_mask(mask: np.ndarray, V: int, sort: bool = True) -> CVSE:
     return CVSE(m_vec, n, V, ro, ci[:nnz], row_swizzle(ro, sort))
 
 
+def transpose(a: CVSE):
+    """Structure of A^T for ops.spmm_t: (t_offsets [n + 1], t_rows [nnz_vec], t_src [nnz_vec]) as int32 arrays — for each
+    column of A its nonzero vectors as (vector-row, index of the vector in the CVSE arrays), ascending in the row."""
+    t_off = np.empty(a.n + 1, dtype=np.int32)
+    t_rows = np.empty(max(a.nnz_vec, 1), dtype=np.int32)
+    t_src = np.empty(max(a.nnz_vec, 1), dtype=np.int32)
+    ci = np.ascontiguousarray(a.col_indices, dtype=np.int32)
+    _lib.check(_lib.lib().vs_cvse_transpose(a.m_vec, a.n, a.nnz_vec, _ptr(a.row_offsets), _ptr(ci), _ptr(t_off),
+                                            _ptr(t_rows), _ptr(t_src)), "vs_cvse_transpose")
+    return t_off, t_rows[:a.nnz_vec], t_src[:a.nnz_vec]
+
+
+def prune_dense(weight: np.ndarray, V: int, sparsity: float, per_row: bool = False, sort: bool = True):
+    """Vector-wise magnitude pruning of a dense [M, n] weight (M a multiple of V): keeps the V x 1 column vectors with
+    the largest sums of absolute values, over the whole matrix or (per_row) the same number in every vector-row.
+    Returns (CVSE, values) with values float32 in the CVSE layout values[j * V + v]."""
+    w = np.ascontiguousarray(weight, dtype=np.float32)
+    if w.ndim != 2 or w.shape[0] % V:
+        raise ValueError("weight must be [M, n] with M a multiple of V")
+    m_vec, n = w.shape[0] // V, w.shape[1]
+    L = _lib.lib()
+    ro = np.empty(m_vec + 1, dtype=np.int32)
+    nnz = L.vs_cvse_prune_dense(m_vec, n, V, _ptr(w), float(sparsity), int(per_row), _ptr(ro), None, None)
+    if nnz < 0:
+        raise _lib.VsError(nnz, "vs_cvse_prune_dense")
+    ci = np.empty(max(nnz, 1), dtype=np.int32)
+    vals = np.empty(max(nnz, 1) * V, dtype=np.float32)
+    L.vs_cvse_prune_dense(m_vec, n, V, _ptr(w), float(sparsity), int(per_row), _ptr(ro), _ptr(ci), _ptr(vals))
+    return CVSE(m_vec, n, V, ro, ci[:nnz], row_swizzle(ro, sort)), vals[:nnz * V]
+
+
 def from_smtx(path: str, V: int, sort: bool = True) -> CVSE:
     """Reads a DLMC .smtx pattern; its row count is the number of VECTOR rows (spmm_benchmark.cpp:26-33)."""
     L = _lib.lib()

@@ -137,6 +137,25 @@ def spmm_batched(path, m_vec, vec_length, k, n, row_indices, row_offsets, column
                  output_matrix, batch)
 
 
+def spmm_t(m_vec, vec_length, k, n, t_offsets, t_rows, t_src, values, rhs_matrix, output_matrix):
+    """output [n, k] (or [B, n, k]) = A^T @ rhs, rhs [m_vec * V, k] (or [B, ...]), values [nnz] (or [B, nnz]): the
+    product with the transposed CVSE matrix; t_offsets / t_rows / t_src come from cvse.transpose (on the device)."""
+    batch = output_matrix.shape[0] if output_matrix.dim() == 3 else 1
+    _need(t_offsets, n + 1, "t_offsets")
+    _need(rhs_matrix, (batch if rhs_matrix.dim() == 3 else 1) * m_vec * vec_length * k, "rhs_matrix")
+    _need(output_matrix, batch * n * k, "output_matrix")
+    sv = values.stride(0) if values.dim() == 2 and batch > 1 else 0
+    sr = rhs_matrix.stride(0) if rhs_matrix.dim() == 3 and batch > 1 else 0
+    so = output_matrix.stride(0) if output_matrix.dim() == 3 and batch > 1 else 0
+    rc = _lib.lib().vs_spmm_t_batched(
+        _dtype_code(values, "values"), _dtype_code(output_matrix, "output_matrix"), m_vec, vec_length, k, n,
+        _dev(t_offsets, "t_offsets", torch.int32), _dev(t_rows, "t_rows", torch.int32), _dev(t_src, "t_src", torch.int32),
+        _dev(values, "values"), _dev(rhs_matrix, "rhs_matrix", values.dtype), _dev(output_matrix, "output_matrix"),
+        batch, sv, sr, so, _stream())
+    _lib.check(rc, "vs_spmm_t")
+    return 0
+
+
 def sddmm_batched(path, m_vec, k, n, nonzeros_vec, row_indices, row_offsets, col_indices, lhs_matrix, rhs_matrix,
                   output_values, vec_length, algorithm=1):
     """lhs [B, m, k], rhs [B, n, k], out [B, nnz]."""
