@@ -69,7 +69,9 @@ const char *vs_version(void);
  * the same whatever the tiles hold; where that is more than a per-row overhead plus a cost per nonzero vector
  * (wide, very sparse matrices), and whenever the dense kernel produced a non-finite sum
  * (0 * Inf from a row of rhs that no nonzero names), one row of rhs is gathered per nonzero vector as in the
- * reference.  A column index may appear only once per vector-row (as in any CVSE built from a mask).
+ * reference.  A matrix that names a column twice in one vector-row (the reference's generator pads rows that
+ * way, include/bm_test_utils.h:110-124, and its kernels add both values) is recognised on the device and goes
+ * to the gather kernel, which adds them too.
  * Environment variable VSPARSE_B200_SPMM = "dense" | "gather" forces one formulation.  The first tensor-path
  * call on a stream allocates a plan scratch buffer with cudaMallocAsync on that stream (8 bytes per nonzero
  * vector, bounded by m_vec * n and by 512 MB; reused and grown by later calls on the stream, never freed): make
