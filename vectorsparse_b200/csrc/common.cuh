@@ -21,6 +21,14 @@ struct SpmmParams {
     int64_t stride_values, stride_rhs, stride_out;  // in elements
 };
 
+// Programmatic dependent launch (a kernel launched with cudaLaunchAttributeProgrammaticStreamSerialization may
+// start before the kernel ahead of it in the stream has finished).  pdl_launch_dependents(): "the kernel behind
+// me may be scheduled now" — its CTAs become resident as room appears and run their set-up.  pdl_wait(): blocks
+// until the kernel ahead has COMPLETED and its writes are visible; everything that reads what that kernel (or
+// anything before it) wrote comes after this call.  Both are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Header of the plan scratch of the densifying SpMM, read by the kernels enqueued behind the plan kernel:
 // word 0 = the plan kernel chose the dense kernel; words 4 .. 4 + checks = one verdict per duplicate-checking CTA
 // of the plan kernel, set when it met the same column twice in one vector-row (the dense tile would keep one of

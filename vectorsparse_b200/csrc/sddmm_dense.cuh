@@ -77,6 +77,7 @@ __global__ void __launch_bounds__(kPlanThreads)
 sddmm_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__restrict__ col_indices, int n, int chunks,
                   int32_t *__restrict__ chunk_offsets, uint2 *__restrict__ chunk_entries) {
     extern __shared__ int plan_sh[];
+    pdl_launch_dependents();   // the multiplying kernel may set itself up while the plan is made
     int *hist = plan_sh;             // [chunks]
     int *cursor = plan_sh + chunks;  // [chunks]
     const int i = blockIdx.x, t = threadIdx.x;
@@ -189,6 +190,7 @@ sddmm_dense_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_
     tc::tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(sm + Smem::kTmemHolder);
 
+    pdl_wait();   // the set-up above may have run beside the plan kernel; its buckets are read from here on
     const int k_blocks = p.k / kBlockK;
     const int64_t total_items = (int64_t)p.batch * m_tiles * n_tiles;
     const int64_t G = gridDim.x;

@@ -111,16 +111,32 @@ static_assert(kBStages == kAStages || kBStages == 2 * kAStages,
 // they hold; the gather kernel ~370 per vector-row plus ~4.7 per nonzero vector.  Dense when cheaper (or forced)
 // and the entries fit the scratch (`entry_capacity`).  Every CTA computes the same answer; CTA 0 publishes it
 // in *use_dense for the two kernels enqueued behind this one, and nothing is planned when the answer is no.
+//
+// kTransposed: the plan of A^T for vs_spmm_t, read from the transposed structure of a CVSE matrix with vectors of
+// 1 << shift values (vs_cvse_transpose): row_offsets = t_offsets (in vectors), cols = t_rows, src = t_src.  Every
+// nonzero vector of A is `1 << shift` scalar entries of A^T in adjacent columns: entry q of the expanded list is
+// value (q & mask) of vector q >> shift, lies in column t_rows[q >> shift] << shift | (q & mask) and reads
+// values[t_src[q >> shift] << shift | (q & mask)] — so the multiplying kernel runs with vectors of one value and
+// the caller's `values` array stays where it is.  Offsets, capacity and counts are in scalar entries then.
+// Costs: `gather_per_row`, `gather_per_entry` for the kernel that takes the call otherwise, `dense_per_entry` for
+// the fill work of the dense kernel where that matters (vectors of one value: eight times the entries).
+template <bool kTransposed>
 __global__ void __launch_bounds__(kPlanThreads)
-dense_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__restrict__ col_indices, int m_vec, int K,
-                  int groups, int rows_per_group, int plan_blocks, int32_t *__restrict__ blk_offsets,
-                  uint2 *__restrict__ blk_entries, int64_t entry_capacity, int force_dense, int32_t *use_dense) {
+dense_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__restrict__ cols, const int32_t *__restrict__ src,
+                  int shift, int m_vec, int K, int groups, int rows_per_group, int plan_blocks,
+                  int32_t *__restrict__ blk_offsets, uint2 *__restrict__ blk_entries, int64_t entry_capacity, int force_dense,
+                  float gather_per_row, float gather_per_entry, float dense_per_entry, int32_t *use_dense) {
+    const int sub = (1 << shift) - 1;
+    auto offset_of = [&](int i) { return kTransposed ? __ldg(row_offsets + i) << shift : __ldg(row_offsets + i); };
+    auto column_of = [&](int j) { return kTransposed ? (__ldg(cols + (j >> shift)) << shift) | (j & sub) : __ldg(cols + j); };
+    auto value_of = [&](int j) { return kTransposed ? (__ldg(src + (j >> shift)) << shift) | (j & sub) : j; };
     extern __shared__ int plan_sh[];
+    pdl_launch_dependents();   // the multiplying kernel may set itself up while the plan is made
     {
-        const int64_t nnz = __ldg(row_offsets + m_vec);
+        const int64_t nnz = (int64_t)__ldg(row_offsets + m_vec) << (kTransposed ? shift : 0);
         const float stages = (float)(groups / (kTileM / kGroupRows)) * (float)(plan_blocks / (kBlockK / kPlanCols));
-        const float dense_cost = stages * 1100.0f;
-        const float gather_cost = (float)m_vec * 370.0f + 4.7f * (float)nnz;
+        const float dense_cost = stages * 1100.0f + dense_per_entry * (float)nnz;
+        const float gather_cost = (float)m_vec * gather_per_row + gather_per_entry * (float)nnz;
         const bool dense = nnz <= entry_capacity && (force_dense || dense_cost < gather_cost);
         if (blockIdx.x == 0 && threadIdx.x == 0) *use_dense = dense ? 1 : 0;
         if (!dense) return;
@@ -131,12 +147,12 @@ dense_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__rest
         unsigned *seen = reinterpret_cast<unsigned *>(plan_sh) + warp * plan_blocks;   // one bit per column of the row in hand
         int twice = 0;
         for (int r = check * kPlanWarps + warp; r < m_vec; r += checks * kPlanWarps) {
-            const int e0 = __ldg(row_offsets + r), e1 = __ldg(row_offsets + r + 1);
+            const int e0 = offset_of(r), e1 = offset_of(r + 1);
             if (e1 - e0 < 2) continue;
             for (int i = lane; i < plan_blocks; i += 32) seen[i] = 0u;
             __syncwarp();
             for (int e = e0 + lane; e < e1; e += 32) {
-                const int c = __ldg(col_indices + e);
+                const int c = column_of(e);
                 if ((unsigned)c >= (unsigned)K) continue;
                 const unsigned bit = 1u << (c & 31);
                 if (atomicOr(seen + (c >> 5), bit) & bit) twice = 1;   // of two lanes with one column, the later sees the earlier's bit
@@ -154,11 +170,11 @@ dense_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__rest
     const int r0 = min(m_vec, g * rows_per_group), r1 = min(m_vec, r0 + rows_per_group);
     const int nr = r1 - r0;
     for (int i = t; i < plan_blocks; i += kPlanThreads) hist[i] = 0;
-    for (int i = t; i <= nr; i += kPlanThreads) roff[i] = __ldg(row_offsets + r0 + i);
+    for (int i = t; i <= nr; i += kPlanThreads) roff[i] = offset_of(r0 + i);
     __syncthreads();
     const int j0 = roff[0], j1 = roff[nr];
     for (int j = j0 + t; j < j1; j += kPlanThreads) {
-        const int c = __ldg(col_indices + j);
+        const int c = column_of(j);
         if ((unsigned)c < (unsigned)K) atomicAdd(hist + c / kPlanCols, 1);
     }
     __syncthreads();
@@ -174,7 +190,7 @@ dense_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__rest
     }
     __syncthreads();
     for (int j = j0 + t; j < j1; j += kPlanThreads) {
-        const int c = __ldg(col_indices + j);
+        const int c = column_of(j);
         if ((unsigned)c >= (unsigned)K) continue;
         int lo = 0, hi = nr;   // vector-row of j: the last i with roff[i] <= j (empty rows share an offset)
         while (hi - lo > 1) {
@@ -182,7 +198,7 @@ dense_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__rest
             if (roff[mid] <= j) lo = mid; else hi = mid;
         }
         const int pos = atomicAdd(cursor + c / kPlanCols, 1);
-        blk_entries[pos] = make_uint2((uint32_t)j, ((uint32_t)lo << 6) | (uint32_t)(c & (kBlockK - 1)));
+        blk_entries[pos] = make_uint2((uint32_t)value_of(j), ((uint32_t)lo << 6) | (uint32_t)(c & (kBlockK - 1)));
     }
 }
 
@@ -301,10 +317,7 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                   const int32_t *__restrict__ blk_offsets,
                   const uint2 *__restrict__ blk_entries, int m_tiles, int n_tiles, int k_blocks, uint32_t *status,
                   int32_t *use_dense, int plan_checks) {
-    // Not chosen (the gather kernel behind this one takes the call): the CTA still sets itself up and tears itself
-    // down, with no work items in between.  (An early return that depends on a barrier's result made the compiler
-    // treat the rest of the kernel as possibly divergent: 17 % slower.)
-    const bool chosen = plan_dense_chosen(use_dense, plan_checks);
+    pdl_launch_dependents();   // the gather kernel behind this one may queue up
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = tc::smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -344,6 +357,12 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
     tc::tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(sm + Smem::kTmemHolder);
 
+    // Everything above ran while the plan kernel may still have been at work; nothing it writes is read before here.
+    pdl_wait();
+    // Not chosen (the gather kernel behind this one takes the call): the CTA still sets itself up and tears itself
+    // down, with no work items in between.  (An early return that depends on a barrier's result made the compiler
+    // treat the rest of the kernel as possibly divergent: 17 % slower.)
+    const bool chosen = plan_dense_chosen(use_dense, plan_checks);
     const int64_t total_items = chosen ? (int64_t)p.batch * n_tiles * m_tiles : 0;
     const int64_t G = gridDim.x;
     const uint32_t my_items = (total_items > blockIdx.x) ? (uint32_t)((total_items - blockIdx.x + G - 1) / G) : 0u;

@@ -17,6 +17,9 @@
 #include <cuda_fp16.h>
 #include <cstdint>
 
+#include "common.cuh"
+
+namespace vs {
 namespace spmmt {
 
 struct Params {
@@ -77,7 +80,12 @@ __device__ __forceinline__ void store8(float *dst, const float (&acc)[8]) {
 // Work item = (batch entry, 256-column chunk, group of kWarps output rows); items are walked grid-stride so that
 // a launch never needs more CTAs than fit the machine a few times over.
 template <typename TOut, int V>
-__global__ void __launch_bounds__(kThreads) spmm_t_kernel(const Params p, int64_t items, int row_groups, int chunks) {
+__global__ void __launch_bounds__(kThreads) spmm_t_kernel(const Params p, int64_t items, int row_groups, int chunks,
+                                                          const int32_t *plan_hdr, int plan_checks) {
+    // Enqueued behind the tensor-core kernel (plan_hdr != null): wait for its end, then leave unless it handed the
+    // call over (a matrix it cannot hold, or a non-finite sum it would not vouch for).
+    pdl_wait();
+    if (plan_hdr && plan_dense_chosen(plan_hdr, plan_checks)) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int64_t w = blockIdx.x; w < items; w += gridDim.x) {
         const int rg = (int)(w % row_groups);
@@ -130,3 +138,4 @@ __global__ void __launch_bounds__(kThreads) spmm_t_kernel(const Params p, int64_
 }
 
 }  // namespace spmmt
+}  // namespace vs

@@ -15,6 +15,7 @@
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
+#include <utility>
 
 #include "vsparse_b200.h"
 #include "common.cuh"
@@ -123,6 +124,28 @@ template <typename K> int set_smem(K kernel, int bytes) {
     return e == cudaSuccess ? VS_OK : (int)e;
 }
 
+// Launches `kernel` so that it may start while the kernel ahead of it in the stream is still running (programmatic
+// dependent launch); such a kernel calls pdl_wait() before it reads anything written earlier in the stream.
+// VSPARSE_B200_PDL=0 launches the ordinary way.
+template <typename... Exp, typename... Act>
+cudaError_t launch_overlapped(void (*kernel)(Exp...), unsigned grid, unsigned block, size_t smem, cudaStream_t s, Act &&...args) {
+    static const bool overlap = []() {
+        const char *e = std::getenv("VSPARSE_B200_PDL");
+        return !(e && !std::strcmp(e, "0"));
+    }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Act>(args)...);
+}
+
 // cuTensorMapEncodeTiled, fetched from the driver at first use (the library does not link libcuda).
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -219,6 +242,7 @@ int launch_spmm_tc_cpasync(const SpmmParams &p, cudaStream_t s, DeviceInfo *d, c
     const int64_t items = (int64_t)p.batch * n_tiles * p.m_vec;
     const int64_t cap = (int64_t)tcspmm::kCtasPerSm * d->sm_count;  // persistent CTAs
     const unsigned grid = (unsigned)(items < cap ? items : cap);
+    if (plan_hdr) return (int)launch_overlapped(kernel, grid, tcspmm::kThreads, tcspmm::kSmemBytes, s, p, d->status, plan_hdr, plan_checks);
     kernel<<<grid, tcspmm::kThreads, tcspmm::kSmemBytes, s>>>(p, d->status, plan_hdr, plan_checks);
     return (int)cudaGetLastError();
 }
@@ -247,6 +271,9 @@ int launch_spmm_gather(const SpmmParams &p, cudaStream_t s, DeviceInfo *d, const
     const int64_t items = (int64_t)p.batch * n_tiles * p.m_vec;
     const int64_t cap = (int64_t)tmaspmm::kCtasPerSm * d->sm_count;  // persistent CTAs
     const unsigned grid = (unsigned)(items < cap ? items : cap);
+    if (plan_hdr)
+        return (int)launch_overlapped(kernel, grid, tmaspmm::kThreads, tmaspmm::kSmemBytes, s, p, map, (int)rows_per_batch,
+                                      (int)total_rows, d->status, plan_hdr, plan_checks);
     kernel<<<grid, tmaspmm::kThreads, tmaspmm::kSmemBytes, s>>>(p, map, (int)rows_per_batch, (int)total_rows, d->status,
                                                                 plan_hdr, plan_checks);
     return (int)cudaGetLastError();
@@ -338,14 +365,15 @@ template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStre
     int32_t *blk_offsets = reinterpret_cast<int32_t *>(plan + header_bytes);
     uint2 *blk_entries = reinterpret_cast<uint2 *>(plan + header_bytes + offsets_bytes);
     const int force_dense = mode == SpmmMode::kDense ? 1 : 0;
-    densespmm::dense_plan_kernel<<<groups + checks, densespmm::kPlanThreads, plan_smem, s>>>(
-        p.row_offsets, p.col_indices, p.m_vec, p.K, groups, rows_per_group, plan_blocks, blk_offsets, blk_entries, capacity,
-        force_dense, flag);
+    densespmm::dense_plan_kernel<false><<<groups + checks, densespmm::kPlanThreads, plan_smem, s>>>(
+        p.row_offsets, p.col_indices, nullptr, 0, p.m_vec, p.K, groups, rows_per_group, plan_blocks, blk_offsets, blk_entries,
+        capacity, force_dense, 370.0f, 4.7f, 0.0f, flag);
     const int64_t items = (int64_t)p.batch * n_tiles * m_tiles;
     const unsigned grid = (unsigned)(items < d->sm_count ? items : d->sm_count);   // one persistent CTA per SM
-    kernel<<<grid, densespmm::kThreads, densespmm::kSmemBytes, s>>>(p, map, map_out, map_b4, use_b4, blk_offsets, blk_entries, m_tiles,
-                                                                    n_tiles, k_blocks, d->status, flag, checks);
     rc = (int)cudaGetLastError();
+    if (rc == VS_OK)
+        rc = (int)launch_overlapped(kernel, grid, densespmm::kThreads, densespmm::kSmemBytes, s, p, map, map_out, map_b4, use_b4,
+                                    blk_offsets, blk_entries, m_tiles, n_tiles, k_blocks, d->status, flag, checks);
     if (rc == VS_OK) rc = launch_spmm_gather<TOut, V>(p, s, d, flag, checks);
     return rc;
 }
@@ -471,9 +499,10 @@ template <typename TOut, int V> int launch_sddmm_tc(const SddmmParams &p, cudaSt
     const int n_tiles = (p.n + densesddmm::kTileN - 1) / densesddmm::kTileN;
     const int64_t items = (int64_t)p.batch * m_tiles * n_tiles;
     const unsigned grid = (unsigned)(items < d->sm_count ? items : d->sm_count);   // one persistent CTA per SM
-    kernel<<<grid, densesddmm::kThreads, densesddmm::kSmemBytes, s>>>(p, map_l, map_r, chunk_offsets, chunk_entries, m_tiles,
-                                                                      n_tiles, chunks, d->status);
-    return (int)cudaGetLastError();
+    rc = (int)cudaGetLastError();
+    if (rc != VS_OK) return rc;
+    return (int)launch_overlapped(kernel, grid, densesddmm::kThreads, densesddmm::kSmemBytes, s, p, map_l, map_r, chunk_offsets,
+                                  chunk_entries, m_tiles, n_tiles, chunks, d->status);
 }
 
 template <typename TOut> int sddmm_tc_by_v(int V, const SddmmParams &p, cudaStream_t s) {
@@ -549,24 +578,99 @@ VS_EXPORT int vs_spmm(int path, int in_dtype, int out_dtype, int m_vec, int vec_
 
 // ---- SpMM with the transposed sparse matrix ------------------------------------------------------------------
 namespace {
-template <typename TOut, int V> int launch_spmm_t(const spmmt::Params &p, cudaStream_t s) {
-    DeviceInfo *d;
-    int rc = device_info(&d);
-    if (rc != VS_OK) return rc;
+// CUDA-core kernel.  With `plan_hdr` it is enqueued behind the dense kernel and returns at once unless that kernel
+// left the call to it.
+template <typename TOut, int V>
+int launch_spmm_t_cc(const spmmt::Params &p, cudaStream_t s, DeviceInfo *d, const int32_t *plan_hdr, int plan_checks) {
     const int row_groups = (p.n + spmmt::kWarps - 1) / spmmt::kWarps;
     const int chunks = (p.N + spmmt::kChunk - 1) / spmmt::kChunk;
     const int64_t items = (int64_t)p.batch * chunks * row_groups;
     const int64_t cap = (int64_t)d->sm_count * 64;   // a few waves of 128-thread CTAs; the rest by grid stride
     const unsigned grid = (unsigned)(items < cap ? items : cap);
-    spmmt::spmm_t_kernel<TOut, V><<<grid, spmmt::kThreads, 0, s>>>(p, items, row_groups, chunks);
+    auto kernel = spmmt::spmm_t_kernel<TOut, V>;
+    if (plan_hdr) return (int)launch_overlapped(kernel, grid, spmmt::kThreads, 0, s, p, items, row_groups, chunks, plan_hdr, plan_checks);
+    kernel<<<grid, spmmt::kThreads, 0, s>>>(p, items, row_groups, chunks, plan_hdr, plan_checks);
     return (int)cudaGetLastError();
 }
-template <typename TOut> int spmm_t_by_v(int V, const spmmt::Params &p, cudaStream_t s) {
+
+enum class SpmmTMode { kAuto, kDense, kGather };
+SpmmTMode spmm_t_mode() {   // read at every call, so that a test can switch kernels inside one process
+    const char *e = std::getenv("VSPARSE_B200_SPMM_T");
+    if (e && !std::strcmp(e, "dense")) return SpmmTMode::kDense;
+    if (e && !std::strcmp(e, "gather")) return SpmmTMode::kGather;
+    return SpmmTMode::kAuto;
+}
+
+// Tensor path of the transposed product: A^T (n x m_vec * V) is handed to the densifying SpMM kernel as a matrix
+// of one-value vectors, its plan built straight from the transposed structure (dense_plan_kernel<true>), the
+// values read where the forward operators keep them.  Costs for the choice, in the plan kernel's units (SM-cycles
+// per 128 columns): the CUDA-core kernel ~5 per scalar entry (0.92 ms for 256 products of 2048 x 512, 90 % sparse,
+// V = 8), the dense kernel ~1100 per stage plus ~1.9 per scalar entry of fill work.
+template <typename TOut, int V> int launch_spmm_t(const spmmt::Params &p, int m_vec, cudaStream_t s) {
+    DeviceInfo *d;
+    int rc = device_info(&d);
+    if (rc != VS_OK) return rc;
+    const SpmmTMode mode = spmm_t_mode();
+    const int shift = V == 8 ? 3 : V == 4 ? 2 : V == 2 ? 1 : 0;
+    const int64_t M = (int64_t)m_vec * V;   // columns of A^T: the contraction
+    SpmmParams q;
+    q.m_vec = p.n; q.N = p.N; q.K = (int)M; q.batch = p.batch;
+    q.row_indices = nullptr; q.row_offsets = p.t_offsets; q.col_indices = p.t_rows;
+    q.values = p.values; q.rhs = p.rhs; q.out = p.out;
+    q.stride_values = p.stride_values; q.stride_rhs = p.stride_rhs; q.stride_out = p.stride_out;
+    const int k_blocks = (q.K + densespmm::kBlockK - 1) / densespmm::kBlockK;
+    const int m_tiles = (q.m_vec + densespmm::kTileM - 1) / densespmm::kTileM;
+    const int n_tiles = (q.N + densespmm::kTileN - 1) / densespmm::kTileN;
+    const int groups = m_tiles * (densespmm::kTileM / densespmm::kGroupRows);
+    const int plan_blocks = k_blocks * (densespmm::kBlockK / densespmm::kPlanCols);
+    const int rows_per_group = densespmm::kGroupRows;
+    int64_t capacity = 0, offsets_bytes = 0;
+    const int64_t plan_bytes = spmm_plan_bytes(q.m_vec, 1, q.K, q.batch, q.stride_values, &capacity, &offsets_bytes);
+    const int checks = spmm_plan_checks(q.m_vec);
+    const size_t plan_words = (size_t)(2 * plan_blocks + rows_per_group + 1), check_words = (size_t)densespmm::kPlanWarps * plan_blocks;
+    const size_t plan_smem = (plan_words > check_words ? plan_words : check_words) * 4;
+    const bool dense_ok = !t_no_scratch && mode != SpmmTMode::kGather && q.K > 0 && q.m_vec > 0 && plan_bytes <= kMaxPlanBytes &&
+                          plan_smem <= 40 * 1024 && (q.batch == 1 || (q.stride_rhs * 2) % 16 == 0) &&
+                          (q.batch == 1 || (q.stride_out * sizeof(TOut)) % 16 == 0);
+    if (!dense_ok) return launch_spmm_t_cc<TOut, V>(p, s, d, nullptr, 0);
+
+    constexpr bool kOutF32 = sizeof(TOut) == 4;
+    CUtensorMap map, map_out;
+    if (make_tile_map(&map, q.rhs, false, (uint64_t)q.K, (uint64_t)q.N, (uint64_t)q.batch, (uint64_t)q.stride_rhs, 64, 64) != VS_OK ||
+        make_tile_map(&map_out, q.out, kOutF32, (uint64_t)q.m_vec, (uint64_t)q.N, (uint64_t)q.batch, (uint64_t)q.stride_out,
+                      densespmm::kStoreCols, 32) != VS_OK)
+        return launch_spmm_t_cc<TOut, V>(p, s, d, nullptr, 0);
+    CUtensorMap map_b4 = map;
+    const int use_b4 = (q.N % 64 == 0 && make_blocked_map(&map_b4, q.rhs, (uint64_t)q.K, (uint64_t)q.N, (uint64_t)q.batch,
+                                                          (uint64_t)q.stride_rhs, densespmm::kTileN / 64) == VS_OK) ? 1 : 0;
+    auto kernel = densespmm::spmm_dense_kernel<TOut, 1>;
+    rc = set_smem(kernel, densespmm::kSmemBytes);
+    if (rc != VS_OK) return rc;
+    uint8_t *plan = nullptr;
+    if (stream_scratch(d, s, (size_t)plan_bytes, reinterpret_cast<void **>(&plan)) != VS_OK)
+        return launch_spmm_t_cc<TOut, V>(p, s, d, nullptr, 0);
+    int32_t *flag = reinterpret_cast<int32_t *>(plan);
+    const int64_t header_bytes = spmm_plan_header_bytes(checks);
+    int32_t *blk_offsets = reinterpret_cast<int32_t *>(plan + header_bytes);
+    uint2 *blk_entries = reinterpret_cast<uint2 *>(plan + header_bytes + offsets_bytes);
+    densespmm::dense_plan_kernel<true><<<groups + checks, densespmm::kPlanThreads, plan_smem, s>>>(
+        p.t_offsets, p.t_rows, p.t_src, shift, q.m_vec, q.K, groups, rows_per_group, plan_blocks, blk_offsets, blk_entries, capacity,
+        mode == SpmmTMode::kDense ? 1 : 0, 0.0f, 5.0f, 1.9f, flag);
+    rc = (int)cudaGetLastError();
+    const int64_t items = (int64_t)q.batch * n_tiles * m_tiles;
+    const unsigned grid = (unsigned)(items < d->sm_count ? items : d->sm_count);   // one persistent CTA per SM
+    if (rc == VS_OK)
+        rc = (int)launch_overlapped(kernel, grid, densespmm::kThreads, densespmm::kSmemBytes, s, q, map, map_out, map_b4, use_b4,
+                                    blk_offsets, blk_entries, m_tiles, n_tiles, k_blocks, d->status, flag, checks);
+    if (rc == VS_OK) rc = launch_spmm_t_cc<TOut, V>(p, s, d, flag, checks);
+    return rc;
+}
+template <typename TOut> int spmm_t_by_v(int V, const spmmt::Params &p, int m_vec, cudaStream_t s) {
     switch (V) {
-        case 1: return launch_spmm_t<TOut, 1>(p, s);
-        case 2: return launch_spmm_t<TOut, 2>(p, s);
-        case 4: return launch_spmm_t<TOut, 4>(p, s);
-        case 8: return launch_spmm_t<TOut, 8>(p, s);
+        case 1: return launch_spmm_t<TOut, 1>(p, m_vec, s);
+        case 2: return launch_spmm_t<TOut, 2>(p, m_vec, s);
+        case 4: return launch_spmm_t<TOut, 4>(p, m_vec, s);
+        case 8: return launch_spmm_t<TOut, 8>(p, m_vec, s);
     }
     return VS_ERR_VEC_LENGTH;
 }
@@ -593,7 +697,7 @@ VS_EXPORT int vs_spmm_t_batched(int in_dtype, int out_dtype, int m_vec, int vec_
     p.values = static_cast<const __half *>(values); p.rhs = static_cast<const __half *>(rhs_matrix); p.out = output_matrix;
     p.stride_values = stride_values; p.stride_rhs = stride_rhs; p.stride_out = stride_out;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    return out_dtype == VS_F16 ? spmm_t_by_v<__half>(vec_length, p, s) : spmm_t_by_v<float>(vec_length, p, s);
+    return out_dtype == VS_F16 ? spmm_t_by_v<__half>(vec_length, p, m_vec, s) : spmm_t_by_v<float>(vec_length, p, m_vec, s);
 }
 
 VS_EXPORT int vs_spmm_t(int in_dtype, int out_dtype, int m_vec, int vec_length, int k, int n, const int32_t *t_offsets,
