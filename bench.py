@@ -64,7 +64,10 @@ def kernels_per_step(w, a=None):
     """Names of the library's kernels one step launches (the count is what `gpu_launches` reports)."""
     tensor = w.get("path") != 1
     if w["op"] == "spmm_t":
-        return ["spmm_t_kernel"]
+        if os.environ.get("VSPARSE_B200_SPMM_T") == "gather":
+            return ["spmm_t_kernel"]
+        return ["dense_plan_kernel<transposed>", "spmm_dense_kernel<V=1>",
+                "spmm_t_kernel (returns at once unless the plan kernel chose it)"]
     if w["op"] == "spmm" and tensor:
         if os.environ.get("VSPARSE_B200_SPMM") == "gather":
             return ["spmm_tma_kernel"]
@@ -339,7 +342,7 @@ def run_ours(args):
             "data": "synthetic",
             "config": {"workload": args.workload, "op": w["op"], "M": M, "K": K, "V": V, "sparsity": w["s"],
                        "dense_width_or_k": N, "nnz_vec": a.nnz_vec, "instances_per_step": inst,
-                       "path": "cuda-core" if path == VS_PATH_CUDA_CORE or w["op"] == "spmm_t" else "tensor (tcgen05)",
+                       "path": "cuda-core" if path == VS_PATH_CUDA_CORE else "tensor (tcgen05)",
                        "l2": "working set 3x L2 (distinct operands per instance), no flush needed",
                        "parallelism": f"independent streams x{world}"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",

@@ -104,8 +104,13 @@ int vs_spmm_batched(int path, int in_dtype, int out_dtype, int m_vec, int vec_le
  * buffers, asynchronous on `stream`, nothing allocated.  `values` is the SAME array the forward operators use;
  * only the structure is transposed, once, on the host, by vs_cvse_transpose below.
  * (in_dtype, out_dtype): (F16,F16), (F16,F32); fp32 accumulation in the listed order (reproducible).
- * vec_length in {1,2,4,8}; k % 8 == 0; values, rhs, out 16-byte aligned.  CUDA cores (one warp per 256 columns
- * of an output row).  The batched form shares the structure and strides values / rhs / out as vs_spmm_batched.
+ * vec_length in {1,2,4,8}; k % 8 == 0; values, rhs, out 16-byte aligned.  Two kernels, chosen on the device from
+ * their measured costs: A^T as a matrix of one-value vectors through the densifying tensor-core kernel of vs_spmm
+ * (plan built from the transposed structure; same plan scratch rules as vs_spmm: per-stream buffer or
+ * vs_set_workspace, first call on a stream outside capture), or CUDA cores (one warp per 256 columns of an
+ * output row: very sparse matrices, a column named twice by one vector-row, non-finite sums, no scratch).
+ * VSPARSE_B200_SPMM_T = "dense" | "gather" forces one.  The batched form shares the structure and strides
+ * values / rhs / out as vs_spmm_batched.
  * ---------------------------------------------------------------------------------------------------- */
 int vs_spmm_t(int in_dtype, int out_dtype, int m_vec, int vec_length, int k, int n, const int32_t *t_offsets,
               const int32_t *t_rows, const int32_t *t_src, const void *values, const void *rhs_matrix,
@@ -219,7 +224,8 @@ int vs_device_status(int clear, uint32_t *status);
  * need device memory for that.  By default the library keeps one buffer per calling stream (see vs_spmm).  A
  * caller that plans its own device memory can instead hand over a buffer:
  *
- *   vs_spmm_workspace_bytes / vs_sddmm_workspace_bytes   bytes the dense formulation needs for such a call
+ *   vs_spmm_workspace_bytes / vs_sddmm_workspace_bytes / vs_spmm_t_workspace_bytes
+ *                                                        bytes the dense formulation needs for such a call
  *                                                        (0: it is never used for this problem); no device needed
  *   vs_set_workspace(ptr, bytes)                         from now on the tensor-path calls made by THIS host
  *                                                        thread put their plan in [ptr, ptr + bytes) when it
@@ -232,6 +238,7 @@ int vs_device_status(int clear, uint32_t *status);
  * ---------------------------------------------------------------------------------------------------- */
 int64_t vs_spmm_workspace_bytes(int m_vec, int vec_length, int n, int batch, int64_t stride_values);
 int64_t vs_sddmm_workspace_bytes(int m_vec, int n, int nonzeros_vec);
+int64_t vs_spmm_t_workspace_bytes(int m_vec, int vec_length, int n, int batch, int64_t stride_values);
 int vs_set_workspace(void *workspace, int64_t bytes);
 
 /* Which tensor-path SDDMM formulation vs_sddmm / vs_sddmm_batched would run for this problem: 1 = dense tiles

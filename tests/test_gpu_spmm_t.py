@@ -1,4 +1,6 @@
-"""vs_spmm_t: out = A^T . rhs for a CVSE matrix A, against the fp64 oracle within conftest.assert_close."""
+"""vs_spmm_t: out = A^T . rhs for a CVSE matrix A, against the fp64 oracle within conftest.assert_close.  Every test
+runs three times: with the tensor-core kernel forced (A^T as one-value vectors through the densifying SpMM kernel),
+with the CUDA-core kernel forced, and with the library's own choice (VSPARSE_B200_SPMM_T, read at every call)."""
 import numpy as np
 import pytest
 import torch
@@ -9,6 +11,15 @@ from gpu_util import DEV, custom, dev, problem
 from vectorsparse_b200 import _lib, cvse, ops
 
 pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(params=["dense", "gather", None], autouse=True)
+def kernel_choice(request, monkeypatch):
+    if request.param:
+        monkeypatch.setenv("VSPARSE_B200_SPMM_T", request.param)
+    else:
+        monkeypatch.delenv("VSPARSE_B200_SPMM_T", raising=False)
+    return request.param
 
 
 def t_structure(a):
@@ -35,6 +46,7 @@ def run(a, N, vals, B, out_dtype):
     d_vals = dev(vals) if vals.size else torch.zeros(8, dtype=torch.float16, device=DEV)
     ops.spmm_t(a.m_vec, a.V, N, a.n, t_off, t_rows, t_src, d_vals, dev(B), out)
     torch.cuda.synchronize()
+    assert ops.device_status() == 0
     host = out.float().cpu().numpy()
     assert np.all(np.isnan(host[a.n * N:])), "wrote past the end of the output"
     return host[:a.n * N].reshape(a.n, N)
@@ -93,6 +105,31 @@ def test_runs_are_bit_identical():
     vals, B = inputs(a, 256, 3)
     first = run(a, 256, vals, B, torch.float32)
     assert np.array_equal(first, run(a, 256, vals, B, torch.float32))
+
+
+def test_a_column_named_twice_by_one_vector_row_is_added_twice():
+    """Two vectors of one vector-row in the same column are two entries of A^T at the same place: the tensor-core
+    kernel's tile has room for one, so the plan kernel sends such a matrix to the CUDA-core kernel."""
+    a = custom([6, 0, 9, 4], 96, 8, seed=3)
+    ci = a.col_indices.copy()
+    ci[1] = ci[0]
+    ci[a.row_offsets[2] + 5] = ci[a.row_offsets[2] + 2]
+    dup = cvse.CVSE(a.m_vec, a.n, 8, a.row_offsets, ci, a.row_indices)
+    vals, B = inputs(dup, 64, 12, sigma=1.0)
+    assert_close(run(dup, 64, vals, B, torch.float32), want_of(dup, 64, vals, B), "repeated column")
+
+
+def test_non_finite_rows_nobody_reads_do_not_leak():
+    """A row of rhs that belongs to a vector-row without nonzeros is never read by the sum; a dense tile would
+    multiply it by zero.  An Inf there must not turn into NaNs in the output."""
+    a = custom([5, 0, 7, 3], 40, 4, seed=6)
+    vals, B = inputs(a, 64, 2)
+    B = B.copy()
+    B[4:8] = np.float16(np.inf)          # the rows of vector-row 1, which is empty
+    want = want_of(a, 64, vals, np.where(np.isfinite(B), B, 0).astype(np.float16))
+    got = run(a, 64, vals, B, torch.float32)
+    assert np.all(np.isfinite(got))
+    assert_close(got, want, "Inf in an unread row")
 
 
 def test_argument_errors():

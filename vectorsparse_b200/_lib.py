@@ -49,6 +49,7 @@ SIGNATURES = {
     "vs_sddmm_formulation": (_i, [_i, _i, _i, _i, _i]),
     "vs_spmm_workspace_bytes": (_i64, [_i, _i, _i, _i, _i64]),
     "vs_sddmm_workspace_bytes": (_i64, [_i, _i, _i]),
+    "vs_spmm_t_workspace_bytes": (_i64, [_i, _i, _i, _i, _i64]),
     "vs_set_workspace": (_i, [_vp, _i64]),
     "vs_selftest_mma": (_i, [_vp, _i, _vp, _i, C.c_uint32, _i, _f, _vp, _vp]),
     "vs_selftest_gather4": (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _vp]),

@@ -957,6 +957,13 @@ VS_EXPORT int64_t vs_spmm_workspace_bytes(int m_vec, int vec_length, int n, int 
     return bytes <= kMaxPlanBytes ? bytes : 0;
 }
 
+VS_EXPORT int64_t vs_spmm_t_workspace_bytes(int m_vec, int vec_length, int n, int batch, int64_t stride_values) {
+    if (m_vec <= 0 || n <= 0 || batch < 1 || !valid_v(vec_length) || (int64_t)m_vec * vec_length > 0x7fffffffll) return 0;
+    // the plan of A^T: n rows of one-value vectors over m_vec * vec_length columns
+    const int64_t bytes = spmm_plan_bytes(n, 1, m_vec * vec_length, batch, stride_values, nullptr, nullptr);
+    return bytes <= kMaxPlanBytes ? bytes : 0;
+}
+
 VS_EXPORT int64_t vs_sddmm_workspace_bytes(int m_vec, int n, int nonzeros_vec) {
     if (m_vec <= 0 || n <= 0 || nonzeros_vec <= 0) return 0;
     const int64_t bytes = sddmm_plan_bytes(m_vec, n, nonzeros_vec, nullptr);
