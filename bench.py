@@ -66,7 +66,7 @@ def kernels_per_step(w, a=None):
     if w["op"] == "spmm_t":
         if os.environ.get("VSPARSE_B200_SPMM_T") == "gather":
             return ["spmm_t_kernel"]
-        return ["dense_plan_kernel<transposed>", "spmm_dense_kernel<V=1>",
+        return ["dense_plan_kernel<transposed>", "spmm_dense_kernel<transposed>",
                 "spmm_t_kernel (returns at once unless the plan kernel chose it)"]
     if w["op"] == "spmm" and tensor:
         if os.environ.get("VSPARSE_B200_SPMM") == "gather":

@@ -105,8 +105,8 @@ int vs_spmm_batched(int path, int in_dtype, int out_dtype, int m_vec, int vec_le
  * only the structure is transposed, once, on the host, by vs_cvse_transpose below.
  * (in_dtype, out_dtype): (F16,F16), (F16,F32); fp32 accumulation in the listed order (reproducible).
  * vec_length in {1,2,4,8}; k % 8 == 0; values, rhs, out 16-byte aligned.  Two kernels, chosen on the device from
- * their measured costs: A^T as a matrix of one-value vectors through the densifying tensor-core kernel of vs_spmm
- * (plan built from the transposed structure; same plan scratch rules as vs_spmm: per-stream buffer or
+ * their measured costs: A^T through the densifying tensor-core kernel of vs_spmm
+ * (plan built from the transposed structure, the V values of a vector side by side in one row of the tile; same plan scratch rules as vs_spmm: per-stream buffer or
  * vs_set_workspace, first call on a stream outside capture), or CUDA cores (one warp per 256 columns of an
  * output row: very sparse matrices, a column named twice by one vector-row, non-finite sums, no scratch).
  * VSPARSE_B200_SPMM_T = "dense" | "gather" forces one.  The batched form shares the structure and strides

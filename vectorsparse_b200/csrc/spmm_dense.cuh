@@ -113,27 +113,26 @@ static_assert(kBStages == kAStages || kBStages == 2 * kAStages,
 // in *use_dense for the two kernels enqueued behind this one, and nothing is planned when the answer is no.
 //
 // kTransposed: the plan of A^T for vs_spmm_t, read from the transposed structure of a CVSE matrix with vectors of
-// 1 << shift values (vs_cvse_transpose): row_offsets = t_offsets (in vectors), cols = t_rows, src = t_src.  Every
-// nonzero vector of A is `1 << shift` scalar entries of A^T in adjacent columns: entry q of the expanded list is
-// value (q & mask) of vector q >> shift, lies in column t_rows[q >> shift] << shift | (q & mask) and reads
-// values[t_src[q >> shift] << shift | (q & mask)] — so the multiplying kernel runs with vectors of one value and
-// the caller's `values` array stays where it is.  Offsets, capacity and counts are in scalar entries then.
+// 1 << shift values (vs_cvse_transpose): row_offsets = t_offsets, cols = t_rows, src = t_src.  A row of A^T is a
+// column of A; a nonzero vector (i, c) of A lies in row c of A^T, columns i << shift .. (i << shift) + V - 1, which
+// never straddle a 32-column block.  The entry keeps the vector's first column and its index in the caller's
+// `values` array (t_src), so the multiplying kernel reads the values where the forward operators keep them and
+// drops the V of them side by side into one row of its tile.  Groups are 128 rows of A^T.
 // Costs: `gather_per_row`, `gather_per_entry` for the kernel that takes the call otherwise, `dense_per_entry` for
-// the fill work of the dense kernel where that matters (vectors of one value: eight times the entries).
+// the fill work of the dense kernel where that matters (V stores per vector instead of one).
 template <bool kTransposed>
 __global__ void __launch_bounds__(kPlanThreads)
 dense_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__restrict__ cols, const int32_t *__restrict__ src,
                   int shift, int m_vec, int K, int groups, int rows_per_group, int plan_blocks,
                   int32_t *__restrict__ blk_offsets, uint2 *__restrict__ blk_entries, int64_t entry_capacity, int force_dense,
                   float gather_per_row, float gather_per_entry, float dense_per_entry, int32_t *use_dense) {
-    const int sub = (1 << shift) - 1;
-    auto offset_of = [&](int i) { return kTransposed ? __ldg(row_offsets + i) << shift : __ldg(row_offsets + i); };
-    auto column_of = [&](int j) { return kTransposed ? (__ldg(cols + (j >> shift)) << shift) | (j & sub) : __ldg(cols + j); };
-    auto value_of = [&](int j) { return kTransposed ? (__ldg(src + (j >> shift)) << shift) | (j & sub) : j; };
+    auto offset_of = [&](int i) { return __ldg(row_offsets + i); };
+    auto column_of = [&](int j) { return kTransposed ? __ldg(cols + j) << shift : __ldg(cols + j); };
+    auto value_of = [&](int j) { return kTransposed ? __ldg(src + j) : j; };
     extern __shared__ int plan_sh[];
     pdl_launch_dependents();   // the multiplying kernel may set itself up while the plan is made
     {
-        const int64_t nnz = (int64_t)__ldg(row_offsets + m_vec) << (kTransposed ? shift : 0);
+        const int64_t nnz = __ldg(row_offsets + m_vec);
         const float stages = (float)(groups / (kTileM / kGroupRows)) * (float)(plan_blocks / (kBlockK / kPlanCols));
         const float dense_cost = stages * 1100.0f + dense_per_entry * (float)nnz;
         const float gather_cost = (float)m_vec * gather_per_row + gather_per_entry * (float)nnz;
@@ -291,12 +290,27 @@ struct ItemIter {
 // The operand is MN-major (rows of A contiguous) with the 128-byte swizzle: element (row m, column k) of the
 // 128 x 64 block lives at (m / 64) * 8 KiB + (k / 8) * 1 KiB + (k % 8) * 128 + (((m % 64) / 8) ^ (k % 8)) * 16 +
 // (m % 8) * 2, so the V consecutive rows of a vector (V divides 8) are one contiguous store.
-template <int V, typename Raw>
+//
+// kTransposed (the tile is a piece of A^T): the V values of a vector belong to ONE row, columns k .. k + V - 1
+// (k a multiple of V, so they share k / 8): V two-byte stores, 128 bytes apart.
+template <int V, bool kTransposed, typename Raw>
 __device__ __forceinline__ void scatter_vector(uint8_t *a_part, uint32_t packed, const Raw &raw) {
     const uint32_t k = packed & 63u;
-    const uint32_t m = ((packed >> 6) * V) & (kGroupRows - 1);   // first row of the vector inside the group
-    uint8_t *dst = a_part + (m >> 6) * 8192 + (k >> 3) * 1024 + (k & 7u) * 128 + ((((m & 63u) >> 3) ^ (k & 7u)) << 4) + (m & 7u) * 2;
-    *reinterpret_cast<Raw *>(dst) = raw;
+    if constexpr (!kTransposed) {
+        const uint32_t m = ((packed >> 6) * V) & (kGroupRows - 1);   // first row of the vector inside the group
+        uint8_t *dst = a_part + (m >> 6) * 8192 + (k >> 3) * 1024 + (k & 7u) * 128 + ((((m & 63u) >> 3) ^ (k & 7u)) << 4) + (m & 7u) * 2;
+        *reinterpret_cast<Raw *>(dst) = raw;
+    } else {
+        const uint32_t m = (packed >> 6) & (kGroupRows - 1);         // the row inside the group
+        const uint32_t m8 = (m & 63u) >> 3;
+        uint8_t *row = a_part + (m >> 6) * 8192 + (k >> 3) * 1024 + (m & 7u) * 2;
+        const unsigned short *h = reinterpret_cast<const unsigned short *>(&raw);
+#pragma unroll
+        for (uint32_t v = 0; v < (uint32_t)V; ++v) {
+            const uint32_t kk = (k & 7u) + v;
+            *reinterpret_cast<unsigned short *>(row + kk * 128 + ((m8 ^ kk) << 4)) = h[v];
+        }
+    }
 }
 
 template <int V> struct ValueVec;   // the V fp16 values of one nonzero vector, loaded with one instruction
@@ -310,7 +324,7 @@ template <> struct ValueVec<1> { typedef unsigned short Raw; unsigned short raw;
 // {64, 64, 2, 1}, i.e. both boxes of a stage in one copy (the TMA unit works through copies one after the
 // other, and two 8 KiB copies per stage were what the MMAs waited for).  map_out: the output, dimensions {N, rows, batch}, box {32, 32, 1}, swizzle span =
 // the 64 (fp16) or 128 (fp32) bytes of a box row (stores clip at the edges of the matrix).
-template <typename TOut, int V>
+template <typename TOut, int V, bool kTransposed>
 __global__ void __launch_bounds__(kThreads, 1)
 spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_b4, int use_b4,
@@ -367,7 +381,7 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
     const int64_t G = gridDim.x;
     const uint32_t my_items = (total_items > blockIdx.x) ? (uint32_t)((total_items - blockIdx.x + G - 1) / G) : 0u;
     const uint32_t total_stages = my_items * (uint32_t)k_blocks;
-    const int m_rows = p.m_vec * V;
+    const int m_rows = kTransposed ? p.m_vec : p.m_vec * V;   // rows of the output (for A^T, p.m_vec counts its rows)
 
     // Stage g of this CTA (item g / k_blocks, column block g % k_blocks) uses A slot g % kAStages, B slot
     // g % kBStages and the barrier pair of its B slot: `full` collects the four fill warps, the loader's arrival
@@ -448,7 +462,7 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                 typename ValueVec<V>::Raw zero{};
 #pragma unroll
                 for (int u = 0; u < kFillBatches; ++u)
-                    if (p_e0 + lane + 32 * u < p_e1) scatter_vector<V>(a_part, p_pos[u], zero);
+                    if (p_e0 + lane + 32 * u < p_e1) scatter_vector<V, kTransposed>(a_part, p_pos[u], zero);
                 for (int e0 = p_e0 + 32 * kFillBatches; e0 < p_e1; e0 += 32 * kOverflowBatches) {   // denser buckets
                     uint32_t pos[kOverflowBatches];
 #pragma unroll
@@ -458,14 +472,14 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                     }
 #pragma unroll
                     for (int u = 0; u < kOverflowBatches; ++u)
-                        if (e0 + 32 * u + lane < p_e1) scatter_vector<V>(a_part, pos[u], zero);
+                        if (e0 + 32 * u + lane < p_e1) scatter_vector<V, kTransposed>(a_part, pos[u], zero);
                 }
             }
             __syncwarp();
             VS_PROF_ADD(1);   // fill: clear the previous stage's vectors
 #pragma unroll
             for (int u = 0; u < kFillBatches; ++u)
-                if (c_e0 + lane + 32 * u < c_e1) scatter_vector<V>(a_part, c_ent[u].y, c_val[u].raw);
+                if (c_e0 + lane + 32 * u < c_e1) scatter_vector<V, kTransposed>(a_part, c_ent[u].y, c_val[u].raw);
             // buckets with more entries (denser rows): several batches of loads in flight at a time
             for (int e0 = c_e0 + 32 * kFillBatches; e0 < c_e1; e0 += 32 * kOverflowBatches) {
                 uint2 en[kOverflowBatches];
@@ -480,7 +494,7 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                     if (e0 + 32 * u + lane < c_e1) val[u].load(vals + (int64_t)en[u].x * V);
 #pragma unroll
                 for (int u = 0; u < kOverflowBatches; ++u)
-                    if (e0 + 32 * u + lane < c_e1) scatter_vector<V>(a_part, en[u].y, val[u].raw);
+                    if (e0 + 32 * u + lane < c_e1) scatter_vector<V, kTransposed>(a_part, en[u].y, val[u].raw);
             }
             p_e0 = c_e0; p_e1 = c_e1;
 #pragma unroll

@@ -316,6 +316,20 @@ int64_t spmm_plan_bytes(int m_vec, int V, int K, int batch, int64_t stride_value
     if (offsets_out) *offsets_out = offsets_bytes;
     return spmm_plan_header_bytes(spmm_plan_checks(m_vec)) + offsets_bytes + capacity * 8;
 }
+// The plan of A^T for the transposed product: n rows over m_vec * V columns, one entry per nonzero VECTOR of A.
+int64_t spmm_t_plan_bytes(int n, int m_vec, int V, int batch, int64_t stride_values, int64_t *capacity_out, int64_t *offsets_out) {
+    const int64_t M = (int64_t)m_vec * V;
+    const int k_blocks = (int)((M + densespmm::kBlockK - 1) / densespmm::kBlockK);
+    const int m_tiles = (n + densespmm::kTileM - 1) / densespmm::kTileM;
+    const int groups = m_tiles * (densespmm::kTileM / densespmm::kGroupRows);
+    const int plan_blocks = k_blocks * (densespmm::kBlockK / densespmm::kPlanCols);
+    int64_t capacity = (int64_t)n * m_vec;   // at most one vector per (column of A, vector-row)
+    if (batch > 1 && stride_values > 0 && stride_values / V < capacity) capacity = stride_values / V;
+    const int64_t offsets_bytes = (((int64_t)groups * (plan_blocks + 1) * 4) + 15) & ~15ll;
+    if (capacity_out) *capacity_out = capacity;
+    if (offsets_out) *offsets_out = offsets_bytes;
+    return spmm_plan_header_bytes(spmm_plan_checks(n)) + offsets_bytes + capacity * 8;
+}
 // The same for the dense SDDMM: per-row chunk offsets and 8 bytes per mask entry.
 int64_t sddmm_plan_bytes(int m_vec, int n, int nnz_vec, int64_t *offsets_out) {
     const int chunks = (n + densesddmm::kChunk - 1) / densesddmm::kChunk;
@@ -354,7 +368,7 @@ template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStre
     CUtensorMap map_b4 = map;
     const int use_b4 = (p.N % 64 == 0 && make_blocked_map(&map_b4, p.rhs, (uint64_t)p.K, (uint64_t)p.N, (uint64_t)p.batch,
                                                           (uint64_t)p.stride_rhs, densespmm::kTileN / 64) == VS_OK) ? 1 : 0;
-    auto kernel = densespmm::spmm_dense_kernel<TOut, V>;
+    auto kernel = densespmm::spmm_dense_kernel<TOut, V, false>;
     rc = set_smem(kernel, densespmm::kSmemBytes);
     if (rc != VS_OK) return rc;
     uint8_t *plan = nullptr;
@@ -601,11 +615,12 @@ SpmmTMode spmm_t_mode() {   // read at every call, so that a test can switch ker
     return SpmmTMode::kAuto;
 }
 
-// Tensor path of the transposed product: A^T (n x m_vec * V) is handed to the densifying SpMM kernel as a matrix
-// of one-value vectors, its plan built straight from the transposed structure (dense_plan_kernel<true>), the
-// values read where the forward operators keep them.  Costs for the choice, in the plan kernel's units (SM-cycles
-// per 128 columns): the CUDA-core kernel ~5 per scalar entry (0.92 ms for 256 products of 2048 x 512, 90 % sparse,
-// V = 8), the dense kernel ~1100 per stage plus ~1.9 per scalar entry of fill work.
+// Tensor path of the transposed product: A^T (n x m_vec * V) goes through the densifying SpMM kernel, its plan
+// built straight from the transposed structure (dense_plan_kernel<true>), the values read where the forward
+// operators keep them; a vector's V values land side by side in one row of the tile.  Costs for the choice, in the
+// plan kernel's units (SM-cycles per 128 columns): the CUDA-core kernel ~5 per value (0.92 ms for 256 products of
+// 2048 x 512, 90 % sparse, V = 8), the dense kernel ~1100 per stage plus ~1.5 per vector of fill work (0.170 ms on
+// the same problem against 0.137 for the forward product with the same tiles).
 template <typename TOut, int V> int launch_spmm_t(const spmmt::Params &p, int m_vec, cudaStream_t s) {
     DeviceInfo *d;
     int rc = device_info(&d);
@@ -625,7 +640,7 @@ template <typename TOut, int V> int launch_spmm_t(const spmmt::Params &p, int m_
     const int plan_blocks = k_blocks * (densespmm::kBlockK / densespmm::kPlanCols);
     const int rows_per_group = densespmm::kGroupRows;
     int64_t capacity = 0, offsets_bytes = 0;
-    const int64_t plan_bytes = spmm_plan_bytes(q.m_vec, 1, q.K, q.batch, q.stride_values, &capacity, &offsets_bytes);
+    const int64_t plan_bytes = spmm_t_plan_bytes(p.n, m_vec, V, q.batch, q.stride_values, &capacity, &offsets_bytes);
     const int checks = spmm_plan_checks(q.m_vec);
     const size_t plan_words = (size_t)(2 * plan_blocks + rows_per_group + 1), check_words = (size_t)densespmm::kPlanWarps * plan_blocks;
     const size_t plan_smem = (plan_words > check_words ? plan_words : check_words) * 4;
@@ -643,7 +658,7 @@ template <typename TOut, int V> int launch_spmm_t(const spmmt::Params &p, int m_
     CUtensorMap map_b4 = map;
     const int use_b4 = (q.N % 64 == 0 && make_blocked_map(&map_b4, q.rhs, (uint64_t)q.K, (uint64_t)q.N, (uint64_t)q.batch,
                                                           (uint64_t)q.stride_rhs, densespmm::kTileN / 64) == VS_OK) ? 1 : 0;
-    auto kernel = densespmm::spmm_dense_kernel<TOut, 1>;
+    auto kernel = densespmm::spmm_dense_kernel<TOut, V, true>;
     rc = set_smem(kernel, densespmm::kSmemBytes);
     if (rc != VS_OK) return rc;
     uint8_t *plan = nullptr;
@@ -655,7 +670,7 @@ template <typename TOut, int V> int launch_spmm_t(const spmmt::Params &p, int m_
     uint2 *blk_entries = reinterpret_cast<uint2 *>(plan + header_bytes + offsets_bytes);
     densespmm::dense_plan_kernel<true><<<groups + checks, densespmm::kPlanThreads, plan_smem, s>>>(
         p.t_offsets, p.t_rows, p.t_src, shift, q.m_vec, q.K, groups, rows_per_group, plan_blocks, blk_offsets, blk_entries, capacity,
-        mode == SpmmTMode::kDense ? 1 : 0, 0.0f, 5.0f, 1.9f, flag);
+        mode == SpmmTMode::kDense ? 1 : 0, 0.0f, 5.0f * V, 1.5f, flag);
     rc = (int)cudaGetLastError();
     const int64_t items = (int64_t)q.batch * n_tiles * m_tiles;
     const unsigned grid = (unsigned)(items < d->sm_count ? items : d->sm_count);   // one persistent CTA per SM
@@ -959,8 +974,7 @@ VS_EXPORT int64_t vs_spmm_workspace_bytes(int m_vec, int vec_length, int n, int 
 
 VS_EXPORT int64_t vs_spmm_t_workspace_bytes(int m_vec, int vec_length, int n, int batch, int64_t stride_values) {
     if (m_vec <= 0 || n <= 0 || batch < 1 || !valid_v(vec_length) || (int64_t)m_vec * vec_length > 0x7fffffffll) return 0;
-    // the plan of A^T: n rows of one-value vectors over m_vec * vec_length columns
-    const int64_t bytes = spmm_plan_bytes(n, 1, m_vec * vec_length, batch, stride_values, nullptr, nullptr);
+    const int64_t bytes = spmm_t_plan_bytes(n, m_vec, vec_length, batch, stride_values, nullptr, nullptr);
     return bytes <= kMaxPlanBytes ? bytes : 0;
 }
 
