@@ -174,6 +174,28 @@ int vs_attention_cvse(int path, int m_vec, int vec_length, int n, int d, int non
                       const void *q, const void *kmat, const void *vmat, void *out, void *workspace,
                       float scale, int batch, void *stream);
 
+/* Backward of vs_softmax_cvse: grad_scores[j*V+v] = scale * probs[j*V+v] * (grad_probs[j*V+v] - sum over the row's
+ * entries of probs * grad_probs), the gradient with respect to the scores the forward call was given (it applies
+ * `scale` inside).  Same layout, dtype (F16 or F32, fp32 sums), batch and alignment rules as vs_softmax_cvse;
+ * grad_scores may be grad_probs.  No counterpart in the reference (it has no softmax, README.md:76). */
+int vs_softmax_cvse_backward(int dtype, int m_vec, int vec_length, const int32_t *row_offsets, const void *probs,
+                             const void *grad_probs, void *grad_scores, float scale, int batch, int64_t stride,
+                             void *stream);
+
+/* Backward of vs_attention_cvse for fp16 q [m x d], kmat, vmat [n x d] per batch entry and one shared mask:
+ * given grad_out [m x d] it writes grad_q [m x d], grad_k and grad_v [n x d] (fp16).  The probabilities are
+ * recomputed (SDDMM + softmax into probs_workspace), then dV = P^T dO (vs_spmm_t), dP = dO V^T at the mask
+ * (SDDMM), dS = softmax backward (in grad_workspace), dQ = dS K (SpMM), dK = dS^T Q (vs_spmm_t): seven launches of
+ * the operators above on `stream`.  t_offsets / t_rows / t_src: the mask's transposed structure from
+ * vs_cvse_transpose.  Both workspaces hold batch * nonzeros_vec * vec_length fp16 values and must differ.
+ * No counterpart in the reference. */
+int vs_attention_cvse_backward(int path, int m_vec, int vec_length, int n, int d, int nonzeros_vec,
+                               const int32_t *row_indices, const int32_t *row_offsets, const int32_t *col_indices,
+                               const int32_t *t_offsets, const int32_t *t_rows, const int32_t *t_src, const void *q,
+                               const void *kmat, const void *vmat, const void *grad_out, void *grad_q, void *grad_k,
+                               void *grad_v, void *probs_workspace, void *grad_workspace, float scale, int batch,
+                               void *stream);
+
 /* vs_attention_cvse for callers that may not allocate device memory.  No counterpart in the reference.
  *
  * Some hosts of this library cannot hand it a workspace: an inference runtime that plans all device memory

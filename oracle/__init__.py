@@ -163,6 +163,64 @@ def attention(m_vec, V, d, dv, row_offsets, col_indices, Q, K, Vm, scale):
     return out
 
 
+def softmax_backward(m_vec, V, row_offsets, probs, grad_probs, scale):
+    """Gradient of `softmax` with respect to its scores, fp64: scale * p * (g - sum_row(p * g)) per real row.  Numpy,
+    one vector-row at a time.  No reference counterpart (the reference has no softmax): parity unpinned."""
+    ro = np.asarray(row_offsets, dtype=np.int64)
+    p = np.asarray(probs, dtype=np.float64).reshape(-1, V)
+    g = np.asarray(grad_probs, dtype=np.float64).reshape(-1, V)
+    out = np.zeros_like(p)
+    for i in range(m_vec):
+        b, e = ro[i], ro[i + 1]
+        if e > b:
+            dot = (p[b:e] * g[b:e]).sum(axis=0, keepdims=True)
+            out[b:e] = scale * p[b:e] * (g[b:e] - dot)
+    return out.reshape(-1)
+
+
+def attention_backward(m_vec, V, d, row_offsets, col_indices, Q, K, Vm, dO, scale):
+    """(dQ, dK, dV) of `attention` for one head, fp64 throughout (intermediates are not rounded): the composition
+    P = softmax(scale * sddmm(Q, K)); dV = P^T dO; dP = sddmm(dO, Vm); dS = softmax_backward(P, dP); dQ = dS K;
+    dK = dS^T Q over the oracle's own loops, each with a double accumulator.  Parity unpinned by the reference."""
+    n = np.asarray(K).shape[0]
+    lib_ = lib()
+    ro, rop = _i32(row_offsets)
+    ci, cip = _i32(col_indices)
+
+    def sddmm64(lhs, rhs):
+        l, lp = _f32(np.asarray(lhs, dtype=np.float32))
+        r, rp = _f32(np.asarray(rhs, dtype=np.float32))
+        out = np.empty(int(ro[m_vec]) * V, dtype=np.float64)
+        lib_.vso_sddmm_f64(m_vec, d, V, rop, cip, lp, rp, out.ctypes.data_as(_F64P), 1)
+        return out
+
+    def dense_of(vals):   # A [M, n] in double from CVSE values in double
+        A = np.zeros((m_vec * V, n), dtype=np.float64)
+        v = vals.reshape(-1, V)
+        for i in range(m_vec):
+            for j in range(ro[i], ro[i + 1]):
+                A[i * V:(i + 1) * V, ci[j]] += v[j]
+        return A
+
+    s = sddmm64(Q, K)
+    sv = s.reshape(-1, V) * scale   # softmax in double from the double scores, so nothing is rounded on the way
+    Pm = np.zeros_like(sv)
+    for i in range(m_vec):
+        b, e = ro[i], ro[i + 1]
+        if e > b:
+            ex = np.exp(sv[b:e] - sv[b:e].max(axis=0, keepdims=True))
+            Pm[b:e] = ex / ex.sum(axis=0, keepdims=True)
+    P = Pm.reshape(-1)
+    dO64 = np.asarray(dO, dtype=np.float64)
+    dP = sddmm64(dO, Vm)
+    dS = softmax_backward(m_vec, V, ro, P, dP, scale)
+    Pd, dSd = dense_of(P), dense_of(dS)
+    dV = Pd.T @ dO64
+    dQ = dSd @ np.asarray(K, dtype=np.float64)
+    dK = dSd.T @ np.asarray(Q, dtype=np.float64)
+    return dQ, dK, dV
+
+
 def f32_to_h16(a):
     a = np.ascontiguousarray(a, dtype=np.float32)
     out = np.empty(a.shape, dtype=np.float16)

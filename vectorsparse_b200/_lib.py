@@ -42,6 +42,8 @@ SIGNATURES = {
     "vs_sddmm_batched": (_i, [_i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i64, _i64, _i64, _vp, _i]),
     "vs_softmax_cvse": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _f, _i, _i64, _vp]),
     "vs_attention_cvse": (_i, [_i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _vp]),
+    "vs_softmax_cvse_backward": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _f, _i, _i64, _vp]),
+    "vs_attention_cvse_backward": (_i, [_i, _i, _i, _i, _i, _i] + [_vp] * 15 + [_f, _i, _vp]),
     "vs_attention_cvse_static": (_i, [_i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _vp]),
     "vs_spmm_host": (_i, [_i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "vs_sddmm_host": (_i, [_i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),

@@ -356,4 +356,76 @@ __global__ void __launch_bounds__(kCcThreads) softmax_cvse_kernel(const SoftmaxP
     }
 }
 
+// Backward of the masked row softmax: for every real row r = i*V+v, over the entries j of vector-row i,
+//   grad_scores[j*V+v] = scale * probs[j*V+v] * (grad_probs[j*V+v] - sum_j probs[j*V+v] * grad_probs[j*V+v]).
+// (The forward kernel applies `scale` to the scores inside, so the gradient with respect to the scores it was
+// given carries the factor.)  One warp per vector-row, two passes over the row (the second comes from L1/L2),
+// fp32 sums; grad_scores may be grad_probs.  The reference has no softmax (README.md:76 points to an external
+// repository for the attention layer).
+struct SoftmaxBackwardParams {
+    int m_vec;
+    const int32_t *row_offsets;
+    const void *probs;
+    const void *grad_probs;
+    void *grad_scores;
+    int64_t stride;  // in elements, between batch entries
+    float scale;
+};
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kCcThreads) softmax_cvse_backward_kernel(const SoftmaxBackwardParams p) {
+    using EW = EntryWords<T, V>;
+    const int warp = (blockIdx.x * kCcThreads + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= p.m_vec) return;
+    const int64_t at = (int64_t)blockIdx.y * p.stride;
+    const T *pr = static_cast<const T *>(p.probs) + at;
+    const T *gp = static_cast<const T *>(p.grad_probs) + at;
+    T *gs = static_cast<T *>(p.grad_scores) + at;
+    const int beg = __ldg(p.row_offsets + warp), end = __ldg(p.row_offsets + warp + 1);
+    float dot[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) dot[v] = 0.f;
+    for (int j = beg + lane; j < end; j += 32) {
+        float a[V], g[V];
+        if constexpr (EW::kVector) {
+            uint32_t wa[EW::kWords], wg[EW::kWords];
+            EW::load(pr + (int64_t)j * V, wa);
+            EW::load(gp + (int64_t)j * V, wg);
+            EW::unpack(wa, a);
+            EW::unpack(wg, g);
+        } else {
+            a[0] = (float)pr[j];
+            g[0] = (float)gp[j];
+        }
+#pragma unroll
+        for (int v = 0; v < V; ++v) dot[v] = fmaf(a[v], g[v], dot[v]);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+        for (int v = 0; v < V; ++v) dot[v] += __shfl_xor_sync(0xffffffffu, dot[v], off);
+    __syncwarp();   // in-place use: every lane has read the row before any lane overwrites its part
+    for (int j = beg + lane; j < end; j += 32) {
+        float a[V], g[V], o[V];
+        if constexpr (EW::kVector) {
+            uint32_t wa[EW::kWords], wg[EW::kWords];
+            EW::load(pr + (int64_t)j * V, wa);
+            EW::load(gp + (int64_t)j * V, wg);
+            EW::unpack(wa, a);
+            EW::unpack(wg, g);
+        } else {
+            a[0] = (float)pr[j];
+            g[0] = (float)gp[j];
+        }
+#pragma unroll
+        for (int v = 0; v < V; ++v) o[v] = p.scale * a[v] * (g[v] - dot[v]);
+        if constexpr (EW::kVector) {
+            EW::store(gs + (int64_t)j * V, o);
+        } else {
+            gs[j] = (T)o[0];
+        }
+    }
+}
+
 }  // namespace vs

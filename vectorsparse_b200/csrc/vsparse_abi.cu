@@ -541,6 +541,19 @@ template <typename T> int softmax_by_v(int V, const SoftmaxParams &p, cudaStream
     return (int)cudaGetLastError();
 }
 
+template <typename T> int softmax_backward_by_v(int V, const SoftmaxBackwardParams &p, int batch, cudaStream_t s) {
+    const int64_t blocks = ((int64_t)p.m_vec * 32 + kCcThreads - 1) / kCcThreads;
+    dim3 grid((unsigned)blocks, (unsigned)batch, 1);
+    switch (V) {
+        case 1: softmax_cvse_backward_kernel<T, 1><<<grid, kCcThreads, 0, s>>>(p); break;
+        case 2: softmax_cvse_backward_kernel<T, 2><<<grid, kCcThreads, 0, s>>>(p); break;
+        case 4: softmax_cvse_backward_kernel<T, 4><<<grid, kCcThreads, 0, s>>>(p); break;
+        case 8: softmax_cvse_backward_kernel<T, 8><<<grid, kCcThreads, 0, s>>>(p); break;
+        default: return VS_ERR_VEC_LENGTH;
+    }
+    return (int)cudaGetLastError();
+}
+
 constexpr int kMaxBatch = 65535;  // grid.y of the CUDA-core kernels
 
 }  // namespace
@@ -797,6 +810,68 @@ VS_EXPORT int vs_softmax_cvse(int dtype, int m_vec, int vec_length, const int32_
     p.stride = stride; p.scale = scale;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return dtype == VS_F16 ? softmax_by_v<__half>(vec_length, p, s) : softmax_by_v<float>(vec_length, p, s);
+}
+
+VS_EXPORT int vs_softmax_cvse_backward(int dtype, int m_vec, int vec_length, const int32_t *row_offsets, const void *probs,
+                                       const void *grad_probs, void *grad_scores, float scale, int batch, int64_t stride,
+                                       void *stream) {
+    if (!valid_v(vec_length)) return VS_ERR_VEC_LENGTH;
+    if (dtype != VS_F16 && dtype != VS_F32) return VS_ERR_DTYPE;
+    if (m_vec < 0) return VS_ERR_SHAPE;
+    if (batch < 1 || batch > kMaxBatch) return VS_ERR_ARG;
+    if (m_vec == 0) return VS_OK;
+    if (!row_offsets || !probs || !grad_probs || !grad_scores) return VS_ERR_NULL;
+    if (stride < 0 || (batch > 1 && stride == 0)) return VS_ERR_ARG;
+    {   // one entry (V values) is read and written as one vector of up to 16 bytes
+        const size_t entry = (size_t)vec_length * elem_size(dtype), al = entry < 16 ? entry : 16;
+        if (reinterpret_cast<uintptr_t>(probs) % al || reinterpret_cast<uintptr_t>(grad_probs) % al ||
+            reinterpret_cast<uintptr_t>(grad_scores) % al || ((size_t)stride * elem_size(dtype)) % al)
+            return VS_ERR_ALIGN;
+    }
+    SoftmaxBackwardParams p;
+    p.m_vec = m_vec; p.row_offsets = row_offsets; p.probs = probs; p.grad_probs = grad_probs; p.grad_scores = grad_scores;
+    p.stride = stride; p.scale = scale;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return dtype == VS_F16 ? softmax_backward_by_v<__half>(vec_length, p, batch, s)
+                           : softmax_backward_by_v<float>(vec_length, p, batch, s);
+}
+
+VS_EXPORT int vs_attention_cvse_backward(int path, int m_vec, int vec_length, int n, int d, int nonzeros_vec,
+                                         const int32_t *row_indices, const int32_t *row_offsets, const int32_t *col_indices,
+                                         const int32_t *t_offsets, const int32_t *t_rows, const int32_t *t_src, const void *q,
+                                         const void *kmat, const void *vmat, const void *grad_out, void *grad_q, void *grad_k,
+                                         void *grad_v, void *probs_workspace, void *grad_workspace, float scale, int batch,
+                                         void *stream) {
+    if ((!probs_workspace || !grad_workspace) && nonzeros_vec > 0) return VS_ERR_NULL;
+    if (probs_workspace && probs_workspace == grad_workspace) return VS_ERR_ARG;
+    const int64_t m = (int64_t)m_vec * vec_length;
+    const int64_t s_ws = (int64_t)nonzeros_vec * vec_length;
+    if ((s_ws * 2) % 16 != 0 && batch > 1) return VS_ERR_ALIGN;
+    const int64_t s_q = m * d, s_k = (int64_t)n * d;
+    // P = softmax(scale * Q K^T) at the mask, recomputed rather than kept from the forward pass
+    int rc = vs_sddmm_batched(path, VS_F16, VS_F16, m_vec, d, n, nonzeros_vec, row_indices, row_offsets, col_indices, q, kmat,
+                              probs_workspace, vec_length, batch, s_q, s_k, s_ws, stream, 0);
+    if (rc != VS_OK) return rc;
+    rc = vs_softmax_cvse(VS_F16, m_vec, vec_length, row_indices, row_offsets, probs_workspace, probs_workspace, scale, batch,
+                         s_ws, stream);
+    if (rc != VS_OK) return rc;
+    // dV = P^T dO
+    rc = vs_spmm_t_batched(VS_F16, VS_F16, m_vec, vec_length, d, n, t_offsets, t_rows, t_src, probs_workspace, grad_out, grad_v,
+                           batch, s_ws, s_q, s_k, stream);
+    if (rc != VS_OK) return rc;
+    // dP = dO V^T at the mask; dS = scale * P o (dP - rowsum(P o dP))
+    rc = vs_sddmm_batched(path, VS_F16, VS_F16, m_vec, d, n, nonzeros_vec, row_indices, row_offsets, col_indices, grad_out, vmat,
+                          grad_workspace, vec_length, batch, s_q, s_k, s_ws, stream, 0);
+    if (rc != VS_OK) return rc;
+    rc = vs_softmax_cvse_backward(VS_F16, m_vec, vec_length, row_offsets, probs_workspace, grad_workspace, grad_workspace, scale,
+                                  batch, s_ws, stream);
+    if (rc != VS_OK) return rc;
+    // dQ = dS K,  dK = dS^T Q
+    rc = vs_spmm_batched(path, VS_F16, VS_F16, m_vec, vec_length, d, n, row_indices, row_offsets, col_indices, grad_workspace,
+                         kmat, grad_q, batch, s_ws, s_k, s_q, stream);
+    if (rc != VS_OK) return rc;
+    return vs_spmm_t_batched(VS_F16, VS_F16, m_vec, vec_length, d, n, t_offsets, t_rows, t_src, grad_workspace, q, grad_k, batch,
+                             s_ws, s_q, s_k, stream);
 }
 
 VS_EXPORT int vs_attention_cvse(int path, int m_vec, int vec_length, int n, int d, int nonzeros_vec,

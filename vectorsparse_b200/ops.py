@@ -192,6 +192,39 @@ def attention_cvse(path, m_vec, vec_length, n, d, nonzeros_vec, row_indices, row
     return 0
 
 
+def softmax_cvse_backward(m_vec, vec_length, row_offsets, probs, grad_probs, grad_scores, scale=1.0):
+    """Gradient of softmax_cvse with respect to its scores; all three [nnz] or [B, nnz]; grad_scores may be grad_probs."""
+    batch = probs.shape[0] if probs.dim() == 2 else 1
+    stride = probs.stride(0) if probs.dim() == 2 and batch > 1 else 0
+    rc = _lib.lib().vs_softmax_cvse_backward(_dtype_code(probs, "probs"), m_vec, vec_length,
+                                             _dev(row_offsets, "row_offsets", torch.int32), _dev(probs, "probs"),
+                                             _dev(grad_probs, "grad_probs", probs.dtype),
+                                             _dev(grad_scores, "grad_scores", probs.dtype), float(scale), batch, stride,
+                                             _stream())
+    _lib.check(rc, "vs_softmax_cvse_backward")
+    return 0
+
+
+def attention_cvse_backward(path, m_vec, vec_length, n, d, nonzeros_vec, row_indices, row_offsets, col_indices, t_offsets,
+                            t_rows, t_src, q, kmat, vmat, grad_out, grad_q, grad_k, grad_v, probs_workspace, grad_workspace,
+                            scale):
+    """Gradients of attention_cvse for [B, ., d] fp16 tensors sharing one mask; both workspaces [B, nnz] fp16."""
+    batch = q.shape[0] if q.dim() == 3 else 1
+    for w, name in ((probs_workspace, "probs_workspace"), (grad_workspace, "grad_workspace")):
+        _need(w, batch * nonzeros_vec * vec_length, name)
+    f16 = torch.float16
+    rc = _lib.lib().vs_attention_cvse_backward(
+        path, m_vec, vec_length, n, d, nonzeros_vec, _dev(row_indices, "row_indices", torch.int32),
+        _dev(row_offsets, "row_offsets", torch.int32), _dev(col_indices, "col_indices", torch.int32),
+        _dev(t_offsets, "t_offsets", torch.int32), _dev(t_rows, "t_rows", torch.int32), _dev(t_src, "t_src", torch.int32),
+        _dev(q, "q", f16), _dev(kmat, "kmat", f16), _dev(vmat, "vmat", f16), _dev(grad_out, "grad_out", f16),
+        _dev(grad_q, "grad_q", f16), _dev(grad_k, "grad_k", f16), _dev(grad_v, "grad_v", f16),
+        _dev(probs_workspace, "probs_workspace", f16), _dev(grad_workspace, "grad_workspace", f16), float(scale), batch,
+        _stream())
+    _lib.check(rc, "vs_attention_cvse_backward")
+    return 0
+
+
 def set_workspace(buffer=None) -> None:
     """Hands the tensor-path kernels a caller-owned plan scratch (a CUDA uint8 tensor) for the calls of this host
     thread, or returns to the library's own per-stream buffers (None).  See include/vsparse_b200.h."""
