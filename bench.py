@@ -45,6 +45,10 @@ WORKLOADS = {
     "sddmm_v8_s90": dict(op="sddmm", M=2048, K=512, V=8, s=0.9, N=256, inst=256, kind="beta"),
     # product with the transposed sparse matrix (vs_spmm_t): out [K x N] = A^T . rhs, rhs [M x N]
     "spmm_t_v8_s90": dict(op="spmm_t", M=2048, K=512, V=8, s=0.9, N=256, inst=256, kind="beta"),
+    # config 5: fixed-mask sparse attention, batch 8 x 16 heads = 128 problems sharing one band + strided mask,
+    # sequence 4096, head dimension 64 (N), V = 8, 90 % sparse; forward (SDDMM -> softmax -> SpMM) and backward
+    "attention_cfg5": dict(op="attention", M=4096, K=4096, V=8, s=0.9, N=64, inst=128, kind="band", band=256),
+    "attention_bwd_cfg5": dict(op="attention_bwd", M=4096, K=4096, V=8, s=0.9, N=64, inst=128, kind="band", band=256),
     "spmm_cc_v8_s90": dict(op="spmm", M=2048, K=512, V=8, s=0.9, N=256, inst=256, kind="beta", path=1),
     # fp32 CUDA-core SpMM (the cudaSpmm entry point), M = K = 4096, uniform random positions, values and B U(-1,1)
     "spmm_f32_v4_s90_n1024": dict(op="spmm", M=4096, K=4096, V=4, s=0.9, N=1024, inst=8, kind="uniform", path=1, dtype="f32"),
@@ -63,6 +67,12 @@ NCU_TRAFFIC_BYTES = {
 def kernels_per_step(w, a=None):
     """Names of the library's kernels one step launches (the count is what `gpu_launches` reports)."""
     tensor = w.get("path") != 1
+    if w["op"] == "attention":
+        return ["sddmm_tma_kernel", "softmax_cvse_kernel", "dense_plan_kernel", "spmm_dense_kernel",
+                "spmm_tma_kernel (returns at once unless the plan kernel chose it)"]
+    if w["op"] == "attention_bwd":
+        plan3 = ["dense_plan_kernel", "spmm_dense_kernel", "fallback kernel (returns at once unless the plan kernel chose it)"]
+        return ["sddmm_tma_kernel", "softmax_cvse_kernel"] + plan3 + ["sddmm_tma_kernel", "softmax_cvse_backward_kernel"] + plan3 + plan3
     if w["op"] == "spmm_t":
         if os.environ.get("VSPARSE_B200_SPMM_T") == "gather":
             return ["spmm_t_kernel"]
@@ -80,6 +90,13 @@ def kernels_per_step(w, a=None):
     from vectorsparse_b200 import _lib
     dense = a is not None and _lib.lib().vs_sddmm_formulation(a.m_vec, w["N"], w["K"], a.nnz_vec, w["V"]) == 1
     return ["sddmm_plan_kernel", "sddmm_dense_kernel"] if dense else ["sddmm_tma_kernel"]
+
+
+def metric_name(w):
+    return {"sddmm": "SDDMM effective TFLOP/s (2*nnz*k)",
+            "attention": "sparse attention effective TFLOP/s (2 products: 4*nnz*d)",
+            "attention_bwd": "sparse attention backward effective TFLOP/s (5 products: 10*nnz*d)",
+            }.get(w["op"], "SpMM effective TFLOP/s (2*nnz*N)")
 
 
 def measured_peaks():
@@ -137,8 +154,8 @@ class ClockSampler:
 
 def build_problem(w, seed=2026):
     from vectorsparse_b200 import cvse
-    kind = {"beta": cvse.GEN_BETA, "fixed": cvse.GEN_FIXED, "uniform": cvse.GEN_UNIFORM}[w["kind"]]
-    a = cvse.generate(kind, seed, w["M"] // w["V"], w["K"], w["V"], w["s"])
+    kind = {"beta": cvse.GEN_BETA, "fixed": cvse.GEN_FIXED, "uniform": cvse.GEN_UNIFORM, "band": cvse.GEN_BAND}[w["kind"]]
+    a = cvse.generate(kind, seed, w["M"] // w["V"], w["K"], w["V"], w["s"], w.get("band", 0))
     return a
 
 
@@ -151,6 +168,15 @@ def algorithmic(w, a):
         k_touched = int(np.unique(a.col_indices).size)
         per = nnz_vec * V * es + k_touched * w["N"] * es + w["M"] * w["N"] * es
         flops = 2.0 * nnz_vec * V * w["N"]
+    elif w["op"] in ("attention", "attention_bwd"):
+        # unfused pipeline: the dense operands once each, the score / probability arrays once per pass over them
+        d, n, nnz = w["N"], w["K"], nnz_vec * V
+        if w["op"] == "attention":   # q, k, v in, o out; scores written, read + written by the softmax, read by the SpMM
+            per = 4 * n * d * 2 + 4 * nnz * 2
+            flops = 2 * 2.0 * nnz * d
+        else:                        # q, k, v, dO in, dq, dk, dv out; P: w, r, w, r, r; dP / dS: w, r, w, r, r
+            per = 7 * n * d * 2 + 10 * nnz * 2
+            flops = 5 * 2.0 * nnz * d
     elif w["op"] == "spmm_t":  # rhs M x N (the rows of nonempty vector-rows), out K x N
         rows_touched = int(np.count_nonzero(np.diff(a.row_offsets))) * V
         per = nnz_vec * V * es + rows_touched * w["N"] * es + w["K"] * w["N"] * es
@@ -198,6 +224,25 @@ def run_ours(args):
 
         def launch(d_a, d_b, out):
             ops.spmm_batched(path, a.m_vec, V, N, K, ri, ro, ci, d_a, d_b, out)
+    elif w["op"] in ("attention", "attention_bwd"):
+        # inputs stacked in one pinned array (q, k, v and, for the backward pass, dO), outputs in another
+        bwd = w["op"] == "attention_bwd"
+        n, d = K, N
+        h_a = torch.from_numpy(cvse.fill_random((4 if bwd else 3, inst, n, d), np.float16, cvse.DIST_NORMAL, seed, 1.0)).pin_memory()
+        h_b = torch.zeros(8, dtype=torch.float16).pin_memory()   # the second input slot of the harness: unused here
+        h_out = torch.empty((3 if bwd else 1, inst, n, d), dtype=torch.float16).pin_memory()
+        d_out = torch.empty((3 if bwd else 1, inst, n, d), dtype=torch.float16, device=dev)
+        ws_p = torch.empty((inst, a.nnz_vec * V), dtype=torch.float16, device=dev)
+        ws_g = torch.empty((inst, a.nnz_vec * V), dtype=torch.float16, device=dev) if bwd else None
+        if bwd:
+            t_off, t_rows, t_src = (torch.from_numpy(x).to(dev) for x in cvse.transpose(a))
+
+        def launch(d_a, d_b, out):
+            if bwd:
+                ops.attention_cvse_backward(path, a.m_vec, V, n, d, a.nnz_vec, ri, ro, ci, t_off, t_rows, t_src, d_a[0], d_a[1],
+                                            d_a[2], d_a[3], out[0], out[1], out[2], ws_p, ws_g, 0.125)
+            else:
+                ops.attention_cvse(path, a.m_vec, V, n, d, a.nnz_vec, ri, ro, ci, d_a[0], d_a[1], d_a[2], out[0], ws_p, 0.125)
     elif w["op"] == "spmm_t":
         row = (a.nnz_vec * V + 7) // 8 * 8
         t_off, t_rows, t_src = (torch.from_numpy(x).to(dev) for x in cvse.transpose(a))
@@ -328,7 +373,7 @@ def run_ours(args):
         h2d = h_a.numel() * h_a.element_size() + h_b.numel() * h_b.element_size()
         d2h = h_out.numel() * h_out.element_size()
         line = {
-            "metric": "SDDMM effective TFLOP/s (2*nnz*k)" if w["op"] == "sddmm" else "SpMM effective TFLOP/s (2*nnz*N)",
+            "metric": metric_name(w),
             "value": flops * args.steps * world / (total_ms * 1e-3) / 1e12,
             "unit": "TFLOP/s",
             "n_gpus": world,
@@ -343,7 +388,7 @@ def run_ours(args):
             "config": {"workload": args.workload, "op": w["op"], "M": M, "K": K, "V": V, "sparsity": w["s"],
                        "dense_width_or_k": N, "nnz_vec": a.nnz_vec, "instances_per_step": inst,
                        "path": "cuda-core" if path == VS_PATH_CUDA_CORE else "tensor (tcgen05)",
-                       "l2": "working set 3x L2 (distinct operands per instance), no flush needed",
+                       "l2": "working set larger than L2 (distinct operands per instance), no flush needed",
                        "parallelism": f"independent streams x{world}"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"of {peak_kind}",
@@ -387,6 +432,16 @@ def cpu_leg(w, a, budget_s, threads=None):
             if use_ref:
                 return oracle.ref_spmm(a.m_vec, V, N, a.row_offsets, a.col_indices, x, y)
             return oracle.spmm(a.m_vec, V, N, a.row_offsets, a.col_indices, x, y, acc="f32", threads=1)
+    elif w["op"] in ("attention", "attention_bwd"):   # no reference code: the oracle's fp64 pipeline, one head per call
+        use_ref = False
+        n, d = K, N
+        q, kk, vv, go = (cvse.fill_random((n, d), np.float16, cvse.DIST_NORMAL, 1 + i, 1.0).astype(np.float32) for i in range(4))
+        flops = (5 if w["op"] == "attention_bwd" else 2) * 2.0 * a.nnz_vec * V * d
+
+        def one(_):
+            if w["op"] == "attention_bwd":
+                return oracle.attention_backward(a.m_vec, V, d, a.row_offsets, a.col_indices, q, kk, vv, go, 0.125)
+            return oracle.attention(a.m_vec, V, d, d, a.row_offsets, a.col_indices, q, kk, vv, 0.125)
     elif w["op"] == "spmm_t":   # no reference code for this product: the oracle's loop is the CPU path
         use_ref = False
         x = cvse.fill_random((a.nnz_vec * V,), np.float16, cvse.DIST_NORMAL, 1, 0.02).astype(np.float32)
@@ -437,7 +492,7 @@ def run_reference(args):
     base["value"] = v
     line = {
         "impl": "reference",
-        "metric": "SDDMM effective TFLOP/s (2*nnz*k)" if w["op"] == "sddmm" else "SpMM effective TFLOP/s (2*nnz*N)",
+        "metric": metric_name(w),
         "value": v, "unit": "TFLOP/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": steps,
         "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
@@ -445,7 +500,7 @@ def run_reference(args):
                    "sparsity": w["s"], "dense_width_or_k": w["N"], "nnz_vec": a.nnz_vec,
                    "instances_per_step": w["inst"], "path": "host loop (spmm_benchmark.cpp:66-86)" if w["op"] == "spmm" else
                    "host loop (include/bm_test_utils.h:171-193)" if w["op"] == "sddmm" else
-                   "host loop of the oracle (the reference has no transposed product)"},
+                   "host loops of the oracle (the reference has no such operator)"},
         "cpu_baseline": base,
         "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,

@@ -612,7 +612,9 @@ int launch_spmm_t_cc(const spmmt::Params &p, cudaStream_t s, DeviceInfo *d, cons
     const int row_groups = (p.n + spmmt::kWarps - 1) / spmmt::kWarps;
     const int chunks = (p.N + spmmt::kChunk - 1) / spmmt::kChunk;
     const int64_t items = (int64_t)p.batch * chunks * row_groups;
-    const int64_t cap = (int64_t)d->sm_count * 64;   // a few waves of 128-thread CTAs; the rest by grid stride
+    const int64_t cap = (int64_t)d->sm_count * 16;   // as many 128-thread CTAs as are resident at once; the rest by grid stride
+                                                      // (behind the dense kernel the launch usually returns at once: 9472 CTAs
+                                                      // took 14 us to do so, a quarter of them a quarter of that)
     const unsigned grid = (unsigned)(items < cap ? items : cap);
     auto kernel = spmmt::spmm_t_kernel<TOut, V>;
     if (plan_hdr) return (int)launch_overlapped(kernel, grid, spmmt::kThreads, 0, s, p, items, row_groups, chunks, plan_hdr, plan_checks);
