@@ -438,6 +438,9 @@ def cpu_leg(w, a, budget_s, threads=None):
         q, kk, vv, go = (cvse.fill_random((n, d), np.float16, cvse.DIST_NORMAL, 1 + i, 1.0).astype(np.float32) for i in range(4))
         flops = (5 if w["op"] == "attention_bwd" else 2) * 2.0 * a.nnz_vec * V * d
 
+        if w["op"] == "attention_bwd":
+            cores = 1   # the backward oracle is numpy / scipy code that holds the interpreter lock: threads would not add up
+
         def one(_):
             if w["op"] == "attention_bwd":
                 return oracle.attention_backward(a.m_vec, V, d, a.row_offsets, a.col_indices, q, kk, vv, go, 0.125)

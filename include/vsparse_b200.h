@@ -185,7 +185,7 @@ int vs_softmax_cvse_backward(int dtype, int m_vec, int vec_length, const int32_t
 /* Backward of vs_attention_cvse for fp16 q [m x d], kmat, vmat [n x d] per batch entry and one shared mask:
  * given grad_out [m x d] it writes grad_q [m x d], grad_k and grad_v [n x d] (fp16).  The probabilities are
  * recomputed (SDDMM + softmax into probs_workspace), then dV = P^T dO (vs_spmm_t), dP = dO V^T at the mask
- * (SDDMM), dS = softmax backward (in grad_workspace), dQ = dS K (SpMM), dK = dS^T Q (vs_spmm_t): seven launches of
+ * (SDDMM), dS = softmax backward (in grad_workspace), dQ = dS K (SpMM), dK = dS^T Q (vs_spmm_t): seven calls of
  * the operators above on `stream`.  t_offsets / t_rows / t_src: the mask's transposed structure from
  * vs_cvse_transpose.  Both workspaces hold batch * nonzeros_vec * vec_length fp16 values and must differ.
  * No counterpart in the reference. */

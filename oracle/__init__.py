@@ -194,13 +194,13 @@ def attention_backward(m_vec, V, d, row_offsets, col_indices, Q, K, Vm, dO, scal
         lib_.vso_sddmm_f64(m_vec, d, V, rop, cip, lp, rp, out.ctypes.data_as(_F64P), 1)
         return out
 
-    def dense_of(vals):   # A [M, n] in double from CVSE values in double
-        A = np.zeros((m_vec * V, n), dtype=np.float64)
-        v = vals.reshape(-1, V)
-        for i in range(m_vec):
-            for j in range(ro[i], ro[i + 1]):
-                A[i * V:(i + 1) * V, ci[j]] += v[j]
-        return A
+    row_of = np.repeat(np.arange(m_vec, dtype=np.int64), np.diff(ro.astype(np.int64)))
+    rows = (row_of[:, None] * V + np.arange(V, dtype=np.int64)[None, :]).reshape(-1)
+    cols = np.repeat(ci[:int(ro[m_vec])].astype(np.int64), V)
+
+    def matrix_of(vals):   # A [M, n] in double from CVSE values in double (repeated columns add up), kept sparse
+        from scipy.sparse import coo_matrix
+        return coo_matrix((vals, (rows, cols)), shape=(m_vec * V, n)).tocsr()
 
     s = sddmm64(Q, K)
     sv = s.reshape(-1, V) * scale   # softmax in double from the double scores, so nothing is rounded on the way
@@ -214,10 +214,10 @@ def attention_backward(m_vec, V, d, row_offsets, col_indices, Q, K, Vm, dO, scal
     dO64 = np.asarray(dO, dtype=np.float64)
     dP = sddmm64(dO, Vm)
     dS = softmax_backward(m_vec, V, ro, P, dP, scale)
-    Pd, dSd = dense_of(P), dense_of(dS)
-    dV = Pd.T @ dO64
-    dQ = dSd @ np.asarray(K, dtype=np.float64)
-    dK = dSd.T @ np.asarray(Q, dtype=np.float64)
+    Pd, dSd = matrix_of(P), matrix_of(dS)
+    dV = np.asarray(Pd.T @ dO64)
+    dQ = np.asarray(dSd @ np.asarray(K, dtype=np.float64))
+    dK = np.asarray(dSd.T @ np.asarray(Q, dtype=np.float64))
     return dQ, dK, dV
 
 

@@ -52,7 +52,7 @@ def test_softmax_backward_batched():
 
 @pytest.mark.parametrize("path", [VS_PATH_TENSOR, VS_PATH_CUDA_CORE])
 def test_attention_backward_small(path):
-    """Seven launches (SDDMM, softmax, SpMM^T, SDDMM, softmax backward, SpMM, SpMM^T) on a band + strided mask,
+    """Seven operator calls (SDDMM, softmax, SpMM^T, SDDMM, softmax backward, SpMM, SpMM^T) on a band + strided mask,
     two heads sharing it; intermediates are fp16 on the GPU and double in the oracle."""
     V, d, n, heads = 8, 64, 512, 2
     a = problem(cvse.GEN_BAND, 6, n // V, n, V, 0.8, band=64)
