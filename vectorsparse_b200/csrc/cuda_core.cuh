@@ -359,8 +359,8 @@ __global__ void __launch_bounds__(kCcThreads) softmax_cvse_kernel(const SoftmaxP
 // Backward of the masked row softmax: for every real row r = i*V+v, over the entries j of vector-row i,
 //   grad_scores[j*V+v] = scale * probs[j*V+v] * (grad_probs[j*V+v] - sum_j probs[j*V+v] * grad_probs[j*V+v]).
 // (The forward kernel applies `scale` to the scores inside, so the gradient with respect to the scores it was
-// given carries the factor.)  One warp per vector-row, two passes over the row (the second comes from L1/L2),
-// fp32 sums; grad_scores may be grad_probs.  The reference has no softmax (README.md:76 points to an external
+// given carries the factor.)  One warp per vector-row; rows that fit the lanes' registers are read once, longer ones
+// twice (the second pass comes from L1/L2); fp32 sums; grad_scores may be grad_probs.  The reference has no softmax (README.md:76 points to an external
 // repository for the attention layer).
 struct SoftmaxBackwardParams {
     int m_vec;
@@ -386,6 +386,49 @@ __global__ void __launch_bounds__(kCcThreads) softmax_cvse_backward_kernel(const
     float dot[V];
 #pragma unroll
     for (int v = 0; v < V; ++v) dot[v] = 0.f;
+    // Rows of up to 32 * kCache entries (config 5: 410) are read once: every lane keeps its entries of both arrays
+    // in registers between the two passes, with all of its loads in flight together.
+    constexpr int kCache = EW::kVector ? (52 / EW::kWords > 16 ? 16 : 52 / EW::kWords) : 0;
+    if constexpr (kCache > 0) {
+        if (end - beg <= 32 * kCache) {
+            uint32_t cp[kCache][EW::kWords], cg[kCache][EW::kWords];
+#pragma unroll
+            for (int c = 0; c < kCache; ++c) {
+                const int j = beg + lane + 32 * c;
+                if (j < end) {
+                    EW::load(pr + (int64_t)j * V, cp[c]);
+                    EW::load(gp + (int64_t)j * V, cg[c]);
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < kCache; ++c) {
+                if (beg + lane + 32 * c < end) {
+                    float a[V], g[V];
+                    EW::unpack(cp[c], a);
+                    EW::unpack(cg[c], g);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) dot[v] = fmaf(a[v], g[v], dot[v]);
+                }
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+                for (int v = 0; v < V; ++v) dot[v] += __shfl_xor_sync(0xffffffffu, dot[v], off);
+#pragma unroll
+            for (int c = 0; c < kCache; ++c) {
+                const int j = beg + lane + 32 * c;
+                if (j < end) {
+                    float a[V], g[V], o[V];
+                    EW::unpack(cp[c], a);
+                    EW::unpack(cg[c], g);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) o[v] = p.scale * a[v] * (g[v] - dot[v]);
+                    EW::store(gs + (int64_t)j * V, o);
+                }
+            }
+            return;
+        }
+    }
     for (int j = beg + lane; j < end; j += 32) {
         float a[V], g[V];
         if constexpr (EW::kVector) {
