@@ -59,7 +59,7 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from an ncu capture of this
 # command (profiles/ holds the summary it comes from); None until one has been taken for the workload.
 NCU_TRAFFIC_BYTES = {
-    "spmm_v8_s90": 334.8e6,    # profiles/spmm_dense_kernel__spmm_v8_s90.md
+    "spmm_v8_s90": 335.4e6,    # profiles/spmm_dense_kernel__spmm_v8_s90.md
     "sddmm_v8_s90": 380.5e6,   # profiles/sddmm_dense_kernel__sddmm_v8_s90.md
 }
 
