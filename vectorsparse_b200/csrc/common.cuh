@@ -33,7 +33,9 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 // word 0 = the plan kernel chose the dense kernel; words 4 .. 4 + checks = one verdict per duplicate-checking CTA
 // of the plan kernel, set when it met the same column twice in one vector-row (the dense tile would keep one of
 // the two values, the reference adds them: such matrices go to the gather kernel).  Block-uniform result; every
-// thread of the block must call it.
+// thread of the block must call it.  The early way out ahead of the barrier is deliberate (word 0 is the same for
+// every thread): with the barrier reached on every path the multiplying kernel came out 14 % slower at 50 %
+// sparsity, for the same instructions.
 __device__ __forceinline__ bool plan_dense_chosen(const int32_t *hdr, int checks) {
     if (*reinterpret_cast<const volatile int32_t *>(hdr) == 0) return false;
     int dup = 0;
