@@ -130,7 +130,8 @@ dense_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__rest
     auto column_of = [&](int j) { return kTransposed ? __ldg(cols + j) << shift : __ldg(cols + j); };
     auto value_of = [&](int j) { return kTransposed ? __ldg(src + j) : j; };
     extern __shared__ int plan_sh[];
-    pdl_launch_dependents();   // the multiplying kernel may set itself up while the plan is made
+    pdl_launch_dependents();   // the multiplying kernel may be scheduled while the plan is made
+    pdl_wait();                // this kernel too is launched as a dependent: the call ahead may still be reading the plan scratch
     {
         const int64_t nnz = __ldg(row_offsets + m_vec);
         const float stages = (float)(groups / (kTileM / kGroupRows)) * (float)(plan_blocks / (kBlockK / kPlanCols));

@@ -84,6 +84,7 @@ __global__ void __launch_bounds__(kThreads) spmm_t_kernel(const Params p, int64_
                                                           const int32_t *plan_hdr, int plan_checks) {
     // Enqueued behind the tensor-core kernel (plan_hdr != null): wait for its end, then leave unless it handed the
     // call over (a matrix it cannot hold, or a non-finite sum it would not vouch for).
+    pdl_launch_dependents();   // the next call's plan kernel may queue up behind this one
     pdl_wait();
     if (plan_hdr && plan_dense_chosen(plan_hdr, plan_checks)) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

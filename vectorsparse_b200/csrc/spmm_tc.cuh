@@ -132,6 +132,7 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
 
 template <typename TOut, int V>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) spmm_tc_kernel(const SpmmParams p, uint32_t *status, const int32_t *plan_hdr, int plan_checks) {
+    pdl_launch_dependents();   // the next call's plan kernel may queue up behind this one
     pdl_wait();   // launched behind the dense kernel without waiting for its end: wait here, before its verdict is read
     if (plan_hdr && plan_dense_chosen(plan_hdr, plan_checks)) return;   // the dense kernel has taken this call (decided on the device)
     extern __shared__ uint8_t smem_raw[];

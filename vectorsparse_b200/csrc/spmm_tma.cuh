@@ -148,6 +148,7 @@ template <typename TOut, int V>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 spmm_tma_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map, int rows_per_batch, int total_rows,
                 uint32_t *status, const int32_t *plan_hdr, int plan_checks) {
+    pdl_launch_dependents();   // the next call's plan kernel may queue up behind this one
     pdl_wait();   // launched behind the dense kernel without waiting for its end: wait here, before its verdict is read
     if (plan_hdr && plan_dense_chosen(plan_hdr, plan_checks)) return;   // the dense kernel has taken this call (decided on the device)
     extern __shared__ uint8_t smem_raw[];

@@ -379,9 +379,11 @@ template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStre
     int32_t *blk_offsets = reinterpret_cast<int32_t *>(plan + header_bytes);
     uint2 *blk_entries = reinterpret_cast<uint2 *>(plan + header_bytes + offsets_bytes);
     const int force_dense = mode == SpmmMode::kDense ? 1 : 0;
-    densespmm::dense_plan_kernel<false><<<groups + checks, densespmm::kPlanThreads, plan_smem, s>>>(
-        p.row_offsets, p.col_indices, nullptr, 0, p.m_vec, p.K, groups, rows_per_group, plan_blocks, blk_offsets, blk_entries,
-        capacity, force_dense, 370.0f, 4.7f, 0.0f, flag);
+    // a dependent launch as well: in a stream of calls the plan kernel queues up behind the previous call's last kernel
+    rc = (int)launch_overlapped(densespmm::dense_plan_kernel<false>, (unsigned)(groups + checks), densespmm::kPlanThreads, plan_smem, s,
+                                p.row_offsets, p.col_indices, (const int32_t *)nullptr, 0, p.m_vec, p.K, groups, rows_per_group,
+                                plan_blocks, blk_offsets, blk_entries, capacity, force_dense, 370.0f, 4.7f, 0.0f, flag);
+    if (rc != VS_OK) return rc;
     const int64_t items = (int64_t)p.batch * n_tiles * m_tiles;
     const unsigned grid = (unsigned)(items < d->sm_count ? items : d->sm_count);   // one persistent CTA per SM
     rc = (int)cudaGetLastError();
@@ -683,10 +685,9 @@ template <typename TOut, int V> int launch_spmm_t(const spmmt::Params &p, int m_
     const int64_t header_bytes = spmm_plan_header_bytes(checks);
     int32_t *blk_offsets = reinterpret_cast<int32_t *>(plan + header_bytes);
     uint2 *blk_entries = reinterpret_cast<uint2 *>(plan + header_bytes + offsets_bytes);
-    densespmm::dense_plan_kernel<true><<<groups + checks, densespmm::kPlanThreads, plan_smem, s>>>(
-        p.t_offsets, p.t_rows, p.t_src, shift, q.m_vec, q.K, groups, rows_per_group, plan_blocks, blk_offsets, blk_entries, capacity,
-        mode == SpmmTMode::kDense ? 1 : 0, 0.0f, 5.0f * V, 1.5f, flag);
-    rc = (int)cudaGetLastError();
+    rc = (int)launch_overlapped(densespmm::dense_plan_kernel<true>, (unsigned)(groups + checks), densespmm::kPlanThreads, plan_smem, s,
+                                p.t_offsets, p.t_rows, p.t_src, shift, q.m_vec, q.K, groups, rows_per_group, plan_blocks, blk_offsets,
+                                blk_entries, capacity, mode == SpmmTMode::kDense ? 1 : 0, 0.0f, 5.0f * V, 1.5f, flag);
     const int64_t items = (int64_t)q.batch * n_tiles * m_tiles;
     const unsigned grid = (unsigned)(items < d->sm_count ? items : d->sm_count);   // one persistent CTA per SM
     if (rc == VS_OK)
