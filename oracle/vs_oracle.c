@@ -15,6 +15,8 @@
  *     vso_attention_f64    : masked row softmax and SDDMM -> softmax -> SpMM.  The reference has no code
  *                            for these (README.md:76 points to an external repository), so they are
  *                            defined here and PARITY IS UNPINNED for them.
+ *   - vso_spmm_t_f64       : the product with the transposed matrix; no reference code either (PARITY UNPINNED);
+ *                            the tests tie it to vso_spmm_f64 on an explicitly transposed matrix.
  *
  * Pinning: vso_sddmm_f32 and vso_row_swizzle are checked bit-for-bit against the reference's own
  * Host_sddmm / SortedRowSwizzle compiled from the reference header, and vso_spmm_f32 against the
