@@ -40,6 +40,8 @@ WORKLOADS = {
     # name: (op, M, K, V, sparsity, N or k, instances, pattern kind)
     "spmm_v8_s90": dict(op="spmm", M=2048, K=512, V=8, s=0.9, N=256, inst=256, kind="beta"),
     "spmm_v8_s50": dict(op="spmm", M=2048, K=512, V=8, s=0.5, N=256, inst=256, kind="beta"),
+    "spmm_v8_s90_n128": dict(op="spmm", M=2048, K=512, V=8, s=0.9, N=128, inst=256, kind="beta"),
+    "spmm_v8_s90_n64": dict(op="spmm", M=2048, K=512, V=8, s=0.9, N=64, inst=256, kind="beta"),
     "spmm_v4_s90": dict(op="spmm", M=2048, K=512, V=4, s=0.9, N=256, inst=256, kind="beta"),
     "spmm_v2_s90": dict(op="spmm", M=2048, K=512, V=2, s=0.9, N=256, inst=256, kind="beta"),
     "sddmm_v8_s90": dict(op="sddmm", M=2048, K=512, V=8, s=0.9, N=256, inst=256, kind="beta"),
@@ -50,11 +52,18 @@ WORKLOADS = {
     "attention_cfg5": dict(op="attention", M=4096, K=4096, V=8, s=0.9, N=64, inst=128, kind="band", band=256),
     "attention_bwd_cfg5": dict(op="attention_bwd", M=4096, K=4096, V=8, s=0.9, N=64, inst=128, kind="band", band=256),
     "spmm_cc_v8_s90": dict(op="spmm", M=2048, K=512, V=8, s=0.9, N=256, inst=256, kind="beta", path=1),
+    "sddmm_cc_v8_s90": dict(op="sddmm", M=2048, K=512, V=8, s=0.9, N=256, inst=256, kind="beta", path=1),
     # fp32 CUDA-core SpMM (the cudaSpmm entry point), M = K = 4096, uniform random positions, values and B U(-1,1)
     "spmm_f32_v4_s90_n1024": dict(op="spmm", M=4096, K=4096, V=4, s=0.9, N=1024, inst=8, kind="uniform", path=1, dtype="f32"),
     "spmm_f32_v1_s90_n1024": dict(op="spmm", M=4096, K=4096, V=1, s=0.9, N=1024, inst=8, kind="uniform", path=1, dtype="f32"),
     "spmm_f32_v4_s80_n8192": dict(op="spmm", M=4096, K=4096, V=4, s=0.8, N=8192, inst=2, kind="uniform", path=1, dtype="f32"),
+    "spmm_f32_v1_s80_n8192": dict(op="spmm", M=4096, K=4096, V=1, s=0.8, N=8192, inst=2, kind="uniform", path=1, dtype="f32"),
 }
+
+# The partitioned configurations, measured by every `--gpus N` run next to the headline number (the `sharded` object
+# of the JSON line): fp32 CUDA-core SpMM split by columns of the dense operand, fixed-mask attention split by
+# batch x head.  One instance each (the configuration itself, not a stream of copies).
+SHARDED = ("spmm_f32_v4_s80_n8192", "spmm_f32_v1_s80_n8192", "attention_cfg5")
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from an ncu capture of this
 # command (profiles/ holds the summary it comes from); None until one has been taken for the workload.
@@ -67,21 +76,25 @@ NCU_TRAFFIC_BYTES = {
 def kernels_per_step(w, a=None):
     """Names of the library's kernels one step launches (the count is what `gpu_launches` reports)."""
     tensor = w.get("path") != 1
+    # the densified product runs on pairs of CTAs for dense widths that are multiples of 128, on single CTAs otherwise
+    pair = w["N"] % 128 == 0 and os.environ.get("VSPARSE_B200_SPMM_PAIR") != "0"
+    dense = "spmm_pair_kernel" if pair else "spmm_dense_kernel"
     if w["op"] == "attention":
-        return ["sddmm_tma_kernel", "softmax_cvse_kernel", "dense_plan_kernel", "spmm_dense_kernel",
+        return ["sddmm_tma_kernel", "softmax_cvse_kernel", "dense_plan_kernel", dense,
                 "spmm_tma_kernel (returns at once unless the plan kernel chose it)"]
     if w["op"] == "attention_bwd":
-        plan3 = ["dense_plan_kernel", "spmm_dense_kernel", "fallback kernel (returns at once unless the plan kernel chose it)"]
+        plan3 = ["dense_plan_kernel", dense,
+                 "fallback kernel (returns at once unless the plan kernel chose it)"]
         return ["sddmm_tma_kernel", "softmax_cvse_kernel"] + plan3 + ["sddmm_tma_kernel", "softmax_cvse_backward_kernel"] + plan3 + plan3
     if w["op"] == "spmm_t":
         if os.environ.get("VSPARSE_B200_SPMM_T") == "gather":
             return ["spmm_t_kernel"]
-        return ["dense_plan_kernel<transposed>", "spmm_dense_kernel<transposed>",
+        return ["dense_plan_kernel<transposed>", dense + "<transposed>",
                 "spmm_t_kernel (returns at once unless the plan kernel chose it)"]
     if w["op"] == "spmm" and tensor:
         if os.environ.get("VSPARSE_B200_SPMM") == "gather":
             return ["spmm_tma_kernel"]
-        return ["dense_plan_kernel", "spmm_dense_kernel",
+        return ["dense_plan_kernel", dense,
                 "spmm_tma_kernel (returns at once unless the plan kernel chose it)"]
     if w["op"] == "spmm":
         return ["spmm_cc_kernel"]
@@ -90,6 +103,12 @@ def kernels_per_step(w, a=None):
     from vectorsparse_b200 import _lib
     dense = a is not None and _lib.lib().vs_sddmm_formulation(a.m_vec, w["N"], w["K"], a.nnz_vec, w["V"]) == 1
     return ["sddmm_plan_kernel", "sddmm_dense_kernel"] if dense else ["sddmm_tma_kernel"]
+
+
+def config_of(name, w, a):
+    """The workload as both arms (this library, the reference's CPU path) print it: identical dictionaries."""
+    return {"workload": name, "op": w["op"], "M": w["M"], "K": w["K"], "V": w["V"], "sparsity": w["s"],
+            "dense_width_or_k": w["N"], "nnz_vec": a.nnz_vec, "instances_per_step": w["inst"]}
 
 
 def metric_name(w):
@@ -360,6 +379,22 @@ def run_ours(args):
         torch.cuda.synchronize()
         lat_us = l0.elapsed_time(l1) * 1000.0 / 50
 
+    # context: the reference's own kernels, recompiled for this part, on the same stream of instances
+    ref_kernels = None
+    if rank == 0 and world == 1 and not args.kernel_only and w["op"] in ("spmm", "sddmm") and path == VS_PATH_TENSOR:
+        ref_kernels = reference_kernels_leg(w, a, dev, d_a, d_b, flops)
+
+    # the partitioned configurations: every rank takes part (timings are reduced inside)
+    h2d = h_a.numel() * h_a.element_size() + h_b.numel() * h_b.element_size()
+    d2h = h_out.numel() * h_out.element_size()
+    sharded = None
+    if not args.kernel_only and not args.no_sharded:
+        del d_a, d_b, d_out, h_a, h_b, h_out
+        if e2e_steps:
+            del bufs
+        torch.cuda.empty_cache()
+        sharded = sharded_leg(world, rank, dev)
+
     # max over ranks
     t = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
@@ -370,8 +405,18 @@ def run_ours(args):
         peak, peak_kind = measured_peaks()
         avg_launch_s = float(np.mean(per_launch_ms)) * 1e-3
         achieved = alg_bytes / avg_launch_s / 1e9
-        h2d = h_a.numel() * h_a.element_size() + h_b.numel() * h_b.element_size()
-        d2h = h_out.numel() * h_out.element_size()
+        if f32 and w["op"] == "spmm":
+            # M = K = 4096 in fp32 is bound by fp32 FMA issue, not by memory (50 to 190 flop per byte): the denominator
+            # is the FMA throughput measured in this run by a register-only probe kernel
+            fma_peak = ops.measure_fp32_fma()
+            tfl = flops / avg_launch_s / 1e12
+            roofline = {"bound": "fp32_fma", "achieved": tfl, "peak": fma_peak, "unit": "TFLOP/s", "frac": tfl / fma_peak,
+                        "peak_source": "fp32 FMA probe kernel, measured in this run", "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                        "algorithmic_bytes_per_launch": alg_bytes, "hbm_gbs_achieved": achieved}
+        else:
+            roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                        "peak_source": f"of {peak_kind}", "frac_of_nominal_8tbs": achieved / 8000.0,
+                        "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "algorithmic_bytes_per_launch": alg_bytes}
         line = {
             "metric": metric_name(w),
             "value": flops * args.steps * world / (total_ms * 1e-3) / 1e12,
@@ -385,15 +430,11 @@ def run_ours(args):
             "vs_baseline": None,
             "dtype": "f32" if f32 else "f16 (fp32 accumulate)",
             "data": "synthetic",
-            "config": {"workload": args.workload, "op": w["op"], "M": M, "K": K, "V": V, "sparsity": w["s"],
-                       "dense_width_or_k": N, "nnz_vec": a.nnz_vec, "instances_per_step": inst,
-                       "path": "cuda-core" if path == VS_PATH_CUDA_CORE else "tensor (tcgen05)",
-                       "l2": "working set larger than L2 (distinct operands per instance), no flush needed",
-                       "parallelism": f"independent streams x{world}"},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "peak_source": f"of {peak_kind}",
-                         "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
-                         "algorithmic_bytes_per_launch": alg_bytes},
+            "config": config_of(args.workload, w, a),
+            "run": {"path": "cuda-core" if path == VS_PATH_CUDA_CORE else "tensor (tcgen05)",
+                    "l2": "working set larger than L2 (distinct operands per instance), no flush needed",
+                    "parallelism": f"independent streams x{world}"},
+            "roofline": roofline,
             "e2e": {"value": flops * e2e_steps * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
             "gpu_launches": args.steps * len(kernels_per_step(w, a)),
@@ -401,11 +442,221 @@ def run_ours(args):
             "single_launch_latency_us": lat_us,
             "clocks": clocks,
         }
+        if ref_kernels is not None:
+            line["reference_kernels_context"] = ref_kernels
+        if sharded is not None:
+            line["sharded"] = sharded
         if world == 1 and not args.no_cpu and not args.kernel_only:
             line["cpu_baseline"] = cpu_leg(w, a, budget_s=12.0)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def reference_kernels_leg(w, a, dev, d_a, d_b, flops, steps=3):
+    """CONTEXT, not a target and not part of any other number: the reference's own tensor-core kernels
+    (spmm::wmmaSpmm, src/wmma_spmm.cu:13-116; sddmm::wmmaSddmm algorithm 1, src/wmma_sddmm.cu:250-504), compiled
+    unmodified for sm_100a into baseline/_ref/, on this workload's stream: one launch per instance, as the reference
+    API works.  For SpMM every vector-row is padded to a positive multiple of 32 vectors with zero values (see
+    baseline/refk.py); the padded product equals the original one.  A small problem is checked first with the
+    reference's own criterion (abs error <= 0.5); nothing is timed if that fails."""
+    import torch
+
+    from baseline import refk
+    from vectorsparse_b200 import cvse, ops
+
+    L = refk.lib()
+    if L is None:
+        return {"unavailable": "baseline/_ref/libvsref_kernels.so is not built (no reference checkout at build time)"}
+    V, M, K, N, inst = w["V"], w["M"], w["K"], w["N"], w["inst"]
+
+    def spmm_call(p_struct, m_vec, vals, B, out):
+        ri, ro, ci = p_struct
+        return L.refk_wmma_spmm(m_vec, V, N, K, ri.data_ptr(), ro.data_ptr(), ci.data_ptr(), vals.data_ptr(), B.data_ptr(), out.data_ptr(), 0)
+
+    def sddmm_call(p_struct, m_vec, nnz_vec, lhs, rhs, out):
+        ri, ro, ci = p_struct
+        return L.refk_wmma_sddmm(m_vec, N, K, nnz_vec, ri.data_ptr(), ro.data_ptr(), ci.data_ptr(), lhs.data_ptr(), rhs.data_ptr(),
+                                 out.data_ptr(), V, 1, 0)
+
+    # ---- a small problem first, against this library's result -------------------------------------------------
+    t = cvse.generate(cvse.GEN_BETA, 3, 128 // V, K, V, 0.8)
+    if w["op"] == "spmm":
+        ro, ci, src = refk.pad_rows(t.row_offsets, t.col_indices, K)
+        tp = cvse.CVSE(t.m_vec, K, V, ro, ci, cvse.row_swizzle(ro))
+        st = tp.to_device(dev)
+        tv = torch.from_numpy(refk.pad_values(cvse.fill_random((t.nnz_vec * V,), np.float16, cvse.DIST_NORMAL, 1, 0.5), src, V)).to(dev)
+        tb = d_b[0]
+        got, want = (torch.zeros((t.m, N), dtype=torch.float16, device=dev) for _ in range(2))
+        rc = spmm_call(st, tp.m_vec, tv, tb, got)
+        ops.spmm.wmmaSpmm(tp.m_vec, V, N, K, *st, tv, tb, want)
+    else:
+        st = t.to_device(dev)
+        lhs = d_a[0][:t.m].contiguous()
+        got, want = (torch.zeros(t.nnz_vec * V, dtype=torch.float16, device=dev) for _ in range(2))
+        rc = sddmm_call(st, t.m_vec, t.nnz_vec, lhs, d_b[0], got)
+        ops.sddmm.wmmaSddmm(t.m_vec, N, K, t.nnz_vec, *st, lhs, d_b[0], want, V)
+    torch.cuda.synchronize()
+    worst = float((got.float() - want.float()).abs().max())
+    if rc != 0 or not (worst <= 0.5):
+        return {"unavailable": f"small check failed (rc {rc}, max abs difference {worst}): not timed"}
+
+    # ---- the stream of the step: one launch per instance --------------------------------------------------------
+    if w["op"] == "spmm":
+        ro, ci, src = refk.pad_rows(a.row_offsets, a.col_indices, K)
+        ap = cvse.CVSE(a.m_vec, K, V, ro, ci, cvse.row_swizzle(ro))
+        st = ap.to_device(dev)
+        keep = torch.from_numpy(np.nonzero(src >= 0)[0]).to(dev)
+        srck = torch.from_numpy(src[src >= 0]).to(dev)
+        vals = torch.zeros((inst, len(src), V), dtype=torch.float16, device=dev)
+        vals[:, keep] = d_a[:, :a.nnz_vec * V].reshape(inst, a.nnz_vec, V)[:, srck]
+        out = torch.empty((inst, M, N), dtype=torch.float16, device=dev)
+
+        def step():
+            for b in range(inst):
+                spmm_call(st, ap.m_vec, vals[b], d_b[b], out[b])
+        note = f"rows padded to multiples of 32 vectors with zero values ({a.nnz_vec} -> {len(src)} vectors)"
+    else:
+        st = a.to_device(dev)
+        out = torch.empty((inst, a.nnz_vec * V), dtype=torch.float16, device=dev)
+
+        def step():
+            for b in range(inst):
+                sddmm_call(st, a.m_vec, a.nnz_vec, d_a[b], d_b[b], out[b])
+        note = "the workload's own mask"
+    step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    return {"kernel": "spmm::wmmaSpmm (src/wmma_spmm.cu:13-116)" if w["op"] == "spmm" else
+            "sddmm::wmmaSddmm, algorithm 1 (src/wmma_sddmm.cu:250-504)",
+            "built": "the reference's sources, unmodified, nvcc -gencode arch=compute_100a,code=sm_100a (it ships -arch=sm_70)",
+            "ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12, "launches_per_step": inst, "input": note,
+            "small_check_max_abs_difference": worst, "role": "context only"}
+
+
+def sharded_leg(world, rank, dev, steps=10, warmup=3):
+    """The two partitions of the operators over the GPUs of one box, each rank computing its shard with no collective
+    on the data path: fp32 CUDA-core SpMM (M = K = 4096, N = 8192) split by COLUMNS of the dense operand, and
+    fixed-mask attention (128 batch x head problems) split by batch x head.  Per configuration: ms per pass of the
+    sharded run (max over ranks), TFLOP/s over all ranks, the same pass on ONE GPU in the same run (rank 0 computing
+    the whole problem) and the strong-scaling efficiency t(1) / (N t(N)); the optional all-gather of the result is
+    timed on its own and is not part of either time.  Rank 0 returns the dictionary, the others None."""
+    import torch
+    import torch.distributed as dist
+
+    from vectorsparse_b200 import VS_PATH_TENSOR, cvse, ops, shard
+
+    def timed(fn):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    def max_over_ranks(ms):
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    def once(fn):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+
+    out = {}
+    for name in SHARDED:
+        w = WORKLOADS[name]
+        a = build_problem(w)
+        V, M, K, N = w["V"], w["M"], w["K"], w["N"]
+        ri, ro, ci = a.to_device(dev)
+        entry = {"n_gpus": world}
+        gather_ms, t_one = None, None
+        if w["op"] == "spmm":      # columns of the dense operand; every rank holds the whole sparse matrix
+            flops = 2.0 * a.nnz_vec * V * N
+            vals = torch.from_numpy(cvse.fill_random((a.nnz_vec * V,), np.float32, cvse.DIST_UNIFORM, 7)).to(dev)
+            B = cvse.fill_random((K, N), np.float32, cvse.DIST_UNIFORM, 8, 1.0)
+            c0, wd = shard.column_shards(N, world, 64)[rank]
+            B_local = torch.from_numpy(np.ascontiguousarray(B[:, c0:c0 + wd])).to(dev)
+            C_local = torch.empty((M, wd), dtype=torch.float32, device=dev)
+            t_shard = max_over_ranks(timed(lambda: shard.spmm_column_sharded(ops.spmm.cudaSpmm, a.m_vec, V, N, K, (ri, ro, ci), vals,
+                                                                            B_local, C_local)))
+            entry["partition"] = f"columns of the dense operand: {N} -> {wd} per GPU"
+            if world > 1:
+                shard.gather_columns(C_local, N, 64)   # first collective of the run: communicator set-up is not timed
+                gather_ms = max_over_ranks(once(lambda: shard.gather_columns(C_local, N, 64)))
+            if rank == 0 and world > 1:
+                B_full = torch.from_numpy(B).to(dev)
+                C_full = torch.empty((M, N), dtype=torch.float32, device=dev)
+                t_one = _timed_local(lambda: ops.spmm.cudaSpmm(a.m_vec, V, N, K, ri, ro, ci, vals, B_full, C_full), steps, warmup)
+                del B_full, C_full
+            del B_local, C_local, vals
+        else:                      # batch x head: every rank holds the mask and its own heads
+            heads, n, d = w["inst"], K, N
+            flops = 2 * 2.0 * a.nnz_vec * V * d * heads
+            h0, cnt = shard.batch_shards(heads, world)[rank]
+            q, k, v = (torch.from_numpy(cvse.fill_random((cnt, n, d), np.float16, cvse.DIST_NORMAL, 11 + 3 * h0 + i, 1.0)).to(dev)
+                       for i in range(3))
+            o = torch.empty((cnt, n, d), dtype=torch.float16, device=dev)
+            ws = torch.empty((cnt, a.nnz_vec * V), dtype=torch.float16, device=dev)
+            t_shard = max_over_ranks(timed(lambda: ops.attention_cvse(VS_PATH_TENSOR, a.m_vec, V, n, d, a.nnz_vec, ri, ro, ci, q, k, v,
+                                                                      o, ws, 0.125)))
+            entry["partition"] = f"batch x head: {heads} -> {cnt} per GPU"
+            if world > 1:
+                shard.gather_batch(o, heads)
+                gather_ms = max_over_ranks(once(lambda: shard.gather_batch(o, heads)))
+            del q, k, v, o, ws
+            if rank == 0 and world > 1:
+                q, k, v = (torch.from_numpy(cvse.fill_random((heads, n, d), np.float16, cvse.DIST_NORMAL, 11 + i, 1.0)).to(dev)
+                           for i in range(3))
+                o = torch.empty((heads, n, d), dtype=torch.float16, device=dev)
+                ws = torch.empty((heads, a.nnz_vec * V), dtype=torch.float16, device=dev)
+                t_one = _timed_local(lambda: ops.attention_cvse(VS_PATH_TENSOR, a.m_vec, V, n, d, a.nnz_vec, ri, ro, ci, q, k, v, o,
+                                                                ws, 0.125), steps, warmup)
+                del q, k, v, o, ws
+        torch.cuda.empty_cache()
+        if world > 1:
+            dist.barrier()   # the other ranks wait while rank 0 times the whole problem on one GPU
+        if rank == 0:
+            if world == 1:
+                t_one = t_shard
+            entry.update({"ms": t_shard, "tflops": flops / (t_shard * 1e-3) / 1e12, "ms_on_one_gpu": t_one,
+                          "strong_scaling_efficiency": t_one / (world * t_shard), "all_gather_ms": gather_ms})
+            out[name] = entry
+    return out if rank == 0 else None
+
+
+def _timed_local(fn, steps, warmup):
+    """CUDA-event time per call on this rank alone (no barrier: the other ranks are idle)."""
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
 
 
 def cpu_leg(w, a, budget_s, threads=None):
@@ -499,11 +750,10 @@ def run_reference(args):
         "value": v, "unit": "TFLOP/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": steps,
         "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
-        "config": {"workload": args.workload, "op": w["op"], "M": w["M"], "K": w["K"], "V": w["V"],
-                   "sparsity": w["s"], "dense_width_or_k": w["N"], "nnz_vec": a.nnz_vec,
-                   "instances_per_step": w["inst"], "path": "host loop (spmm_benchmark.cpp:66-86)" if w["op"] == "spmm" else
-                   "host loop (include/bm_test_utils.h:171-193)" if w["op"] == "sddmm" else
-                   "host loops of the oracle (the reference has no such operator)"},
+        "config": config_of(args.workload, w, a),
+        "run": {"path": "host loop (spmm_benchmark.cpp:66-86)" if w["op"] == "spmm" else
+                "host loop (include/bm_test_utils.h:171-193)" if w["op"] == "sddmm" else
+                "host loops of the oracle (the reference has no such operator)"},
         "cpu_baseline": base,
         "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -558,6 +808,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "dense-library"])
     ap.add_argument("--workload", default="spmm_v8_s90", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-sharded", action="store_true", help="skip the partitioned configurations (`sharded` in the JSON line)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-resident leg only (for profiler captures): no end-to-end, latency or CPU legs")
     args = ap.parse_args()

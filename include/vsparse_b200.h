@@ -2,8 +2,11 @@
  * vsparse_b200 — C ABI of the column-vector-sparse (CVSE) SpMM / SDDMM library for NVIDIA B200 (sm_100a).
  *
  * Every entry point takes plain pointers and sizes.  Unless a function says "host", pointers are DEVICE
- * pointers owned by the caller; the library allocates nothing, keeps no workspace between calls, enqueues
- * its kernels on `stream` (a cudaStream_t passed as void*) and returns without synchronising.
+ * pointers owned by the caller; the library enqueues its kernels on `stream` (a cudaStream_t passed as void*)
+ * and returns without synchronising.  One piece of device memory is the library's own: the tensor-path
+ * operators keep a plan scratch per calling stream (cudaMallocAsync at the first call on a stream, and again
+ * when a larger matrix needs more — make those calls outside stream capture; vs_release_scratch frees it).
+ * A caller that hands over a buffer with vs_set_workspace gets a library that never allocates.
  *
  * Return value of every function: 0 on success, a negative VS_ERR_* code when the arguments are rejected
  * before anything is launched, or a positive cudaError_t if the CUDA runtime reported one.
@@ -263,6 +266,18 @@ int64_t vs_sddmm_workspace_bytes(int m_vec, int n, int nonzeros_vec);
 int64_t vs_spmm_t_workspace_bytes(int m_vec, int vec_length, int n, int batch, int64_t stride_values);
 int vs_set_workspace(void *workspace, int64_t bytes);
 
+/* Frees the plan scratch the library keeps on the current device for `stream` (stream-ordered: behind the work
+ * already enqueued there), or for every stream when every_stream != 0.  The next tensor-path call on such a
+ * stream allocates again.  With the per-thread default stream handle (cudaStreamPerThread) the buffer of the
+ * calling thread is meant: each host thread has its own.  No counterpart in the reference. */
+int vs_release_scratch(void *stream, int every_stream);
+
+/* Measures the fp32 fused-multiply-add throughput of the current device (TFLOP/s, 2 flops per FMA) with a
+ * register-only kernel: the roofline denominator for the fp32 CUDA-core SpMM, which is bound by FMA issue and not by
+ * memory.  Synchronous (times three short launches on the legacy default stream and returns the best); diagnostic,
+ * no counterpart in the reference. */
+int vs_measure_fp32_fma(double *tflops);
+
 /* Which tensor-path SDDMM formulation vs_sddmm / vs_sddmm_batched would run for this problem: 1 = dense tiles
  * sampled at the mask, 0 = row gather (environment override included).  Diagnostic, no counterpart in the
  * reference; lets a benchmark name the kernels it measures.  Needs no device. */
@@ -271,13 +286,23 @@ int vs_sddmm_formulation(int m_vec, int k, int n, int nonzeros_vec, int vec_leng
 /* ------------------------------------------------------------------------------------------------------
  * Tensor-core encoding self-test (diagnostic; no counterpart in the reference).  Copies `image_bytes` of a
  * caller-built shared-memory image (device pointer) to the start of a 1024-byte aligned buffer, issues n_mma
- * tcgen05.mma kind::f16 instructions with the given 64-bit (A, B) descriptor pairs — their start-address field
- * relative to the image — accumulating into one tile, and copies the accumulator, pre-filled with `fill`, to
- * out[lane * ncols + col] (128 lanes, ncols a multiple of 8, at most 128).  Lets the host confirm an operand
- * layout convention against a plain matrix product before trusting a kernel built on it.
+ * (1..64) tcgen05.mma kind::f16 instructions with the given 64-bit (A, B) descriptor pairs — a HOST array of
+ * 2 * n_mma descriptors, their start-address field relative to the image — accumulating into one tile, and
+ * copies the accumulator, pre-filled with `fill`, to out[lane * ncols + col] (128 lanes, ncols a multiple of 8,
+ * at most 128).  Lets the host confirm an operand layout convention against a plain matrix product before
+ * trusting a kernel built on it.  Nothing is launched unless every operand lies inside the image: idesc must be
+ * fp16 x fp16 -> fp32 with M = 128 and N <= ncols, descriptors unswizzled or with the 128-byte swizzle, and
+ * start + extent (from the leading / stride byte offsets) <= image_bytes, else VS_ERR_SHAPE.
  * ---------------------------------------------------------------------------------------------------- */
 int vs_selftest_mma(const void *image, int image_bytes, const uint64_t *descs, int n_mma, uint32_t idesc,
                     int ncols, float fill, float *out, void *stream);
+
+/* The same for a PAIR of CTAs (tcgen05 cta_group::2, M = 256): each CTA of the pair loads its own image (128
+ * rows of A and N / 2 columns of B at the offsets the shared descriptors name), the first CTA issues the MMAs for
+ * both, and CTA r copies its accumulator lanes to out[(r * 128 + lane) * ncols + col]; ncols <= 256, N % 32 == 0.
+ * Same host-side checks. */
+int vs_selftest_mma_pair(const void *image0, const void *image1, int image_bytes, const uint64_t *descs, int n_mma,
+                         uint32_t idesc, int ncols, float fill, float *out, void *stream);
 
 /* Row-gather self-test (diagnostic; no counterpart in the reference): `groups` (1..32) hardware row gathers of
  * four rows each — indices from row_indices[4*groups] (device), rows >= `rows` read as zeros — 64 fp16 columns

@@ -25,11 +25,13 @@ _F64P = C.POINTER(C.c_double)
 _U16P = C.POINTER(C.c_uint16)
 
 
-def build(ref: bool = False) -> None:
-    """Compile the oracle (and, with ref=True and a reference checkout present, the reference shim)."""
+def build(ref: bool = False, reference: str | None = None) -> None:
+    """Compile the oracle (and, with ref=True and a reference checkout present, the reference shim).  `reference`:
+    where that checkout lies (default: the Makefile's, a directory named `reference` next to this repository)."""
     subprocess.run(["make", "-C", _HERE, "all"], check=True, capture_output=True)
     if ref:
-        subprocess.run(["make", "-C", _HERE, "ref"], check=True, capture_output=True)
+        cmd = ["make", "-C", _HERE, "ref"] + ([f"REFERENCE={reference}"] if reference else [])
+        subprocess.run(cmd, check=True, capture_output=True)
 
 
 def lib() -> C.CDLL:

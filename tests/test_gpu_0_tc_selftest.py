@@ -24,9 +24,9 @@ def idesc(M, N, a_mn, b_mn):
 
 def run(image, descs, idesc_, ncols):
     img = torch.from_numpy(image.view(np.uint8)).to("cuda:0")
-    d = torch.tensor(np.array(descs, dtype=np.uint64).view(np.int64), device="cuda:0")
+    d = np.array(descs, dtype=np.uint64)   # host array: the library checks every descriptor against the image
     out = torch.zeros(128 * ncols, dtype=torch.float32, device="cuda:0")
-    rc = _lib.lib().vs_selftest_mma(img.data_ptr(), img.numel(), d.data_ptr(), len(descs) // 2, idesc_, ncols,
+    rc = _lib.lib().vs_selftest_mma(img.data_ptr(), img.numel(), d.ctypes.data, len(descs) // 2, idesc_, ncols,
                                     -77.0, out.data_ptr(), None)
     assert rc == 0
     torch.cuda.synchronize()
@@ -126,3 +126,62 @@ def test_mn_major_both_swizzled_wide():
     got = run(image, descs, idesc(128, NN, 1, 1), NN)
     want = A.astype(np.float32) @ B.astype(np.float32)
     assert np.array_equal(got, want)
+
+
+def test_pair_of_ctas_m256_n256():
+    """Two CTAs, one MMA stream (cta_group::2, M = 256, N = 256): CTA r holds rows 128 r .. of A and of the
+    accumulator and columns 128 r .. of B; operands in the densified-SpMM layouts (both MN-major, 128-byte swizzle),
+    four K = 16 steps.  Also pins that the issuing CTA can tell the other CTA's barrier with a commit of its own."""
+    rng = np.random.default_rng(4)
+    KK, NN = 64, 256
+    A = rng.integers(-4, 5, (256, KK)).astype(np.float16)
+    B = rng.integers(-4, 5, (KK, NN)).astype(np.float16)
+    b_base = 16384
+    images = []
+    for r in range(2):
+        image = np.zeros((b_base + 2 * 8192) // 2, np.float16)
+        Ar, Br = A[128 * r:128 * r + 128], B[:, 128 * r:128 * r + 128]
+        for m in range(128):
+            for kk in range(KK):
+                off = (m // 64) * 8192 + (kk // 8) * 1024 + (kk % 8) * 128 + ((((m % 64) // 8) ^ (kk % 8)) * 16) + (m % 8) * 2
+                put(image, off, Ar[m, kk])
+        for kk in range(KK):
+            for n in range(128):
+                off = b_base + (n // 64) * 8192 + (kk // 8) * 1024 + (kk % 8) * 128 + ((((n % 64) // 8) ^ (kk % 8)) * 16) + (n % 8) * 2
+                put(image, off, Br[kk, n])
+        images.append(torch.from_numpy(image.view(np.uint8)).to("cuda:0"))
+    descs = []
+    for mm in range(KK // 16):
+        descs += [desc(mm * 2048, 8192, 1024, 2), desc(b_base + mm * 2048, 8192, 1024, 2)]
+    d = np.array(descs, dtype=np.uint64)
+    out = torch.zeros(256 * NN, dtype=torch.float32, device="cuda:0")
+    rc = _lib.lib().vs_selftest_mma_pair(images[0].data_ptr(), images[1].data_ptr(), images[0].numel(), d.ctypes.data,
+                                         len(descs) // 2, idesc(256, NN, 1, 1), NN, -77.0, out.data_ptr(), None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    got = out.cpu().numpy().reshape(256, NN)
+    want = A.astype(np.float32) @ B.astype(np.float32)
+    assert np.array_equal(got, want)
+
+
+def test_descriptors_outside_the_image_are_refused():
+    """An operand that would reach past the image is rejected on the host: nothing is launched."""
+    image = torch.zeros(16384 + 2048, dtype=torch.uint8, device="cuda:0")
+    out = torch.zeros(128 * 16, dtype=torch.float32, device="cuda:0")
+    L = _lib.lib()
+
+    def rc(descs, idesc_, ncols=16):
+        d = np.array(descs, dtype=np.uint64)
+        return L.vs_selftest_mma(image.data_ptr(), image.numel(), d.ctypes.data, len(descs) // 2, idesc_, ncols, 0.0,
+                                 out.data_ptr(), None)
+
+    good = [desc(0, 16, 1024, 2), desc(16384, 16, 1024, 2)]
+    assert rc(good, idesc(128, 16, 0, 0)) == 0
+    assert rc([desc(4096, 16, 1024, 2), good[1]], idesc(128, 16, 0, 0)) == -3    # A: 16 blocks of 1 KiB from 4096 > image
+    assert rc([good[0], desc(16384, 16, 8192, 2)], idesc(128, 16, 0, 0)) == -3   # B: second block 8 KiB on
+    assert rc(good, idesc(128, 32, 0, 0), 16) == -3                              # N wider than the accumulator columns read
+    assert rc(good, idesc(64, 16, 0, 0)) == -3                                   # M the sandbox does not run
+    assert rc([desc(0, 16, 1024, 4), good[1]], idesc(128, 16, 0, 0)) == -3       # a swizzle mode no kernel uses
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0

@@ -71,3 +71,25 @@ def test_attention_backward_small(path):
         assert_close(gv[h].float().cpu().numpy(), wv, f"dV head {h}")
         assert_close(gq[h].float().cpu().numpy(), wq, f"dQ head {h}")
         assert_close(gk[h].float().cpu().numpy(), wk, f"dK head {h}")
+
+
+def test_attention_backward_config5_full_size():
+    """The configured size of the fixed-mask attention workload (sequence 4096, head dimension 64, V = 8, band 256 +
+    strided vectors, 410 entries per row, scale 1/8), two heads: dQ, dK, dV against the fp64 oracle."""
+    V, d, n, heads = 8, 64, 4096, 2
+    a = problem(cvse.GEN_BAND, 2026, n // V, n, V, 0.9, band=256)
+    q, k, v, go = (cvse.fill_random((heads, n, d), np.float16, cvse.DIST_NORMAL, 40 + i, 1.0) for i in range(4))
+    ri, ro, ci = structure(a)
+    t_off, t_rows, t_src = (dev(x) for x in cvse.transpose(a))
+    gq, gk, gv = (torch.full((heads, n, d), float("nan"), dtype=torch.float16, device=DEV) for _ in range(3))
+    ws_p, ws_g = (torch.empty((heads, a.nnz_vec * V), dtype=torch.float16, device=DEV) for _ in range(2))
+    ops.attention_cvse_backward(VS_PATH_TENSOR, a.m_vec, V, n, d, a.nnz_vec, ri, ro, ci, t_off, t_rows, t_src, dev(q), dev(k),
+                                dev(v), dev(go), gq, gk, gv, ws_p, ws_g, 0.125)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    for h in range(heads):
+        wq, wk, wv = oracle.attention_backward(a.m_vec, V, d, a.row_offsets, a.col_indices, q[h].astype(np.float32),
+                                               k[h].astype(np.float32), v[h].astype(np.float32), go[h].astype(np.float32), 0.125)
+        assert_close(gv[h].float().cpu().numpy(), wv, f"config 5 dV head {h}")
+        assert_close(gq[h].float().cpu().numpy(), wq, f"config 5 dQ head {h}")
+        assert_close(gk[h].float().cpu().numpy(), wk, f"config 5 dK head {h}")

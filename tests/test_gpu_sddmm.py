@@ -104,7 +104,7 @@ def test_edge_rows(path):
 def test_config3_shapes(MK, V):
     """Same masks as the SpMM sweep; lhs M x 256, rhs K x 256, N(0,1) fp16."""
     M, K = MK
-    for s in (0.5, 0.9, 0.98):
+    for s in (0.5, 0.7, 0.8, 0.9, 0.95, 0.98):
         a = problem(cvse.GEN_BETA, 1000 + M + int(s * 100), M // V, K, V, s)
         lhs, rhs = operands(a, 256, 21, 1.0)
         want = sddmm_oracle(a, 256, lhs, rhs)
@@ -200,3 +200,42 @@ def test_software_gather_kernel_for_strides_tma_cannot_address():
     assert ops.device_status() == 0
     for b in range(batch):
         assert_close(out[b].cpu().numpy(), sddmm_oracle(a, k, lhs[b], rhs[b]), f"software gather, entry {b}")
+
+
+@pytest.mark.parametrize("path", [VS_PATH_TENSOR])
+def test_attention_config5_full_size(path):
+    """The configured size of the fixed-mask attention workload: sequence 4096, head dimension 64, V = 8, a band of
+    256 plus strided vectors at 90 % sparsity (410 entries per row), scale 1/8 — two heads sharing the mask, forward,
+    against the fp64 oracle of the whole pipeline."""
+    V, d, n, heads = 8, 64, 4096, 2
+    a = problem(cvse.GEN_BAND, 2026, n // V, n, V, 0.9, band=256)
+    assert abs(a.nnz_vec / a.m_vec - 410) <= 1
+    q, k, v = (cvse.fill_random((heads, n, d), np.float16, cvse.DIST_NORMAL, 31 + i, 1.0) for i in range(3))
+    ri, ro, ci = structure(a)
+    out = torch.full((heads, n, d), float("nan"), dtype=torch.float16, device=DEV)
+    ws = torch.empty((heads, a.nnz_vec * V), dtype=torch.float16, device=DEV)
+    ops.attention_cvse(path, a.m_vec, V, n, d, a.nnz_vec, ri, ro, ci, dev(q), dev(k), dev(v), out, ws, 0.125)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    for h in range(heads):
+        want = oracle.attention(a.m_vec, V, d, d, a.row_offsets, a.col_indices, q[h].astype(np.float32),
+                                k[h].astype(np.float32), v[h].astype(np.float32), 0.125)
+        assert_close(out[h].float().cpu().numpy(), want, f"config 5, head {h}")
+
+
+def test_attention_with_an_empty_mask_writes_zeros():
+    """No mask entries and no workspace: the output rows are zero (nothing to average), nothing else is touched."""
+    V, d, n, heads = 8, 64, 128, 2
+    a = custom([0] * (n // V), n, V)
+    ri, ro, ci = structure(a)
+    q = torch.ones((heads, n, d), dtype=torch.float16, device=DEV)
+    out = torch.full((heads * n * d + 64,), float("nan"), dtype=torch.float16, device=DEV)
+    from vectorsparse_b200 import _lib
+    import ctypes as C
+    rc = _lib.lib().vs_attention_cvse(VS_PATH_TENSOR, a.m_vec, V, n, d, 0, ri.data_ptr(), ro.data_ptr(), ci.data_ptr(), q.data_ptr(),
+                                      q.data_ptr(), q.data_ptr(), out.data_ptr(), None, C.c_float(0.125), heads,
+                                      torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    host = out.float().cpu().numpy()
+    assert np.all(host[:heads * n * d] == 0.0) and np.all(np.isnan(host[heads * n * d:]))

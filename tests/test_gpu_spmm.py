@@ -115,7 +115,7 @@ def test_inf_in_unreferenced_row_does_not_leak():
 def test_config2_shapes(MK, V):
     """ResNet-50-like layer shapes, Beta(2,2)-skewed rows, values N(0, 0.02), B N(0,1), N = 256."""
     M, K = MK
-    for s in (0.5, 0.9, 0.98):
+    for s in (0.5, 0.7, 0.8, 0.9, 0.95, 0.98):
         a = problem(cvse.GEN_BETA, 1000 + M + int(s * 100), M // V, K, V, s)
         vals, B = spmm_inputs(a, 256, np.float16, 11, sigma=0.02)
         want = spmm_oracle(a, 256, vals, B)
@@ -131,6 +131,25 @@ def test_config4_full_size_fp32(V):
     vals, B = spmm_inputs(a, 256, np.float32, 13)
     got = run_spmm(VS_PATH_CUDA_CORE, a, 256, vals, B, torch.float32)
     assert_close(got, spmm_oracle(a, 256, vals, B), f"cfg4 V={V}")
+
+
+@pytest.mark.parametrize("V", [1, 4])
+@pytest.mark.parametrize("N", [1024, 8192])
+@pytest.mark.parametrize("s", [0.8, 0.95])
+def test_config4_wide_dense_operands(V, N, s):
+    """M = K = 4096, fp32, N = 1024 and 8192 (B and C of 134 MB each at 8192: element offsets beyond 2^24 in every
+    direction), sparsity 0.8 and 0.95, every output compared with the fp64 oracle.  At N = 8192 a size-independent
+    property is checked as well: the product is linear in B, so C restricted to a column block must equal the
+    product with that block of B alone, bit for bit (first, middle and last 256 columns)."""
+    a = problem(cvse.GEN_UNIFORM, 400 + V + int(s * 100), 4096 // V, 4096, V, s)
+    vals = cvse.fill_random((a.nnz_vec * V,), np.float32, cvse.DIST_UNIFORM, 13)
+    B = cvse.fill_random((4096, N), np.float32, cvse.DIST_UNIFORM, 14, 1.0)
+    got = run_spmm(VS_PATH_CUDA_CORE, a, N, vals, B, torch.float32)
+    assert_close(got, spmm_oracle(a, N, vals, B, threads=16), f"cfg4 V={V} N={N} s={s}")
+    if N == 8192:
+        for c0 in (0, N // 2 - 128, N - 256):
+            part = run_spmm(VS_PATH_CUDA_CORE, a, 256, vals, np.ascontiguousarray(B[:, c0:c0 + 256]), torch.float32)
+            assert np.array_equal(part, got[:, c0:c0 + 256]), f"column block at {c0}"
 
 
 @pytest.mark.parametrize("path,dt", [(VS_PATH_TENSOR, np.float16), (VS_PATH_CUDA_CORE, np.float16), (VS_PATH_CUDA_CORE, np.float32)])

@@ -11,13 +11,15 @@ import numpy as np
 import pytest
 import torch
 
+import oracle
+from conftest import assert_close
 from vectorsparse_b200 import VS_PATH_CUDA_CORE, VS_PATH_TENSOR, _lib, cvse, ops
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def attention_pair(path, seed, heads, n, band, sparsity):
+def attention_pair(path, seed, heads, n, band, sparsity, check_oracle=False):
     """Runs both entry points on one seeded problem; returns (with caller workspace, with built-in scratch)."""
     V, d = 8, 64
     a = cvse.generate(cvse.GEN_BAND, seed, n // V, n, V, sparsity, band=band)
@@ -35,6 +37,11 @@ def attention_pair(path, seed, heads, n, band, sparsity):
     assert L.vs_attention_cvse_static(*args, got.data_ptr(), C.c_float(0.125), heads, stream) == 0
     torch.cuda.synchronize()
     assert ops.device_status() == 0
+    if check_oracle:   # the entry point against the fp64 oracle itself, not only against its sibling
+        for h in range(heads):
+            ref = oracle.attention(a.m_vec, V, d, d, a.row_offsets, a.col_indices, q[h].float().cpu().numpy(),
+                                   k[h].float().cpu().numpy(), v[h].float().cpu().numpy(), 0.125)
+            assert_close(got[h].float().cpu().numpy(), ref, f"static scratch, head {h}")
     return want, got
 
 
@@ -44,11 +51,11 @@ def test_two_calls_in_a_row_match_the_workspace_form(path, monkeypatch):
     # the workspace form is pinned to the same ones here, so that the comparison can be bit for bit.
     monkeypatch.setenv("VSPARSE_B200_SPMM", "gather")
     monkeypatch.setenv("VSPARSE_B200_SDDMM", "gather")
-    want, got = attention_pair(path, seed=31, heads=3, n=512, band=64, sparsity=0.8)
+    want, got = attention_pair(path, seed=31, heads=3, n=512, band=64, sparsity=0.8, check_oracle=True)
     assert not torch.isnan(got).any()
     assert torch.equal(got, want)          # same kernels in the same order: the results are bit-identical
     # second call: a smaller, different problem over the scratch the first call left behind
-    want2, got2 = attention_pair(path, seed=77, heads=2, n=256, band=32, sparsity=0.7)
+    want2, got2 = attention_pair(path, seed=77, heads=2, n=256, band=32, sparsity=0.7, check_oracle=True)
     assert not torch.isnan(got2).any()
     assert torch.equal(got2, want2)
 
@@ -70,3 +77,31 @@ def test_requests_beyond_the_built_in_scratch_are_refused():
     rc = L.vs_attention_cvse_static(VS_PATH_TENSOR, 512, 8, 4096, 64, 100000, p, p, p, p, p, p, p, C.c_float(1.0), 64, None)
     assert rc == -3
     torch.cuda.synchronize()
+
+
+def test_a_request_of_exactly_the_built_in_size_runs_and_one_vector_more_is_refused(monkeypatch):
+    """4 heads x 131072 vectors x 8 values x 2 bytes = 8 388 608 bytes: the whole array, accepted and correct; one
+    vector more per head is refused on the host."""
+    monkeypatch.setenv("VSPARSE_B200_SPMM", "gather")
+    monkeypatch.setenv("VSPARSE_B200_SDDMM", "gather")
+    V, n, heads = 8, 2048, 4
+    a = cvse.generate(cvse.GEN_BAND, 9, n // V, n, V, 0.75, band=128)
+    assert heads * a.nnz_vec * V * 2 == 8 * 1024 * 1024, "the generator no longer gives 512 vectors per row"
+    want, got = attention_pair(VS_PATH_TENSOR, seed=9, heads=heads, n=n, band=128, sparsity=0.75, check_oracle=True)
+    assert torch.equal(got, want)
+    z = torch.zeros(64, dtype=torch.int32, device=DEV)
+    p = z.data_ptr()
+    rc = _lib.lib().vs_attention_cvse_static(VS_PATH_TENSOR, n // V, V, n, 64, a.nnz_vec + 1, p, p, p, p, p, p, p, C.c_float(1.0),
+                                             heads, None)
+    assert rc == -3
+
+
+def test_a_batch_whose_entries_would_be_misaligned_is_refused():
+    """Probabilities of consecutive heads lie nonzeros_vec * V * 2 bytes apart in the scratch; when that is not a
+    multiple of 16 bytes and there is more than one head, the call is refused (VS_ERR_ALIGN) before any launch."""
+    z = torch.zeros(64, dtype=torch.int32, device=DEV)
+    p = z.data_ptr()
+    rc = _lib.lib().vs_attention_cvse_static(VS_PATH_TENSOR, 4, 2, 8, 64, 3, p, p, p, p, p, p, p, C.c_float(1.0), 2, None)
+    assert rc == -5
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0

@@ -48,12 +48,15 @@ SIGNATURES = {
     "vs_spmm_host": (_i, [_i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "vs_sddmm_host": (_i, [_i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
     "vs_device_status": (_i, [_i, C.POINTER(C.c_uint32)]),
+    "vs_measure_fp32_fma": (_i, [C.POINTER(C.c_double)]),
     "vs_sddmm_formulation": (_i, [_i, _i, _i, _i, _i]),
     "vs_spmm_workspace_bytes": (_i64, [_i, _i, _i, _i, _i64]),
     "vs_sddmm_workspace_bytes": (_i64, [_i, _i, _i]),
     "vs_spmm_t_workspace_bytes": (_i64, [_i, _i, _i, _i, _i64]),
     "vs_set_workspace": (_i, [_vp, _i64]),
+    "vs_release_scratch": (_i, [_vp, _i]),
     "vs_selftest_mma": (_i, [_vp, _i, _vp, _i, C.c_uint32, _i, _f, _vp, _vp]),
+    "vs_selftest_mma_pair": (_i, [_vp, _vp, _i, _vp, _i, C.c_uint32, _i, _f, _vp, _vp]),
     "vs_selftest_gather4": (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _vp]),
     "vs_cvse_validate": (_i, [_i, _i, _i, _vp, _vp]),
     "vs_row_swizzle": (_i, [_i, _i, _vp, _vp]),

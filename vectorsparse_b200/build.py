@@ -53,10 +53,11 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
 
 
 def build_drivers(force: bool = False):
-    """spmm_benchmark / sddmm_benchmark: same positional command line as the reference drivers."""
+    """spmm_benchmark / sddmm_benchmark: same positional command line as the reference drivers; compat_check: every
+    overload of include/vsparse_compat.h against a host product."""
     out = []
     d = os.path.join(HERE, "drivers")
-    for name in ("spmm_benchmark", "sddmm_benchmark"):
+    for name in ("spmm_benchmark", "sddmm_benchmark", "compat_check"):
         src = os.path.join(d, name + ".cpp")
         exe = os.path.join(d, name)
         deps = [src, os.path.join(d, "driver_common.h"), os.path.join(ROOT, "include", "vsparse_compat.h"), LIB]

@@ -471,4 +471,22 @@ __global__ void __launch_bounds__(kCcThreads) softmax_cvse_backward_kernel(const
     }
 }
 
+// fp32 FMA throughput probe: every thread runs 8 independent chains of `iters` fused multiply-adds on registers;
+// the result is stored so that nothing is optimised away.  2 * 8 * iters flops per thread, no memory traffic.
+// The denominator for kernels that are bound by fp32 FMA issue (the fp32 CUDA-core SpMM).
+__global__ void __launch_bounds__(256) fp32_fma_probe_kernel(int iters, float seed, float *sink) {
+    float a[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = seed + (float)(threadIdx.x + j);
+    const float m = 1.0f - seed * 1e-7f, c = seed * 1e-7f;
+    for (int i = 0; i < iters; ++i) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] = fmaf(a[j], m, c);
+    }
+    float s = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += a[j];
+    if (s == 12345.678f && sink) sink[0] = s;   // keeps the chains alive; `sink` may be null
+}
+
 }  // namespace vs

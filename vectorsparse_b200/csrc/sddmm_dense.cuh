@@ -74,14 +74,16 @@ static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 // outside [0, n) are dropped: their outputs are not written (the gather kernels write zeros there; the host
 // entry points reject such structures where they can see them).
 __global__ void __launch_bounds__(kPlanThreads)
-sddmm_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__restrict__ col_indices, int n, int chunks,
+sddmm_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__restrict__ col_indices, int n, int chunks, int nnz_vec,
                   int32_t *__restrict__ chunk_offsets, uint2 *__restrict__ chunk_entries) {
     extern __shared__ int plan_sh[];
     pdl_launch_dependents();   // the multiplying kernel may set itself up while the plan is made
     int *hist = plan_sh;             // [chunks]
     int *cursor = plan_sh + chunks;  // [chunks]
     const int i = blockIdx.x, t = threadIdx.x;
-    const int j0 = __ldg(row_offsets + i), j1 = __ldg(row_offsets + i + 1);
+    // the scratch holds nnz_vec entries (the caller's count): offsets that claim more are cut there, so that a
+    // count smaller than row_offsets[m_vec] leaves outputs unwritten instead of writing past the scratch
+    const int j0 = min(max(__ldg(row_offsets + i), 0), nnz_vec), j1 = min(max(__ldg(row_offsets + i + 1), j0), nnz_vec);
     for (int c = t; c < chunks; c += kPlanThreads) hist[c] = 0;
     __syncthreads();
     for (int j = j0 + t; j < j1; j += kPlanThreads) {

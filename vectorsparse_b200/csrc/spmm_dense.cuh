@@ -13,7 +13,7 @@
 // when B holds Inf / NaN in rows no nonzero names (0 x Inf = NaN): the epilogue therefore watches for
 // non-finite sums and, if it sees one, clears the flag that keeps the gather kernel behind it from running.
 //
-// Plan.  A small kernel first buckets the nonzero vectors by (128-row group, 32-column block): `blk_offsets`
+// Plan.  A small kernel first buckets the nonzero vectors by (128-row group, 16-column block): `blk_offsets`
 // [row groups][column blocks + 1] and `blk_entries` (vector index, vector-row within the group, column within
 // the block).  The plan depends on the structure only and is shared by every matrix of a batch.
 //
@@ -21,7 +21,7 @@
 // consecutive CTAs taking consecutive row tiles of the same B so that it stays in L2.  A stage is one 64-wide
 // block of A's columns: 32 KiB of A (two 128-row MMA operands) + 16 KiB of B, four of each in a ring.
 //   warps 0-7    epilogue: TMEM -> registers -> swizzled shared-memory boxes -> TMA stores of whole rows
-//   warps 8-23   fill: four warps per A slot, one per plan bucket (128 rows x 32 columns) of the stage
+//   warps 8-23   fill: four warps per A slot, one per 128 rows x 32 columns (two plan buckets) of the stage
 //   warp 24      one thread issuing the B loads, up to four stages ahead
 //   warp 25      L2 prefetch of the next item's part of B
 //   warps 26-27  one MMA-issuing thread per 128-row half of the tile
@@ -41,12 +41,13 @@ constexpr int kTileM = 256;                              // rows of A per work i
 constexpr int kTileN = 128;                              // columns of B per work item (MMA N)
 constexpr int kBlockK = 64;                              // columns of A (rows of B) per stage
 constexpr int kGroupRows = 128;                          // rows per plan bucket: one MMA operand
-constexpr int kPlanCols = 32;                            // columns per plan bucket: half a stage
+constexpr int kPlanCols = 16;                            // columns per plan bucket: a quarter of a stage
+constexpr int kFillCols = 32;                            // columns one fill warp of this kernel owns: two neighbouring buckets
 constexpr int kAStages = 4;                              // ring of densified A tiles
 constexpr int kBStages = 4;                              // ring of B tiles: deeper, their loads have the latency to hide
 constexpr int kEpiWarps = 8;                             // warps 0..7: TMEM lane quarter = warp % 4, half of the tile = warp / 4
 constexpr int kFillWarp0 = kEpiWarps;
-constexpr int kFillPerSlot = (kTileM / kGroupRows) * (kBlockK / kPlanCols);   // 4: one warp per plan bucket of a stage
+constexpr int kFillPerSlot = (kTileM / kGroupRows) * (kBlockK / kFillCols);   // 4: one warp per 128 rows x 32 columns of a stage
 constexpr int kFillWarps = kAStages * kFillPerSlot;      // 16: warp f fills A slot f % kAStages, bucket f / kAStages
 constexpr int kFillBatches = 2;                          // entries a fill warp keeps in flight: 2 x 32
 constexpr int kOverflowBatches = 4;                      // batches of 32 loaded together beyond those
@@ -96,7 +97,7 @@ static_assert(kBStages == kAStages || kBStages == 2 * kAStages,
 // ---- plan -------------------------------------------------------------------------------------------------
 // CTAs 0 .. groups-1: one per 128-row group (128 / V vector-rows, whose nonzero vectors are contiguous in the
 // CVSE arrays).  blk_offsets[g * (plan_blocks + 1) + c] .. [.. + c + 1] delimit the entries of group g in the
-// 32-column block c; entry = (vector index j, (vector-row within the group << 6) | column within the 64-column
+// 16-column block c; entry = (vector index j, (vector-row within the group << 6) | column within the 64-column
 // stage).  Columns outside [0, K) are dropped (the gather kernels read zeros for them).
 //
 // CTAs groups .. gridDim.x-1 look for a column that appears twice in one vector-row (the reference's generator
@@ -115,7 +116,7 @@ static_assert(kBStages == kAStages || kBStages == 2 * kAStages,
 // kTransposed: the plan of A^T for vs_spmm_t, read from the transposed structure of a CVSE matrix with vectors of
 // 1 << shift values (vs_cvse_transpose): row_offsets = t_offsets, cols = t_rows, src = t_src.  A row of A^T is a
 // column of A; a nonzero vector (i, c) of A lies in row c of A^T, columns i << shift .. (i << shift) + V - 1, which
-// never straddle a 32-column block.  The entry keeps the vector's first column and its index in the caller's
+// never straddle a 16-column block (V divides 16).  The entry keeps the vector's first column and its index in the caller's
 // `values` array (t_src), so the multiplying kernel reads the values where the forward operators keep them and
 // drops the V of them side by side into one row of its tile.  Groups are 128 rows of A^T.
 // Costs: `gather_per_row`, `gather_per_entry` for the kernel that takes the call otherwise, `dense_per_entry` for
@@ -397,7 +398,7 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
         const int half = bucket >> 1;                      // rows 128 * half .. + 127 of the tile
         const int khalf = bucket & 1;                      // columns 32 * khalf .. + 31 of the stage
         uint8_t *a_part = sm + Smem::kA + a_slot * kAStageBytes + half * (kGroupRows * kBlockK * 2);
-        const int plan_blocks = 2 * k_blocks;
+        const int plan_blocks = (kBlockK / kPlanCols) * k_blocks;
 
         // Software pipeline over this warp's stages (a_slot, a_slot + 3, ...): bucket bounds two stages ahead,
         // the first 64 entries one stage ahead, their values before the wait for the slot.
@@ -413,9 +414,11 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
         auto bounds = [&](const Pos &q, int &e0, int &e1) {
             e0 = 0; e1 = 0;
             if (q.valid) {
-                const int32_t *o = blk_offsets + ((int64_t)q.mt * (kTileM / kGroupRows) + half) * (plan_blocks + 1) + 2 * q.kb + khalf;
+                // this warp's two buckets follow one another in the entry list
+                const int32_t *o = blk_offsets + ((int64_t)q.mt * (kTileM / kGroupRows) + half) * (plan_blocks + 1) +
+                                   (kBlockK / kPlanCols) * q.kb + (kFillCols / kPlanCols) * khalf;
                 e0 = __ldg(o);
-                e1 = __ldg(o + 1);
+                e1 = __ldg(o + kFillCols / kPlanCols);
             }
         };
         Pos cur = locate(), nxt = locate();

@@ -19,8 +19,10 @@ __device__ unsigned long long g_prof[16];
 // Time line of one CTA (block 0): clock64 at event `ev` of stage / item `idx`.
 __device__ long long g_trace[16][2048];
 #define VS_TRACE(ev, idx) do { if (blockIdx.x == 0 && (idx) < 2048u) g_trace[ev][idx] = clock64(); } while (0)
+#define VS_TRACE_B(blk, ev, idx) do { if (blockIdx.x == (blk) && (idx) < 2048u) g_trace[ev][idx] = clock64(); } while (0)
 #else
 #define VS_TRACE(ev, idx) do { } while (0)
+#define VS_TRACE_B(blk, ev, idx) do { } while (0)
 #define VS_PROF_T0() do { } while (0)
 #define VS_PROF_ADD(slot) do { } while (0)
 #define VS_PROF_FLUSH(first) do { } while (0)
@@ -234,6 +236,94 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uin
 // Arrives once on `bar` when every tcgen05.mma issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// ---- pairs of CTAs (a cluster of two, tcgen05 cta_group::2) ------------------------------------------------------
+// The two CTAs of a pair run on neighbouring SMs and can address each other's shared memory.  One thread of the
+// pair's first CTA (the leader, %cluster_ctarank 0) issues MMAs that span both: with M = 256 each CTA contributes
+// 128 rows of A from its own shared memory and receives the matching 128 accumulator lanes in its own tensor
+// memory; B is split by columns, the first CTA holding columns 0 .. N/2-1 and the second N/2 .. N-1 at the same
+// shared-memory offsets, each SM reading only its own half.  Descriptors and tensor-memory addresses are offsets
+// that mean the same in both CTAs.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_id_x() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_count_x() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r));
+    return r;
+}
+// The shared::cluster address of `addr` (a shared-memory address of this CTA) in the CTA of rank `rank`.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+// Barrier over all threads of the cluster: every thread of both CTAs must reach it (no early exits).
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release;\n"
+                 "barrier.cluster.wait.acquire;" ::: "memory");
+}
+// Arrives on an mbarrier of any CTA of the cluster (`cluster_addr` from map_to_cta).  Default semantics on purpose: the
+// cluster-scope release form of this instruction was measured at ~1100 cycles per arrival on B200 (it waits for every
+// outstanding write of the SM), which made a once-per-stage forwarder the pace of a whole pipeline.  What crosses
+// between the CTAs here is consumed by the tensor core through the async proxy from shared memory that its writers
+// have fenced (fence.proxy.async) and signalled through their own CTA's barrier before this arrive is issued.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// One poll of an mbarrier of THIS CTA whose arrivals may come from the other CTA of the pair.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(kSuspendNs)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void st_remote_u32(uint32_t cluster_addr, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// Tensor memory of a pair: one warp of EACH CTA (the same warp index) executes these together; both CTAs get the
+// same columns, and both must pass the same `dst_smem` offset.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// D[tmem of both CTAs] (+)= A * B over the pair; issued by ONE thread of the leader CTA.
+__device__ __forceinline__ void mma_f16_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives once on the mbarrier at `cluster_addr` (this CTA's or, through map_to_cta, the other's) when every
+// pair MMA issued so far by this thread has completed.  One barrier per instruction: a pair of these, not a
+// cluster-wide broadcast, tells both CTAs.
+__device__ __forceinline__ void mma_commit_pair(uint32_t cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
 }
 
 // ---- TMEM -> registers: each thread of a warp reads N consecutive 32-bit columns of its own lane ------------

@@ -14,6 +14,8 @@
 #include <algorithm>
 #include <cstring>
 #include <mutex>
+#include <thread>
+#include <functional>
 #include <unordered_map>
 #include <utility>
 
@@ -23,6 +25,7 @@
 #include "spmm_tc.cuh"
 #include "spmm_tma.cuh"
 #include "spmm_dense.cuh"
+#include "spmm_pair.cuh"
 #include "spmm_t.cuh"
 #include "sddmm_tc.cuh"
 #include "sddmm_tma.cuh"
@@ -30,6 +33,11 @@
 #include "tc_selftest.cuh"
 
 #define VS_EXPORT extern "C" __attribute__((visibility("default")))
+#define VS_CUDA_TRY(expr)                      \
+    do {                                       \
+        cudaError_t e__ = (expr);              \
+        if (e__ != cudaSuccess) return (int)e__; \
+    } while (0)
 
 namespace {
 
@@ -48,8 +56,20 @@ struct DeviceInfo {
     int sm_count = 0;
     uint32_t *status = nullptr;
     // Plan scratch of the densifying SpMM, one buffer per stream that has called it: calls on one stream run
-    // in order, so they can share a buffer; calls on different streams cannot.
-    std::unordered_map<cudaStream_t, Scratch> scratch;
+    // in order, so they can share a buffer; calls on different streams cannot.  cudaStreamPerThread is one handle
+    // value that names a different stream in every host thread, so there the calling thread is part of the key.
+    struct Key {
+        cudaStream_t stream;
+        std::thread::id thread;
+        bool operator==(const Key &o) const { return stream == o.stream && thread == o.thread; }
+    };
+    struct KeyHash {
+        size_t operator()(const Key &k) const {
+            return std::hash<const void *>()(static_cast<const void *>(k.stream)) ^ (std::hash<std::thread::id>()(k.thread) * 0x9e3779b97f4a7c15ull);
+        }
+    };
+    std::unordered_map<Key, Scratch, KeyHash> scratch;
+    static Key key_of(cudaStream_t s) { return Key{s, s == cudaStreamPerThread ? std::this_thread::get_id() : std::thread::id()}; }
 };
 DeviceInfo g_devices[kMaxDevices];
 std::mutex g_devices_mutex;
@@ -88,7 +108,7 @@ thread_local int64_t t_ws_bytes = 0;
 
 // Scratch of at least `bytes` for work enqueued on `stream`.  Grows by stream-ordered allocation (the old buffer
 // is released behind the work already enqueued); in the steady state this makes no CUDA call.  Buffers live
-// until the process ends.
+// until vs_release_scratch or the end of the process.
 int stream_scratch(DeviceInfo *d, cudaStream_t stream, size_t bytes, void **out) {
     if (t_ws_set) {   // the caller's buffer or nothing: never allocate behind a caller that manages memory itself
         if ((int64_t)bytes > t_ws_bytes) return VS_ERR_SHAPE;
@@ -96,7 +116,7 @@ int stream_scratch(DeviceInfo *d, cudaStream_t stream, size_t bytes, void **out)
         return VS_OK;
     }
     std::lock_guard<std::mutex> lock(g_devices_mutex);
-    Scratch &sc = d->scratch[stream];
+    Scratch &sc = d->scratch[DeviceInfo::key_of(stream)];
     if (sc.bytes < bytes) {
         size_t want = 1u << 20;
         while (want < bytes) want <<= 1;
@@ -143,6 +163,31 @@ cudaError_t launch_overlapped(void (*kernel)(Exp...), unsigned grid, unsigned bl
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = overlap ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Act>(args)...);
+}
+
+// Launches `pairs` clusters of two CTAs (tcgen05 cta_group::2 kernels), optionally as a programmatic dependent.
+template <typename... Exp, typename... Act>
+cudaError_t launch_pairs(void (*kernel)(Exp...), unsigned pairs, unsigned block, size_t smem, cudaStream_t s, bool overlapped,
+                         Act &&...args) {
+    static const bool overlap = []() {
+        const char *e = std::getenv("VSPARSE_B200_PDL");
+        return !(e && !std::strcmp(e, "0"));
+    }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (overlapped && overlap) ? 2 : 1;
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Act>(args)...);
 }
 
@@ -338,6 +383,60 @@ int64_t sddmm_plan_bytes(int m_vec, int n, int nnz_vec, int64_t *offsets_out) {
     return offsets_bytes + (int64_t)nnz_vec * 8;
 }
 
+// How many pairs of CTAs of `kernel` the device holds at once (one CTA per SM, two neighbouring SMs per pair).
+template <typename K> int max_resident_pairs(K kernel, int block, size_t smem, DeviceInfo *d) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (unsigned)d->sm_count);
+    cfg.blockDim = dim3((unsigned)block);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+// The densified product by pairs of CTAs (spmm_pair.cuh) takes dense widths that are multiples of 128; the
+// single-CTA kernel (spmm_dense.cuh) the other widths.  VSPARSE_B200_SPMM_PAIR=0 keeps every width on the latter.
+inline bool spmm_pair_enabled() {
+    const char *e = std::getenv("VSPARSE_B200_SPMM_PAIR");
+    return !(e && !std::strcmp(e, "0"));
+}
+// Enqueues the pair kernel for a call whose plan kernel has been enqueued; false if this device cannot hold it.
+template <typename TOut, int V, bool kTransposed>
+bool launch_spmm_pair(const SpmmParams &q, cudaStream_t s, DeviceInfo *d, const CUtensorMap &map, const CUtensorMap &map_out,
+                      const CUtensorMap &map_b2, const int32_t *blk_offsets, const uint2 *blk_entries, int m_tiles, int k_blocks,
+                      int32_t *flag, int checks, int *rc_out) {
+    static int resident[kMaxDevices];   // 0 = not asked yet, -1 = the kernel cannot run here
+    auto kernel = pairspmm::spmm_pair_kernel<TOut, V, kTransposed>;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return false;
+    if (resident[dev] == 0) {
+        if (set_smem(kernel, pairspmm::kSmemBytes) != VS_OK) {
+            resident[dev] = -1;
+        } else {
+            const int n = max_resident_pairs(kernel, pairspmm::kThreads, pairspmm::kSmemBytes, d);
+            resident[dev] = n > 0 ? n : -1;
+        }
+    }
+    if (resident[dev] < 0) return false;
+    const int tn = q.N % 256 == 0 ? 256 : 128;
+    const int n_tiles = q.N / tn;
+    const int64_t items = (int64_t)q.batch * n_tiles * m_tiles;
+    const unsigned pairs = (unsigned)(items < resident[dev] ? items : resident[dev]);
+    *rc_out = (int)launch_pairs(kernel, pairs, pairspmm::kThreads, (size_t)pairspmm::kSmemBytes, s, true, q, map, map_out, map_b2, tn,
+                                blk_offsets, blk_entries, m_tiles, n_tiles, k_blocks, d->status, flag, checks);
+    return true;
+}
+
 template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStream_t s) {
     DeviceInfo *d;
     int rc = device_info(&d);
@@ -387,9 +486,15 @@ template <typename TOut, int V> int launch_spmm_tc(const SpmmParams &p, cudaStre
     const int64_t items = (int64_t)p.batch * n_tiles * m_tiles;
     const unsigned grid = (unsigned)(items < d->sm_count ? items : d->sm_count);   // one persistent CTA per SM
     rc = (int)cudaGetLastError();
-    if (rc == VS_OK)
-        rc = (int)launch_overlapped(kernel, grid, densespmm::kThreads, densespmm::kSmemBytes, s, p, map, map_out, map_b4, use_b4,
-                                    blk_offsets, blk_entries, m_tiles, n_tiles, k_blocks, d->status, flag, checks);
+    if (rc == VS_OK) {
+        int rc_pair = VS_OK;
+        if (use_b4 && p.N % 128 == 0 && spmm_pair_enabled() &&
+            launch_spmm_pair<TOut, V, false>(p, s, d, map, map_out, map_b4, blk_offsets, blk_entries, m_tiles, k_blocks, flag, checks, &rc_pair))
+            rc = rc_pair;
+        else
+            rc = (int)launch_overlapped(kernel, grid, densespmm::kThreads, densespmm::kSmemBytes, s, p, map, map_out, map_b4, use_b4,
+                                        blk_offsets, blk_entries, m_tiles, n_tiles, k_blocks, d->status, flag, checks);
+    }
     if (rc == VS_OK) rc = launch_spmm_gather<TOut, V>(p, s, d, flag, checks);
     return rc;
 }
@@ -510,7 +615,7 @@ template <typename TOut, int V> int launch_sddmm_tc(const SddmmParams &p, cudaSt
     int32_t *chunk_offsets = reinterpret_cast<int32_t *>(plan);
     uint2 *chunk_entries = reinterpret_cast<uint2 *>(plan + offsets_bytes);
     densesddmm::sddmm_plan_kernel<<<p.m_vec, densesddmm::kPlanThreads, plan_smem, s>>>(p.row_offsets, p.col_indices, p.n, chunks,
-                                                                                   chunk_offsets, chunk_entries);
+                                                                                   p.nnz_vec, chunk_offsets, chunk_entries);
     const int m_tiles = (p.m_vec * V + densesddmm::kTileM - 1) / densesddmm::kTileM;
     const int n_tiles = (p.n + densesddmm::kTileN - 1) / densesddmm::kTileN;
     const int64_t items = (int64_t)p.batch * m_tiles * n_tiles;
@@ -690,9 +795,15 @@ template <typename TOut, int V> int launch_spmm_t(const spmmt::Params &p, int m_
                                 blk_entries, capacity, mode == SpmmTMode::kDense ? 1 : 0, 0.0f, 5.0f * V, 1.5f, flag);
     const int64_t items = (int64_t)q.batch * n_tiles * m_tiles;
     const unsigned grid = (unsigned)(items < d->sm_count ? items : d->sm_count);   // one persistent CTA per SM
-    if (rc == VS_OK)
-        rc = (int)launch_overlapped(kernel, grid, densespmm::kThreads, densespmm::kSmemBytes, s, q, map, map_out, map_b4, use_b4,
-                                    blk_offsets, blk_entries, m_tiles, n_tiles, k_blocks, d->status, flag, checks);
+    if (rc == VS_OK) {
+        int rc_pair = VS_OK;
+        if (use_b4 && q.N % 128 == 0 && spmm_pair_enabled() &&
+            launch_spmm_pair<TOut, V, true>(q, s, d, map, map_out, map_b4, blk_offsets, blk_entries, m_tiles, k_blocks, flag, checks, &rc_pair))
+            rc = rc_pair;
+        else
+            rc = (int)launch_overlapped(kernel, grid, densespmm::kThreads, densespmm::kSmemBytes, s, q, map, map_out, map_b4, use_b4,
+                                        blk_offsets, blk_entries, m_tiles, n_tiles, k_blocks, d->status, flag, checks);
+    }
     if (rc == VS_OK) rc = launch_spmm_t_cc<TOut, V>(p, s, d, flag, checks);
     return rc;
 }
@@ -851,6 +962,16 @@ VS_EXPORT int vs_attention_cvse_backward(int path, int m_vec, int vec_length, in
     const int64_t s_ws = (int64_t)nonzeros_vec * vec_length;
     if ((s_ws * 2) % 16 != 0 && batch > 1) return VS_ERR_ALIGN;
     const int64_t s_q = m * d, s_k = (int64_t)n * d;
+    if (nonzeros_vec == 0) {   // an empty mask: the output does not depend on q, k or v
+        if (m_vec < 0 || n < 0 || d < 0 || batch < 1 || !valid_v(vec_length)) return VS_ERR_ARG;
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        if (s_q > 0 && !grad_q) return VS_ERR_NULL;
+        if (s_k > 0 && (!grad_k || !grad_v)) return VS_ERR_NULL;
+        if (s_q > 0) VS_CUDA_TRY(cudaMemsetAsync(grad_q, 0, (size_t)batch * s_q * 2, st));
+        if (s_k > 0) VS_CUDA_TRY(cudaMemsetAsync(grad_k, 0, (size_t)batch * s_k * 2, st));
+        if (s_k > 0) VS_CUDA_TRY(cudaMemsetAsync(grad_v, 0, (size_t)batch * s_k * 2, st));
+        return VS_OK;
+    }
     // P = softmax(scale * Q K^T) at the mask, recomputed rather than kept from the forward pass
     int rc = vs_sddmm_batched(path, VS_F16, VS_F16, m_vec, d, n, nonzeros_vec, row_indices, row_offsets, col_indices, q, kmat,
                               probs_workspace, vec_length, batch, s_q, s_k, s_ws, stream, 0);
@@ -885,6 +1006,12 @@ VS_EXPORT int vs_attention_cvse(int path, int m_vec, int vec_length, int n, int 
     const int64_t m = (int64_t)m_vec * vec_length;
     const int64_t s_ws = (int64_t)nonzeros_vec * vec_length;
     if ((s_ws * 2) % 16 != 0 && batch > 1) return VS_ERR_ALIGN;
+    if (nonzeros_vec == 0) {   // an empty mask: no scores, no probabilities, every output row is zero
+        if (m_vec < 0 || d < 0 || batch < 1 || !valid_v(vec_length)) return VS_ERR_ARG;
+        if (m == 0 || d == 0) return VS_OK;
+        if (!out) return VS_ERR_NULL;
+        return (int)cudaMemsetAsync(out, 0, (size_t)batch * m * d * 2, static_cast<cudaStream_t>(stream));
+    }
     int rc = vs_sddmm_batched(path, VS_F16, VS_F16, m_vec, d, n, nonzeros_vec, row_indices, row_offsets,
                               col_indices, q, kmat, workspace, vec_length, batch, m * d, (int64_t)n * d, s_ws,
                               stream, 0);
@@ -964,11 +1091,6 @@ struct DeviceBuffers {  // frees whatever was allocated when it goes out of scop
         for (int i = 0; i < count; ++i) cudaFree(ptr[i]);
     }
 };
-#define VS_CUDA_TRY(expr)                      \
-    do {                                       \
-        cudaError_t e__ = (expr);              \
-        if (e__ != cudaSuccess) return (int)e__; \
-    } while (0)
 }  // namespace
 
 VS_EXPORT int vs_spmm_host(int path, int in_dtype, int out_dtype, int m_vec, int vec_length, int k, int n,
@@ -1071,12 +1193,64 @@ VS_EXPORT int vs_set_workspace(void *workspace, int64_t bytes) {
     return VS_OK;
 }
 
+VS_EXPORT int vs_release_scratch(void *stream, int every_stream) {
+    DeviceInfo *d;
+    int rc = device_info(&d);
+    if (rc != VS_OK) return rc;
+    std::lock_guard<std::mutex> lock(g_devices_mutex);
+    if (every_stream) {
+        for (auto &kv : d->scratch)
+            if (kv.second.ptr) (void)cudaFreeAsync(kv.second.ptr, kv.first.stream);
+        d->scratch.clear();
+        return VS_OK;
+    }
+    auto it = d->scratch.find(DeviceInfo::key_of(static_cast<cudaStream_t>(stream)));
+    if (it != d->scratch.end()) {
+        if (it->second.ptr) (void)cudaFreeAsync(it->second.ptr, it->first.stream);
+        d->scratch.erase(it);
+    }
+    return VS_OK;
+}
+
 VS_EXPORT int vs_sddmm_formulation(int m_vec, int k, int n, int nonzeros_vec, int vec_length) {
     if (m_vec <= 0 || n <= 0 || k < densesddmm::kBlockK || nonzeros_vec <= 0 || !(vec_length == 2 || vec_length == 4 || vec_length == 8))
         return 0;
     SddmmParams p{};
     p.m_vec = m_vec; p.k = k; p.n = n; p.nnz_vec = nonzeros_vec;
     return sddmm_use_dense(p, vec_length) ? 1 : 0;
+}
+
+VS_EXPORT int vs_measure_fp32_fma(double *tflops) {
+    if (!tflops) return VS_ERR_NULL;
+    DeviceInfo *d;
+    int rc = device_info(&d);
+    if (rc != VS_OK) return rc;
+    const int iters = 1 << 14, blocks = d->sm_count * 8, threads = 256;
+    cudaEvent_t e0, e1;
+    VS_CUDA_TRY(cudaEventCreate(&e0));
+    VS_CUDA_TRY(cudaEventCreate(&e1));
+    float *sink = nullptr;
+    fp32_fma_probe_kernel<<<blocks, threads>>>(iters, 1.0f, sink);   // warm-up
+    double best = 0.0;
+    for (int rep = 0; rep < 3; ++rep) {
+        cudaEventRecord(e0);
+        fp32_fma_probe_kernel<<<blocks, threads>>>(iters, 1.0f, sink);
+        cudaEventRecord(e1);
+        cudaError_t e = cudaEventSynchronize(e1);
+        float ms = 0.0f;
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+        if (e != cudaSuccess) {
+            cudaEventDestroy(e0);
+            cudaEventDestroy(e1);
+            return (int)e;
+        }
+        const double t = 2.0 * 8.0 * iters * (double)blocks * threads / (ms * 1e-3) / 1e12;
+        if (t > best) best = t;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    *tflops = best;
+    return VS_OK;
 }
 
 VS_EXPORT int vs_device_status(int clear, uint32_t *status) {
@@ -1126,19 +1300,85 @@ VS_EXPORT int vs_debug_trace(long long *out_16x2048) {
 }
 #endif
 
-VS_EXPORT int vs_selftest_mma(const void *image, int image_bytes, const uint64_t *descs, int n_mma,
+namespace {
+// Whether the 16 contraction elements x `rows` fp16 operand a shared-memory descriptor names lies inside an image
+// of `image_bytes` (descriptor start relative to the image).  Only the layouts the kernels use are accepted:
+// no swizzle or the 128-byte swizzle, either major.
+bool selftest_operand_fits(uint64_t desc, int rows, bool mn_major, int image_bytes) {
+    const int64_t start = (int64_t)(desc & 0x3fffu) << 4, lbo = (int64_t)((desc >> 16) & 0x3fffu) << 4,
+                  sbo = (int64_t)((desc >> 32) & 0x3fffu) << 4;
+    const unsigned swizzle = (unsigned)(desc >> 61) & 7u;
+    if (swizzle != 0 && swizzle != 2) return false;
+    if (rows < 8 || rows % 8 != 0) return false;
+    int64_t end;
+    if (swizzle == 2 && mn_major) {          // atoms of 64 rows x 8 contraction elements (1 KiB): LBO between atoms along the rows, SBO along the contraction
+        if (rows % 64 != 0) return false;
+        end = start + (rows / 64 - 1) * lbo + sbo + 1024;
+    } else if (swizzle == 2) {               // rows of 128 bytes, eight to a 1 KiB block, SBO between blocks; the 32 bytes of a step stay inside a row
+        if (start % 128 + 32 > 128) return false;
+        end = start - start % 128 + (rows / 8 - 1) * sbo + 1024;
+    } else {                                 // unswizzled: 128-byte core matrices, LBO between them along the contraction, SBO along the rows
+        end = start + (rows / 8 - 1) * sbo + lbo + 128;
+    }
+    return start >= 0 && end <= image_bytes;
+}
+// Decodes what the self-test kernels rely on from an instruction descriptor; false for anything else.
+bool selftest_idesc(uint32_t idesc, int max_m, int *M, int *N, bool *a_mn, bool *b_mn) {
+    *N = (int)((idesc >> 17) & 0x3fu) << 3;
+    *M = (int)((idesc >> 24) & 0x1fu) << 4;
+    *a_mn = (idesc >> 15) & 1u;
+    *b_mn = (idesc >> 16) & 1u;
+    if ((idesc & ~((0x3fu << 17) | (0x1fu << 24) | (1u << 15) | (1u << 16))) != (1u << 4)) return false;   // fp16 x fp16 -> fp32 only
+    return *M == max_m && *N >= 16 && *N <= 256 && *N % 16 == 0;
+}
+}  // namespace
+
+VS_EXPORT int vs_selftest_mma(const void *image, int image_bytes, const uint64_t *descs_host, int n_mma,
                               uint32_t idesc, int ncols, float fill, float *out, void *stream) {
-    if (!image || !descs || !out) return VS_ERR_NULL;
+    if (!image || !descs_host || !out) return VS_ERR_NULL;
     if (image_bytes <= 0 || image_bytes > 128 * 1024 || n_mma < 1 || n_mma > 64) return VS_ERR_SHAPE;
     if (ncols < 8 || ncols > tcselftest::kTmemCols || ncols % 8 != 0) return VS_ERR_SHAPE;
     if (!aligned16(image)) return VS_ERR_ALIGN;
+    int M, N;
+    bool a_mn, b_mn;
+    if (!selftest_idesc(idesc, 128, &M, &N, &a_mn, &b_mn) || N > ncols) return VS_ERR_SHAPE;
+    for (int i = 0; i < n_mma; ++i)
+        if (!selftest_operand_fits(descs_host[2 * i], M, a_mn, image_bytes) || !selftest_operand_fits(descs_host[2 * i + 1], N, b_mn, image_bytes))
+            return VS_ERR_SHAPE;
     DeviceInfo *d;
     int rc = device_info(&d);
     if (rc != VS_OK) return rc;
     const int smem = ((image_bytes + 15) & ~15) + 16 + 1024;
     rc = set_smem(tcselftest::sandbox_kernel, smem);
     if (rc != VS_OK) return rc;
+    tcselftest::DescList descs;
+    std::memcpy(descs.d, descs_host, sizeof(uint64_t) * 2 * n_mma);
     tcselftest::sandbox_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint8_t *>(image), image_bytes, descs, n_mma, idesc, ncols, fill, out, d->status);
     return (int)cudaGetLastError();
+}
+
+VS_EXPORT int vs_selftest_mma_pair(const void *image0, const void *image1, int image_bytes, const uint64_t *descs_host,
+                                   int n_mma, uint32_t idesc, int ncols, float fill, float *out, void *stream) {
+    if (!image0 || !image1 || !descs_host || !out) return VS_ERR_NULL;
+    if (image_bytes <= 0 || image_bytes > 128 * 1024 || n_mma < 1 || n_mma > 64) return VS_ERR_SHAPE;
+    if (ncols < 8 || ncols > tcselftest::kPairTmemCols || ncols % 8 != 0) return VS_ERR_SHAPE;
+    if (!aligned16(image0) || !aligned16(image1)) return VS_ERR_ALIGN;
+    int M, N;
+    bool a_mn, b_mn;
+    if (!selftest_idesc(idesc, 256, &M, &N, &a_mn, &b_mn) || N > ncols || N % 32 != 0) return VS_ERR_SHAPE;
+    for (int i = 0; i < n_mma; ++i)   // per CTA: 128 rows of A, N / 2 columns of B
+        if (!selftest_operand_fits(descs_host[2 * i], 128, a_mn, image_bytes) || !selftest_operand_fits(descs_host[2 * i + 1], N / 2, b_mn, image_bytes))
+            return VS_ERR_SHAPE;
+    DeviceInfo *d;
+    int rc = device_info(&d);
+    if (rc != VS_OK) return rc;
+    const int smem = ((image_bytes + 15) & ~15) + 16 + 1024;
+    rc = set_smem(tcselftest::sandbox_pair_kernel, smem);
+    if (rc != VS_OK) return rc;
+    tcselftest::DescList descs;
+    std::memcpy(descs.d, descs_host, sizeof(uint64_t) * 2 * n_mma);
+    return (int)launch_pairs(tcselftest::sandbox_pair_kernel, 1, 128, (size_t)smem, static_cast<cudaStream_t>(stream), false,
+                             static_cast<const uint8_t *>(image0), static_cast<const uint8_t *>(image1), image_bytes, descs, n_mma,
+                             idesc, ncols, fill, out, d->status);
 }

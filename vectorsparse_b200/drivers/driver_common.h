@@ -59,6 +59,9 @@ inline HostCvse load_benchmark(const std::string &bm, int vec_length, bool sorte
             fprintf(stderr, "unknown synthetic kind: %s\n", kind);
             exit(1);
         }
+        // a vector length the operators do not support still gets a pattern, so that the call is made and answers
+        // "Unsupported Vector Length!" itself, as the reference's dispatch does (src/wmma_spmm.cu:345-346)
+        if (!(vec_length == 1 || vec_length == 2 || vec_length == 4 || vec_length == 8)) vec_length = 1;
         a.row_offsets.resize((size_t)a.m_vec + 1);
         int nnz = vs_cvse_generate(k, seed, a.m_vec, a.n, vec_length, sparsity, band, a.row_offsets.data(), nullptr);
         check_vs(nnz < 0 ? nnz : 0, "vs_cvse_generate");
