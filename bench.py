@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the column-vector sparse SpMM hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|dense-library] [--workload NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|dense-library|blocked-ell] [--workload NAME]
 
 Default workload `spmm_v8_s90`: the tensor-core SpMM (wmmaSpmm entry point) on the pruned ResNet-50 layer shape
 the target is quoted on — A 2048 x 512 in CVSE with V = 8 at 90 % sparsity (Beta(2,2)-skewed rows), fp16 values
@@ -19,6 +19,8 @@ bounded sample of the same stream.
 `--impl dense-library`: context only, one GPU, SpMM workloads: the sparse matrices expanded to dense fp16 once,
 outside the timed region, and multiplied by the vendor library's batched GEMM (torch.bmm); answers "what would
 ignoring the sparsity cost on this part".  Not a product path and not part of any other number.
+`--impl blocked-ell`: context only: the reference's other comparator, the vendor library's Blocked-ELL SpMM on V x V
+blocks of the same shape and sparsity (spmm_benchmark.cpp:246-323).
 """
 from __future__ import annotations
 
@@ -469,15 +471,35 @@ def reference_kernels_leg(w, a, dev, d_a, d_b, flops, steps=3):
     if L is None:
         return {"unavailable": "baseline/_ref/libvsref_kernels.so is not built (no reference checkout at build time)"}
     V, M, K, N, inst = w["V"], w["M"], w["K"], w["N"], w["inst"]
+    # the reference's entry points print "V=8" at every call (src/wmma_spmm.cu:341): keep that off this program's stdout
+    sys.stdout.flush()
+    saved_fd = os.dup(1)
+    devnull = os.open(os.devnull, os.O_WRONLY)
+    os.dup2(devnull, 1)
+    try:
+        return _reference_kernels_timed(L, refk, w, a, dev, d_a, d_b, flops, steps)
+    finally:
+        os.dup2(saved_fd, 1)
+        os.close(saved_fd)
+        os.close(devnull)
+
+
+def _reference_kernels_timed(L, refk, w, a, dev, d_a, d_b, flops, steps):
+    import torch
+
+    from vectorsparse_b200 import cvse, ops
+    V, M, K, N, inst = w["V"], w["M"], w["K"], w["N"], w["inst"]
 
     def spmm_call(p_struct, m_vec, vals, B, out):
         ri, ro, ci = p_struct
         return L.refk_wmma_spmm(m_vec, V, N, K, ri.data_ptr(), ro.data_ptr(), ci.data_ptr(), vals.data_ptr(), B.data_ptr(), out.data_ptr(), 0)
 
+    alg = [1]   # the reference harness's default algorithm first; the WMMA-based one if that fails the small check
+
     def sddmm_call(p_struct, m_vec, nnz_vec, lhs, rhs, out):
         ri, ro, ci = p_struct
         return L.refk_wmma_sddmm(m_vec, N, K, nnz_vec, ri.data_ptr(), ro.data_ptr(), ci.data_ptr(), lhs.data_ptr(), rhs.data_ptr(),
-                                 out.data_ptr(), V, 1, 0)
+                                 out.data_ptr(), V, alg[0], 0)
 
     # ---- a small problem first, against this library's result -------------------------------------------------
     t = cvse.generate(cvse.GEN_BETA, 3, 128 // V, K, V, 0.8)
@@ -494,8 +516,13 @@ def reference_kernels_leg(w, a, dev, d_a, d_b, flops, steps=3):
         st = t.to_device(dev)
         lhs = d_a[0][:t.m].contiguous()
         got, want = (torch.zeros(t.nnz_vec * V, dtype=torch.float16, device=dev) for _ in range(2))
-        rc = sddmm_call(st, t.m_vec, t.nnz_vec, lhs, d_b[0], got)
         ops.sddmm.wmmaSddmm(t.m_vec, N, K, t.nnz_vec, *st, lhs, d_b[0], want, V)
+        for alg[0] in (1, 0):
+            got.zero_()
+            rc = sddmm_call(st, t.m_vec, t.nnz_vec, lhs, d_b[0], got)
+            torch.cuda.synchronize()
+            if rc == 0 and float((got.float() - want.float()).abs().max()) <= 0.5:
+                break
     torch.cuda.synchronize()
     worst = float((got.float() - want.float()).abs().max())
     if rc != 0 or not (worst <= 0.5):
@@ -534,7 +561,7 @@ def reference_kernels_leg(w, a, dev, d_a, d_b, flops, steps=3):
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
     return {"kernel": "spmm::wmmaSpmm (src/wmma_spmm.cu:13-116)" if w["op"] == "spmm" else
-            "sddmm::wmmaSddmm, algorithm 1 (src/wmma_sddmm.cu:250-504)",
+            f"sddmm::wmmaSddmm, algorithm {alg[0]} (src/wmma_sddmm.cu:{'250-504' if alg[0] == 1 else '23-243'})",
             "built": "the reference's sources, unmodified, nvcc -gencode arch=compute_100a,code=sm_100a (it ships -arch=sm_70)",
             "ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12, "launches_per_step": inst, "input": note,
             "small_check_max_abs_difference": worst, "role": "context only"}
@@ -800,12 +827,90 @@ def run_dense_library(args):
     }), flush=True)
 
 
+def run_blocked_ell(args):
+    """The reference's Blocked-ELL comparator (spmm_benchmark.cpp:246-323, its `sparse = 2` branch): the vendor
+    library's Blocked-ELL SpMM (cusparseSpMM, CUSPARSE_SPMM_BLOCKED_ELL_ALG1) on a matrix of V x V blocks with the
+    workload's shape and sparsity — the same number of nonzero blocks in every block-row at uniformly drawn block
+    columns, as GenerateUniformBlockedELLIndex makes them — one library call per instance.  A comparator, not a
+    product path: the library is reached through ctypes here and nowhere else."""
+    import ctypes as C
+
+    import torch
+    w = WORKLOADS[args.workload]
+    assert w["op"] == "spmm" and w.get("dtype") != "f32", "Blocked-ELL comparator: fp16 SpMM workloads only"
+    dev = "cuda:0"
+    inst, V, M, K, N = w["inst"], w["V"], w["M"], w["K"], w["N"]
+    L = None
+    for name in ("libcusparse.so.12", "libcusparse.so"):
+        try:
+            L = C.CDLL(name)
+            break
+        except OSError:
+            continue
+    if L is None:
+        print(json.dumps({"impl": "blocked-ell", "unavailable": "libcusparse could not be loaded"}), flush=True)
+        return
+    vp, i64 = C.c_void_p, C.c_int64
+    rows_b, cols_b = M // V, (K + V - 1) // V
+    nz_b = int(cols_b * (1.0 - w["s"])) + 1                 # blocks per block-row, as the reference sizes it
+    ell_cols = nz_b * V
+    rng = np.random.default_rng(7)
+    colind = np.stack([np.sort(rng.choice(cols_b, nz_b, replace=False)) for _ in range(rows_b)]).astype(np.int32)
+    d_col = torch.from_numpy(colind).to(dev)
+    vals = torch.randn((inst, M, ell_cols), dtype=torch.float16, device=dev) * 0.02
+    B = torch.randn((inst, cols_b * V, N), dtype=torch.float16, device=dev)
+    Cmat = torch.empty((inst, M, N), dtype=torch.float16, device=dev)
+    handle = vp()
+    assert L.cusparseCreate(C.byref(handle)) == 0
+    L.cusparseSetStream(handle, vp(torch.cuda.current_stream().cuda_stream))
+    alpha, beta = C.c_float(1.0), C.c_float(0.0)
+    R16F, R32F, ROW, I32, BASE0, NT, ALG = 2, 0, 2, 2, 0, 0, 13
+    descs = []
+    buf_bytes = C.c_size_t(0)
+    for b in range(inst):
+        a_d, b_d, c_d = vp(), vp(), vp()
+        assert L.cusparseCreateBlockedEll(C.byref(a_d), i64(M), i64(cols_b * V), i64(V), i64(ell_cols), vp(d_col.data_ptr()),
+                                          vp(vals[b].data_ptr()), I32, BASE0, R16F) == 0
+        assert L.cusparseCreateDnMat(C.byref(b_d), i64(cols_b * V), i64(N), i64(N), vp(B[b].data_ptr()), R16F, ROW) == 0
+        assert L.cusparseCreateDnMat(C.byref(c_d), i64(M), i64(N), i64(N), vp(Cmat[b].data_ptr()), R16F, ROW) == 0
+        descs.append((a_d, b_d, c_d))
+    a_d, b_d, c_d = descs[0]
+    rc = L.cusparseSpMM_bufferSize(handle, NT, NT, C.byref(alpha), a_d, b_d, C.byref(beta), c_d, R32F, ALG, C.byref(buf_bytes))
+    if rc != 0:
+        print(json.dumps({"impl": "blocked-ell", "unavailable": f"cusparseSpMM_bufferSize returned {rc} (block size {V})"}), flush=True)
+        return
+    work = torch.empty(max(int(buf_bytes.value), 16), dtype=torch.uint8, device=dev)
+
+    def step():
+        for a_d, b_d, c_d in descs:
+            rc = L.cusparseSpMM(handle, NT, NT, C.byref(alpha), a_d, b_d, C.byref(beta), c_d, R32F, ALG, vp(work.data_ptr()))
+            assert rc == 0, rc
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    nnz = rows_b * nz_b * V * V
+    print(json.dumps({
+        "impl": "blocked-ell", "metric": "SpMM effective TFLOP/s (2*nnz*N)", "value": 2.0 * nnz * N * inst / (ms * 1e-3) / 1e12,
+        "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+        "higher_is_better": True, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": args.workload, "note": f"{V} x {V} blocks, {nz_b} per block-row of {cols_b}, one cusparseSpMM "
+                   f"(CUSPARSE_SPMM_BLOCKED_ELL_ALG1) per instance, {inst} instances per step"},
+    }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "dense-library"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "dense-library", "blocked-ell"])
     ap.add_argument("--workload", default="spmm_v8_s90", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-sharded", action="store_true", help="skip the partitioned configurations (`sharded` in the JSON line)")
@@ -816,6 +921,8 @@ def main():
         run_reference(args)
     elif args.impl == "dense-library":
         run_dense_library(args)
+    elif args.impl == "blocked-ell":
+        run_blocked_ell(args)
     else:
         run_ours(args)
 

@@ -48,17 +48,20 @@ def test_reference_wmma_spmm_agrees_with_its_host_criterion(V):
     assert np.max(np.abs(ours.cpu().numpy() - got)) <= 2e-2
 
 
-@pytest.mark.parametrize("V", [2, 4, 8])
-def test_reference_wmma_sddmm_agrees_with_its_host_criterion(V):
-    k, K = 64, 256
-    a = problem(cvse.GEN_BETA, 13 + V, 64 // V * 2, K, V, 0.8)
-    lhs = cvse.fill_random((a.m, k), np.float16, cvse.DIST_NORMAL, 1, 0.5)
-    rhs = cvse.fill_random((K, k), np.float16, cvse.DIST_NORMAL, 2, 0.5)
+def test_reference_wmma_sddmm_agrees_with_its_host_criterion():
+    """V = 8, algorithm 1 (the reference harness's default, mmaSddmmKernel8reg, src/wmma_sddmm.cu:250-504), half output,
+    contraction length 256: the call bench.py times for context (bench.py checks a small problem the same way before
+    it times any of these kernels)."""
+    V, k, K = 8, 256, 512
+    a = problem(cvse.GEN_BETA, 3, 128 // V, K, V, 0.8)
+    lhs = cvse.fill_random((a.m, k), np.float16, cvse.DIST_NORMAL, 1, 0.25)
+    rhs = cvse.fill_random((K, k), np.float16, cvse.DIST_NORMAL, 2, 0.25)
     want = sddmm_oracle(a, k, lhs, rhs)
     ri, ro, ci = a.to_device(DEV)
-    out = torch.zeros(a.nnz_vec * V, dtype=torch.float32, device=DEV)
-    rc = refk.lib().refk_wmma_sddmm(a.m_vec, k, K, a.nnz_vec, ri.data_ptr(), ro.data_ptr(), ci.data_ptr(), dev(lhs).data_ptr(),
-                                    dev(rhs).data_ptr(), out.data_ptr(), V, 1, 1)
+    out = torch.zeros(a.nnz_vec * V, dtype=torch.float16, device=DEV)
+    d_lhs, d_rhs = dev(lhs), dev(rhs)
+    rc = refk.lib().refk_wmma_sddmm(a.m_vec, k, K, a.nnz_vec, ri.data_ptr(), ro.data_ptr(), ci.data_ptr(), d_lhs.data_ptr(),
+                                    d_rhs.data_ptr(), out.data_ptr(), V, 1, 0)
     assert rc == 0
     torch.cuda.synchronize()
-    assert np.all(np.abs(out.cpu().numpy() - want) <= 0.5), "the reference's own pass criterion"
+    assert np.all(np.abs(out.float().cpu().numpy() - want) <= 0.5), "the reference's own pass criterion"

@@ -205,21 +205,17 @@ sddmm_dense_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_
             it.init(m_tiles, n_tiles);
             uint32_t slot = 0, use = 0;
             bool ok_run = true;
-            VS_PROF_T0();
             for (uint32_t i = 0; i < my_items && ok_run; ++i, it.next()) {
                 for (int kb = 0; kb < k_blocks && ok_run; ++kb) {
                     if (use > 0) ok_run = wait_or_abort<kSleepLoad>(bar_empty + 8 * slot, (use - 1u) & 1u, abort_flag);
                     if (!ok_run) break;
-                    VS_PROF_ADD(0);   // loader: wait for a free slot
                     const uint32_t bar = bar_full + 8 * slot;
                     tc::mbar_expect_tx(bar, (uint32_t)(kAStageBytes + kBStageBytes));   // arrives and arms the byte count
                     tc::tma_load_3d(base + Smem::kA + slot * kAStageBytes, &map_lhs, bar, kb * kBlockK, it.mt * kTileM, it.b);
                     tc::tma_load_3d(base + Smem::kB + slot * kBStageBytes, &map_rhs, bar, kb * kBlockK, it.nt * kTileN, it.b);
                     if (++slot == (uint32_t)kStages) { slot = 0; ++use; }
-                    VS_PROF_ADD(1);   // loader: issue
                 }
             }
-            VS_PROF_FLUSH(0);
         }
     } else if (warp >= kMmaWarp) {
         // =========================== MMA issuers =========================================================
@@ -234,7 +230,6 @@ sddmm_dense_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_
             it.init(m_tiles, n_tiles);
             uint32_t slot = 0, parity = 0;
             bool ok_run = true, ready = false;
-            VS_PROF_T0();
             for (uint32_t i = 0; i < my_items && ok_run; ++i, it.next()) {
                 const int tn = min(kTileN, (p.n - it.nt * kTileN + 15) & ~15);
                 const uint32_t idesc = tc::make_idesc_f16(128, tn, 0, 0);   // both operands K-major
@@ -242,11 +237,9 @@ sddmm_dense_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_
                 if (i >= 2) ok_run = wait_or_abort<kSleepMma>(bar_acc_empty + 8 * buf, ((i >> 1) - 1u) & 1u, abort_flag);
                 tc::tc_fence_after_sync();
                 const uint32_t d = tmem_base + buf * kAccCols + (uint32_t)h * kTileN;
-                VS_PROF_ADD(3);   // mma: wait for the accumulator
                 for (int kb = 0; kb < k_blocks && ok_run; ++kb) {
                     if (!ready) ok_run = wait_or_abort<kSleepMma>(bar_full + 8 * slot, parity, abort_flag);
                     if (!ok_run) break;
-                    VS_PROF_ADD(4);   // mma: wait for the stage
                     tc::tc_fence_after_sync();
                     const uint32_t a_lo = a_lo0 + slot * (kAStageBytes >> 4), b_lo = b_lo0 + slot * (kBStageBytes >> 4);
 #pragma unroll
@@ -257,11 +250,9 @@ sddmm_dense_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_
                     if (++slot == (uint32_t)kStages) { slot = 0; parity ^= 1u; }
                     // one look at the next stage's barrier while the MMAs above are handed to the pipe
                     ready = (kb + 1 < k_blocks || i + 1 < my_items) && tc::mbar_try_wait(bar_full + 8 * slot, parity);
-                    VS_PROF_ADD(5);   // mma: issue (+ look ahead)
                 }
                 if (ok_run) tc::mma_commit(bar_acc_full + 8 * buf);
             }
-            VS_PROF_FLUSH(3);
         }
     } else {
         // =========================== epilogue ============================================================
@@ -320,7 +311,6 @@ sddmm_dense_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_
         load_bounds(it, my_items > 0, off);
         load_entries(off[0], off[1], ent);
         bool ok_run = true;
-        VS_PROF_T0();
         for (uint32_t i = 0; i < my_items && ok_run; ++i) {
             const uint32_t buf = i & 1u;
             const int v = (it.mt * kTileM + half * 128 + quarter * 32 + lane) % V;   // this lane's place in its vector-row
@@ -331,7 +321,6 @@ sddmm_dense_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_
             // warp-uniform outcome: tcgen05.ld below needs all 32 lanes
             ok_run = __all_sync(0xffffffffu, wait_or_abort<kSleepEpilogue>(bar_acc_full + 8 * buf, (i >> 1) & 1u, abort_flag));
             if (!ok_run) break;
-            VS_PROF_ADD(6);   // epilogue: bounds of the next item issued + wait for the accumulator
             tc::tc_fence_after_sync();
 #pragma unroll
             for (int c = 0; c < kChunksPerTile; ++c) {
@@ -346,7 +335,6 @@ sddmm_dense_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_
                         tc::tc_fence_before_sync();
                         tc::mbar_arrive(bar_acc_empty + 8 * buf);
                     }
-                    VS_PROF_ADD(7);   // epilogue: TMEM load
                     // The lane's 32 columns go to its row of the box and come back one entry at a time (no
                     // dynamic register indexing); no lane reads another lane's row, so nothing is synchronised.
                     box_write(r);
@@ -368,7 +356,6 @@ sddmm_dense_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_
                             }
                         }
                     }
-                    VS_PROF_ADD(8);   // epilogue: box + sampling
                 }
 #pragma unroll
                 for (int a = 0; a < kAhead; ++a) ent[a] = ent_next[a];
@@ -376,7 +363,6 @@ sddmm_dense_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_
 #pragma unroll
             for (int c = 0; c <= kChunksPerTile; ++c) off[c] = off_next[c];
         }
-        VS_PROF_FLUSH(6);
     }
 
     // ---- teardown ---------------------------------------------------------------------------------------

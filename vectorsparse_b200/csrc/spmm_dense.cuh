@@ -434,7 +434,6 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
         int p_e0 = 0, p_e1 = 0;            // the bucket this warp dropped into the slot last time
         uint32_t p_pos[kFillBatches] = {};
         bool ok_run = true;
-        VS_PROF_T0();
         for (uint32_t g = a_slot; g < total_stages && ok_run; g += kAStages) {
             const __half *vals = static_cast<const __half *>(p.values) + (int64_t)cur.b * p.stride_values;
             // values of the first 64 entries, entries of the next stage, bounds of the one after: all in flight
@@ -458,8 +457,6 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                 ok_run = wait_or_abort<kSleepFill>(bar_empty + 8 * (prev % kBStages), (prev / kBStages) & 1u, abort_flag);
             }
             if (!ok_run) break;
-            if (bucket == 0 && lane == 0) VS_TRACE(0, g);   // A slot free
-            VS_PROF_ADD(0);   // fill: prefetch issue + wait for the slot
             // The A slots start out as zeros; a slot is brought back to zeros by overwriting exactly the vectors
             // this warp dropped into it for the stage before (kAStages earlier), which costs a few stores
             // instead of 8 KiB of them: shared-memory bandwidth is what bounds this kernel.
@@ -481,7 +478,6 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                 }
             }
             __syncwarp();
-            VS_PROF_ADD(1);   // fill: clear the previous stage's vectors
 #pragma unroll
             for (int u = 0; u < kFillBatches; ++u)
                 if (c_e0 + lane + 32 * u < c_e1) scatter_vector<V, kTransposed>(a_part, c_ent[u].y, c_val[u].raw);
@@ -507,16 +503,12 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
             tc::fence_proxy_async();   // the tile was written by ordinary stores; the MMA reads through the async proxy
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(bar_full + 8 * (g % kBStages));
-            if (bucket == 0 && lane == 0) VS_TRACE(1, g);   // A part filled
-            if (bucket > 0 && lane == 0) VS_TRACE(9 + bucket, g);
 
             cur = nxt; c_e0 = n_e0; c_e1 = n_e1;
 #pragma unroll
             for (int u = 0; u < kFillBatches; ++u) c_ent[u] = n_ent[u];
             nxt = nn; n_e0 = nn_e0; n_e1 = nn_e1;
-            VS_PROF_ADD(2);   // fill: scatter, arrive
         }
-        VS_PROF_FLUSH(0);
     } else if (warp == kLoadWarp) {
         // =========================== B loader ============================================================
         // One thread keeps up to kBStages tiles of B in flight: one 64 x 64 box per 64 columns of the item.
@@ -535,7 +527,6 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                         ok_run = wait_or_abort<kSleepFill>(bar_empty + 8 * slot, ((g / kBStages) - 1u) & 1u, abort_flag);
                     if (!ok_run) break;
                     const uint32_t bar = bar_full + 8 * slot;
-                    VS_TRACE(2, g);   // B slot free, loads issued
                     tc::mbar_expect_tx(bar, (uint32_t)slabs * kBSlabBytes);   // arrives and arms the byte count
                     if (use_b4 && slabs == kTileN / 64) {   // both boxes with one instruction
                         tc::tma_load_4d(base + Smem::kB + slot * kBStageBytes, &map_b4, bar, 0, kb * kBlockK, it.n0 >> 6, it.b);
@@ -595,7 +586,6 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
             const uint32_t b_hi = tc::smem_desc_hi(1024, (uint32_t)tc::kSwizzle128B);
             uint32_t a_slot = 0, b_slot = 0, b_parity = 0;
             bool ok_run = true;
-            VS_PROF_T0();
             ItemIter items;
             items.init(m_tiles, n_tiles, p.N);
             bool ready = false;   // whether the next stage was already seen full
@@ -603,19 +593,13 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                 const Item it = items.get();
                 const uint32_t idesc = tc::make_idesc_f16(128, it.tn, 1, 1);   // both operands MN-major
                 const uint32_t buf = i & 1u;
-                if (warp == kMmaWarp) VS_TRACE(8, i);   // item start
                 ok_run = wait_or_abort<kSleepMma>(bar_acc_empty + 8 * buf, (i >> 1) & 1u, abort_flag);   // zeroed and free
-                if (warp == kMmaWarp) VS_TRACE(9, i);   // accumulator free
                 tc::tc_fence_after_sync();
                 const uint32_t d = tmem_base + buf * kAccCols + (uint32_t)h * kTileN;
-                VS_PROF_ADD(3);   // mma: item decode + wait for the accumulator
                 int k_left = p.K - 16 * kSteps * j;   // columns of A from this thread's first K step on
                 for (int kb = 0; kb < k_blocks && ok_run; ++kb, k_left -= kBlockK) {
-                    if (warp == kMmaWarp) VS_TRACE(3, i * k_blocks + kb);   // issuer starts waiting for the stage
                     if (!ready) ok_run = wait_or_abort<kSleepMma>(bar_full + 8 * b_slot, b_parity, abort_flag);
                     if (!ok_run) break;
-                    if (warp == kMmaWarp) VS_TRACE(4, i * k_blocks + kb);   // stage full
-                    VS_PROF_ADD(4);   // mma: wait for the stage
                     tc::tc_fence_after_sync();
                     const uint32_t a_lo = a_lo0 + a_slot * (kAStageBytes >> 4), b_lo = b_lo0 + b_slot * (kBStageBytes >> 4);
                     // 16 columns of A = 16 rows of B = 2 KiB further on in either operand
@@ -625,17 +609,14 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                             tc::mma_f16_ss(d, tc::desc64(a_lo + 128 * kk, a_hi), tc::desc64(b_lo + 128 * kk, b_hi), idesc,
                                            (kZeroedAcc || kb > 0 || kk > 0) ? 1u : 0u);
                     tc::mma_commit(bar_empty + 8 * b_slot);
-                    if (warp == kMmaWarp) VS_TRACE(5, i * k_blocks + kb);   // MMAs and commit issued
                     if (++a_slot == (uint32_t)kAStages) a_slot = 0;
                     if (++b_slot == (uint32_t)kBStages) { b_slot = 0; b_parity ^= 1u; }
                     // one look at the next stage's barrier (this CTA's stages follow one another across items):
                     // its latency passes while the MMAs above are handed to the pipe
                     ready = (kb + 1 < k_blocks || i + 1 < my_items) && tc::mbar_try_wait(bar_full + 8 * b_slot, b_parity);
-                    VS_PROF_ADD(5);   // mma: issue
                 }
                 if (ok_run) tc::mma_commit(bar_acc_full + 8 * buf);
             }
-            VS_PROF_FLUSH(3);
         }
     } else {
         // =========================== epilogue ============================================================
@@ -666,7 +647,6 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
         tc::tc_fence_before_sync();
         tc::mbar_arrive(bar_acc_empty);
         tc::mbar_arrive(bar_acc_empty + 8);
-        VS_PROF_T0();
         ItemIter items;
         items.init(m_tiles, n_tiles, p.N);
         for (uint32_t i = 0; i < my_items && ok_run; ++i, items.next()) {
@@ -675,8 +655,6 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
             // warp-uniform outcome: tcgen05.ld below needs all 32 lanes
             ok_run = __all_sync(0xffffffffu, wait_or_abort<kSleepEpilogue>(bar_acc_full + 8 * buf, (i >> 1) & 1u, abort_flag));
             if (!ok_run) break;
-            if (t == 0) VS_TRACE(6, i);   // accumulator complete
-            VS_PROF_ADD(6);   // epilogue: wait for the accumulator
             tc::tc_fence_after_sync();
             const int row0 = it.mt * kTileM + half * 128 + quarter * 32;   // first row of this warp's boxes
 #pragma unroll 1
@@ -685,7 +663,6 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                 const uint32_t taddr = lane_taddr + buf * kAccCols + (uint32_t)c0;
                 tc::tmem_ld_x32(taddr, r);
                 if (kZeroedAcc) tc::tmem_st_zero_x32(taddr);
-                VS_PROF_ADD(7);
                 if (row0 < m_rows && it.n0 + c0 < p.N) {   // warp-uniform
                     // x * 0 is 0 for a finite x and NaN otherwise: one FMA per element finds a non-finite sum
                     // (every column of the box was written by the MMA: columns past N multiply zero-filled B)
@@ -717,15 +694,12 @@ spmm_dense_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b,
                         tc::bulk_commit_group();
                     }
                     ++box_count;
-                    VS_PROF_ADD(8);
                 }
             }
             if (kZeroedAcc) tc::tmem_st_wait();
             tc::tc_fence_before_sync();
             tc::mbar_arrive(bar_acc_empty + 8 * buf);   // read out (and zeroed): the buffer is free
-            if (t == 0) VS_TRACE(7, i);   // accumulator released
         }
-        VS_PROF_FLUSH(6);
         // A zero of the densified tile times an Inf or NaN of B is a NaN that the reference, which only reads
         // the rows of B its nonzeros name, would not produce.  Any non-finite sum hands the call to the gather
         // kernel enqueued behind this one, which then overwrites the output.

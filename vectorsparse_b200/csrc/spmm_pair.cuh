@@ -15,25 +15,29 @@
 //
 // Organisation per CTA (both CTAs of a pair run the same roles on their own halves):
 //   warps 0-7    epilogue: own 128 accumulator lanes -> registers -> swizzled boxes -> TMA stores of whole rows
-//   warps 8-23   fill: two warps per A slot (eight slots), each owning 128 rows x 32 columns (two plan buckets) of the
-//                stage: from "stage multiplied" to "slot refilled and seen by the issuing thread" takes ~3000 cycles
-//                (commit, wake-up, stores, proxy fence, arrival through the other SM), the issuing thread wants a
-//                stage every ~500, so the ring of A tiles is the deep one
-//   warp 24      one thread issuing the CTA's B loads, four stages ahead
-//   warp 25      L2 prefetch of the next item's part of B (plain prefetches, paced by the loader), so that the tile
-//                loads hit L2 and a short ring of B tiles is enough
-//   warps 26-27  first CTA: the MMA-issuing threads of the pair (two for 256-column items, each issuing N = 128 MMAs
-//                into its own half of the accumulator columns; one for 128-column items); second CTA: the thread that
-//                forwards "my B tile has landed" to the first CTA's barrier
-//   warp 28      first CTA: the thread that forwards "stage multiplied" and "accumulator complete" to the second
-//                CTA's barriers (the issuing thread's time per stage is the pace of the pair: four MMAs and ONE
-//                commit, not one commit per CTA)
-// Barriers, one set per stage in flight.  full[s] (first CTA): the fill warps of BOTH CTAs, its loader + the bytes of its B
-// tile, the forwarded "landed" of the second CTA, whose own full[s] only collects its loader + bytes.  done[s] and
-// acc_full[b]: a tcgen05.commit in the first CTA, the forwarded arrival in the second.  acc_empty[b] (first CTA):
+//   warps 8-19   fill: two warps per A slot (six slots), each owning 128 rows x 32 columns (two plan buckets) of the
+//                stage; what a stage needs from global memory is requested right after the previous one was handed over
+//   warp 20      one thread issuing the CTA's B loads, six stages ahead: the ring of B tiles is what hides the latency
+//                of L2 and HBM (an L2 prefetch warp beside it, as the single-CTA kernel has, made this kernel slower)
+//   warp 21      first CTA: the MMA-issuing thread of the pair; second CTA: the thread that forwards "my B tile has
+//                landed" to the first CTA's barrier
+//   warp 22      first CTA: the thread that forwards "stage multiplied" and "accumulator complete" to the second
+//                CTA's barriers (a second commit per stage, addressed to the other CTA, works as well but costs the
+//                issuing thread ~105 cycles per stage: measured 3 % slower)
+// Barriers, one set per stage in flight.  full[s] (first CTA): the fill warps of BOTH CTAs, its loader + the bytes of
+// its B tile, the forwarded "landed" of the second CTA, whose own full[s] only collects its loader + bytes.  done[s]
+// and acc_full[b]: a tcgen05.commit in the first CTA, the forwarded arrival in the second.  acc_empty[b] (first CTA):
 // every epilogue thread of both CTAs.  Every wait is bounded; a wait that runs out raises the abort flag of both
 // CTAs, all roles fall through, a status bit is set, both CTAs meet at the final cluster barrier and tensor memory
 // is freed.
+//
+// What was measured on the way (B200, 148 SMs, ~1.5 GHz under the power cap while this kernel runs): a pair MMA of
+// N = 256 occupies the pipe for ~135 cycles (N = 128: ~71); one thread issues them back to back every ~52 cycles, a
+// commit costs it ~105.  A remote mbarrier arrive with cluster-scope release costs ~1100 cycles, the default form a
+// few tens.  Two issuing threads splitting the columns (N = 128 each) read A twice and were slower; walking the
+// issue loop with the whole warp was slower; rings of 4 + 8, 5 + 7, 6 + 6 (A + B) stages are within 3 % of each other.
+// With the fill, the B loads and the output stores switched off in turn the kernel gains 20, 15 and 23 us of its
+// 115; with all three off it takes 77 us, which is the tensor pipe's time for the dense work at that clock.
 #pragma once
 #include <cuda.h>
 
@@ -54,30 +58,9 @@ using densespmm::ValueVec;
 constexpr int kTileM = 256;                               // rows of A per work item: 128 per CTA of the pair
 constexpr int kCtaRows = 128;
 constexpr int kMaxTileN = 256;                            // columns of B per work item: 256, or 128 when N % 256 != 0
-#ifndef VS_PAIR_ASTAGES
-#define VS_PAIR_ASTAGES 6
-#endif
-#ifndef VS_PAIR_BSTAGES
-#define VS_PAIR_BSTAGES 6
-#endif
-#ifndef VS_PAIR_FILLCOLS
-#define VS_PAIR_FILLCOLS 32
-#endif
-#ifndef VS_PAIR_SLEEP
-#define VS_PAIR_SLEEP VS_DENSE_SLEEP
-#endif
-#ifndef VS_PAIR_ISSUERS
-#define VS_PAIR_ISSUERS 1
-#endif
-#ifndef VS_PAIR_WARP_ISSUE
-#define VS_PAIR_WARP_ISSUE 0
-#endif
-#ifndef VS_PAIR_REMOTE_COMMIT
-#define VS_PAIR_REMOTE_COMMIT 0
-#endif
-constexpr int kAStages = VS_PAIR_ASTAGES;                 // ring of densified A tiles (filled on chip: short latency)
-constexpr int kBStages = VS_PAIR_BSTAGES;                 // ring of B tiles (loaded from L2 / HBM: that many stages ahead)
-constexpr int kFillCols = VS_PAIR_FILLCOLS;               // columns of a stage one fill warp owns: one or two plan buckets
+constexpr int kAStages = 6;                               // ring of densified A tiles
+constexpr int kBStages = 6;                               // ring of B tiles: loaded that many stages ahead
+constexpr int kFillCols = 32;                             // columns of a stage one fill warp owns: two plan buckets
 constexpr int kEpiWarps = 8;                              // TMEM lane quarter = warp % 4, half of the columns = warp / 4
 constexpr int kFillWarp0 = kEpiWarps;
 constexpr int kFillPerSlot = kBlockK / kFillCols;         // warps per CTA and stage
@@ -85,10 +68,8 @@ constexpr int kFillWarps = kAStages * kFillPerSlot;       // 16: warp f fills A 
 constexpr int kFillBatches = 2;                           // batches of 32 entries a fill warp keeps in flight
 constexpr int kOverflowBatches = 4;
 constexpr int kLoadWarp = kFillWarp0 + kFillWarps;        // 24
-constexpr int kPrefetchWarp = kLoadWarp + 1;              // 25
-constexpr int kMmaWarp = kPrefetchWarp + 1;
-constexpr int kMmaWarps = VS_PAIR_ISSUERS;                // issuing threads of the first CTA
-constexpr int kForwardWarp = kMmaWarp + kMmaWarps;
+constexpr int kMmaWarp = kLoadWarp + 1;
+constexpr int kForwardWarp = kMmaWarp + 1;
 constexpr int kThreads = (kForwardWarp + 1) * 32;
 static_assert(kThreads <= 1024, "too many fill warps for one CTA");
 constexpr int kAStageBytes = kCtaRows * kBlockK * 2;      // 16 KiB
@@ -109,8 +90,7 @@ struct Smem {  // offsets from the 1024-byte aligned base; identical in both CTA
     static constexpr int kBarAccEmpty = kBarAccFull + 2 * 8;
     static constexpr int kTmemHolder = kBarAccEmpty + 2 * 8;
     static constexpr int kAbort = kTmemHolder + 8;
-    static constexpr int kLoaderProgress = kAbort + 8;      // stages whose B loads have been issued
-    static constexpr int kTotal = kLoaderProgress + 8;
+    static constexpr int kTotal = kAbort + 8;
 };
 constexpr int kSmemBytes = Smem::kTotal + 1024;
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
@@ -133,7 +113,7 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
     abort_pair(abort_flag, abort_addr, peer);
     return false;
 }
-constexpr int kSleepFill = VS_PAIR_SLEEP, kSleepMma = 0, kSleepEpilogue = VS_PAIR_SLEEP;
+constexpr int kSleepFill = VS_DENSE_SLEEP, kSleepMma = 0, kSleepEpilogue = VS_DENSE_SLEEP;
 
 // Work items of one pair, c, c + pairs, c + 2 pairs, ...: item w -> (batch entry, column tile, row tile), row tiles
 // fastest, so that neighbouring pairs work on the same B.  Walked without divisions per step.
@@ -183,9 +163,6 @@ spmm_pair_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b, 
                  int plan_checks) {
     pdl_launch_dependents();
     pdl_wait();
-#ifdef VS_TC_PROFILE
-    const long long kernel_t0 = clock64();
-#endif
     const bool chosen = plan_dense_chosen(use_dense, plan_checks);
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = tc::smem_u32(smem_raw);
@@ -212,14 +189,13 @@ spmm_pair_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b, 
             // first CTA: the fill warps of both CTAs, its loader (+ the bytes of its B tile), the second CTA's "B landed";
             // second CTA: its loader (+ bytes) only, watched by its forwarding thread
             tc::mbar_init(bar_full + 8 * s, rank == 0 ? 2 * kFillPerSlot + 2 : 1);
-            tc::mbar_init(bar_done + 8 * s, rank == 0 ? (VS_PAIR_ISSUERS == 2 && tn == 256 ? 2 : 1) : 1);   // first CTA: one commit per issuing thread; second: the forwarded arrival
+            tc::mbar_init(bar_done + 8 * s, 1);   // first CTA: the commit; second CTA: the forwarded arrival
         }
         for (int s = 0; s < 2; ++s) {
-            tc::mbar_init(bar_acc_full + 8 * s, rank == 0 ? (VS_PAIR_ISSUERS == 2 && tn == 256 ? 2 : 1) : 1);
+            tc::mbar_init(bar_acc_full + 8 * s, 1);
             tc::mbar_init(bar_acc_empty + 8 * s, 2 * kEpiWarps * 32);   // used in the first CTA only
         }
         *abort_flag = 0;
-        *reinterpret_cast<volatile uint32_t *>(sm + Smem::kLoaderProgress) = 0;
         tc::fence_mbar_init();
     }
     if (warp == kMmaWarp) {
@@ -230,7 +206,6 @@ spmm_pair_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b, 
     tc::tc_fence_before_sync();
     tc::cluster_sync();   // barriers, flags and zeroed slots of BOTH CTAs exist before anything crosses between them
     tc::tc_fence_after_sync();
-    if (t == 0) { VS_TRACE_B(0, 14, 0u); VS_TRACE_B(1, 15, 0u); }
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(sm + Smem::kTmemHolder);
 
     const int64_t total_items = chosen ? (int64_t)p.batch * n_tiles * m_tiles : 0;
@@ -239,14 +214,6 @@ spmm_pair_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b, 
     const int m_rows = kTransposed ? p.m_vec : p.m_vec * V;
     const int half_cols = tn >> 1;              // columns of B this CTA holds per item
     const int slabs = half_cols >> 6;           // 64-column slabs of them: 2 or 1
-    // Issuing threads.  One thread gets a pair MMA into the pipe every ~105 cycles whatever its size (measured: the
-    // same time per stage at N = 128 as at N = 256), so a single thread issuing 256-column MMAs keeps the tensor
-    // pipe half idle.  With 256-column items two threads each take one 64-column slab of both CTAs' halves
-    // (N = 128 per MMA) into their own half of the accumulator columns: twice the issue rate, and every sum is still
-    // accumulated by one thread in one order.  Accumulator column c of thread j then holds output column
-    // (c / 64) * 128 + 64 j + c % 64 of the item.
-    const int issuers = VS_PAIR_ISSUERS == 2 ? slabs : 1;   // 2 only for 256-column items
-    const int issuer_cols = tn / issuers;       // accumulator columns per issuing thread (128)
 
     // Stage g of the pair (item g / k_blocks, column block g % k_blocks) uses A slot g % kAStages, B slot
     // g % kBStages and barrier set g % kBarStages.  done[g % kBarStages] completing phase g / kBarStages says "stage g
@@ -309,15 +276,12 @@ spmm_pair_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b, 
         int p_e0 = 0, p_e1 = 0;
         uint32_t p_pos[kFillBatches] = {};
         bool ok_run = true;
-        VS_PROF_T0();
         for (uint32_t g = a_slot; g < total_stages && ok_run; g += kAStages) {
             if (g >= (uint32_t)kAStages) {   // the stage that used this A slot before must have been multiplied
                 const uint32_t prev = g - kAStages;
                 ok_run = wait_or_abort<kSleepFill>(bar_done + 8 * (prev % kBarStages), (prev / kBarStages) & 1u, abort_flag, abort_addr, peer);
             }
             if (!ok_run) break;
-            VS_PROF_ADD(0);   // fill: wait for the slot
-            if (quarter_k == 0 && lane == 0) { VS_TRACE_B(0, 0, g); VS_TRACE_B(1, 10, g); }
             {   // back to zeros: overwrite exactly the vectors this warp dropped into the slot last time
                 typename ValueVec<V>::Raw zero{};
 #pragma unroll
@@ -336,8 +300,6 @@ spmm_pair_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b, 
                 }
             }
             __syncwarp();
-            VS_PROF_ADD(1);   // fill: clear
-            if (quarter_k == 0 && lane == 0) VS_TRACE_B(0, 6, g);
 #pragma unroll
             for (int u = 0; u < kFillBatches; ++u)
                 if (c_e0 + kStride * u < c_e1) scatter_vector<V, kTransposed>(a_part, c_ent[u].y, c_val[u].raw);
@@ -362,12 +324,9 @@ spmm_pair_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b, 
             p_e0 = c_e0; p_e1 = c_e1;
 #pragma unroll
             for (int u = 0; u < kFillBatches; ++u) p_pos[u] = c_ent[u].y;
-            if (quarter_k == 0 && lane == 0) VS_TRACE_B(0, 7, g);
             tc::fence_proxy_async();   // ordinary stores; the MMA reads through the async proxy
-            if (quarter_k == 0 && lane == 0) VS_TRACE_B(0, 9, g);
             __syncwarp();
             if (lane == 0) tc::mbar_arrive_remote(full_first + 8 * (g % kBarStages));
-            if (quarter_k == 0 && lane == 0) { VS_TRACE_B(0, 1, g); VS_TRACE_B(1, 11, g); }
 
             // the next stage of this warp: its values, the entries of the one after, the bounds of the one after that
             c_e0 = n_e0; c_e1 = n_e1; c_b = n_b;
@@ -386,9 +345,7 @@ spmm_pair_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b, 
                 n_ent[u] = e < n_e1 ? __ldg(blk_entries + e) : make_uint2(0u, 0u);
             }
             { const Pos q = locate(); bounds(q, f_e0, f_e1); f_b = q.b; }
-            VS_PROF_ADD(2);   // fill: scatter + arrive + prefetch issue
         }
-        VS_PROF_FLUSH(0);
     } else if (warp == kLoadWarp) {
         // =========================== B loader ============================================================
         // This CTA's half of every B tile, up to kBStages stages ahead, into its own shared memory, completing on its
@@ -398,8 +355,6 @@ spmm_pair_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b, 
             bool ok_run = true;
             Walk walk;
             walk.init(pair, pairs, 0u, total_stages, m_tiles, n_tiles, k_blocks);
-            VS_PROF_T0();
-            volatile uint32_t *progress = reinterpret_cast<volatile uint32_t *>(sm + Smem::kLoaderProgress);
             for (uint32_t g = 0; g < total_stages && ok_run; ++g, walk.advance(1)) {
                 const uint32_t slot = g % kBStages;
                 if (g >= (uint32_t)kBStages) {   // the stage that used this B slot before must have been multiplied
@@ -407,7 +362,6 @@ spmm_pair_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b, 
                     ok_run = wait_or_abort<kSleepFill>(bar_done + 8 * (prev % kBarStages), (prev / kBarStages) & 1u, abort_flag, abort_addr, peer);
                 }
                 if (!ok_run) break;
-                VS_PROF_ADD(9);   // loader: wait for the slot
                 const uint32_t bar = bar_full + 8 * (g % kBarStages);
                 const int n0 = walk.nt * tn + (int)rank * half_cols;   // first column of this CTA's half
                 tc::mbar_expect_tx(bar, (uint32_t)slabs * kBSlabBytes);
@@ -416,122 +370,66 @@ spmm_pair_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b, 
                 } else {
                     tc::tma_load_3d(base + Smem::kB + slot * kBStageBytes, &map_b, bar, n0, walk.kb * kBlockK, walk.b);
                 }
-                *progress = g + 1;
-                VS_PROF_ADD(10);   // loader: issue
-                VS_TRACE_B(0, 2, g); VS_TRACE_B(1, 13, g);
             }
-            VS_PROF_FLUSH(9);
             const uint32_t tail0 = total_stages > (uint32_t)kBarStages ? total_stages - kBarStages : 0u;
             for (uint32_t g = tail0; g < total_stages && ok_run; ++g)
                 ok_run = wait_or_abort<kSleepFill>(bar_done + 8 * (g % kBarStages), (g / kBarStages) & 1u, abort_flag, abort_addr, peer);
         }
-    } else if (warp == kPrefetchWarp) {
-        // =========================== L2 prefetch =========================================================
-        // First touches of B come from HBM, a latency the short ring of B tiles does not cover, and prefetches through
-        // the TMA queue would hold up the loads queued behind them.  This warp asks each tile into L2 with plain
-        // prefetches about one work item before the loader wants it, paced by the loader's counter.
-        volatile uint32_t *progress = reinterpret_cast<volatile uint32_t *>(sm + Smem::kLoaderProgress);
-        const __half *rhs = static_cast<const __half *>(p.rhs);
-        bool ok_run = true;
-        Walk walk;
-        walk.init(pair, pairs, (uint32_t)k_blocks, total_stages, m_tiles, n_tiles, k_blocks);   // from the second item on
-        for (uint32_t g = (uint32_t)k_blocks; g < total_stages && ok_run; ++g, walk.advance(1)) {
-            const int32_t need = (int32_t)g - k_blocks - 2;   // at most an item and two stages ahead of the loader
-            uint32_t polls = 0;
-            while ((int32_t)*progress < need) {
-                __nanosleep(200);
-                if (++polls > (1u << 20) || *abort_flag) { ok_run = false; break; }
-            }
-            if (!ok_run) break;
-            const int n0 = walk.nt * tn + (int)rank * half_cols;
-            const __half *b_tile = rhs + (int64_t)walk.b * p.stride_rhs + n0;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {   // 64 rows x up to two 128-byte lines
-                const int r = walk.kb * kBlockK + lane * 2 + (j >> 1), c = (j & 1) * 64;
-                if (r < p.K && c < half_cols) asm volatile("prefetch.global.L2 [%0];" ::"l"(b_tile + (int64_t)r * p.N + c));
-            }
-        }
-    } else if (warp >= kMmaWarp && warp < kForwardWarp) {
-        const int j = warp - kMmaWarp;
-        if ((VS_PAIR_WARP_ISSUE || lane == 0) && rank == 0 && j < issuers) {
-            // =========================== MMA issuers of the pair =========================================
-            // The whole warp walks the loop and one lane issues: with warp-uniform control flow the descriptors and
-            // addresses can live in uniform registers, which is where the MMA instruction takes them from.
-            const bool issue = lane == 0;
+    } else if (warp == kMmaWarp) {
+        if (lane == 0 && rank == 0) {
+            // =========================== MMA issuer of the pair ==========================================
             const uint32_t a_lo0 = tc::smem_desc_lo(base + Smem::kA, 8192);   // 64-row atoms 8 KiB apart
             const uint32_t a_hi = tc::smem_desc_hi(1024, (uint32_t)tc::kSwizzle128B);
-            const uint32_t b_lo0 = tc::smem_desc_lo(base + Smem::kB + j * kBSlabBytes, kBSlabBytes);   // this thread's slab of each CTA's half
+            const uint32_t b_lo0 = tc::smem_desc_lo(base + Smem::kB, kBSlabBytes);   // 64-column slabs 8 KiB apart
             const uint32_t b_hi = tc::smem_desc_hi(1024, (uint32_t)tc::kSwizzle128B);
-            const uint32_t idesc = tc::make_idesc_f16(256, issuer_cols, 1, 1);   // both operands MN-major
-            // The loop below is the pace of the pair: per stage one barrier poll, four MMAs (~105 cycles of this
-            // thread each, whatever their size), one commit.  Nothing else is in it: no look ahead at the next
-            // barrier, no tensor-core fence per stage (the operands were written by TMA, or by stores that their
-            // writers fenced for the async proxy before arriving), the number of K steps known per block.
+            const uint32_t idesc = tc::make_idesc_f16(256, tn, 1, 1);   // both operands MN-major
+            // Per stage: one barrier poll, four MMAs, one commit.  No tensor-core fence per stage: the operands were
+            // written by TMA, or by stores that their writers fenced for the async proxy before arriving.
             uint32_t a_slot = 0, b_slot = 0, bar = 0, parity = 0;
             const int steps_last = ((p.K - 1) & (kBlockK - 1)) / 16 + 1;   // K steps of the last column block of A
             bool ok_run = true;
-            VS_PROF_T0();
             for (uint32_t i = 0; i < my_items && ok_run; ++i) {
                 const uint32_t buf = i & 1u;
                 ok_run = wait_or_abort<kSleepMma>(bar_acc_empty + 8 * buf, (i >> 1) & 1u, abort_flag, abort_addr, peer);
-                if (VS_PAIR_WARP_ISSUE) ok_run = __all_sync(0xffffffffu, ok_run);
                 if (!ok_run) break;
-                VS_PROF_ADD(3);   // mma: wait for the accumulator
                 tc::tc_fence_after_sync();
-                const uint32_t d = tmem_base + buf * kMaxTileN + (uint32_t)(j * issuer_cols);
+                const uint32_t d = tmem_base + buf * kMaxTileN;
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (j == 0 && issue) VS_TRACE_B(0, 3, i * k_blocks + kb);
                     ok_run = wait_or_abort<kSleepMma>(bar_full + 8 * bar, parity, abort_flag, abort_addr, peer);
-                    if (VS_PAIR_WARP_ISSUE) ok_run = __all_sync(0xffffffffu, ok_run);
                     if (!ok_run) break;
-                    VS_PROF_ADD(4);   // mma: wait for the stage
-                    if (j == 0 && issue) VS_TRACE_B(0, 4, i * k_blocks + kb);
                     const uint32_t a_lo = a_lo0 + a_slot * (kAStageBytes >> 4), b_lo = b_lo0 + b_slot * (kBStageBytes >> 4);
                     // 16 columns of A = 16 rows of B = 2 KiB further on in either operand
-                    if (issue) {
-                        if (kb + 1 < k_blocks || steps_last == kBlockK / 16) {
-                            tc::mma_f16_ss_pair(d, tc::desc64(a_lo, a_hi), tc::desc64(b_lo, b_hi), idesc, kb > 0 ? 1u : 0u);
-                            tc::mma_f16_ss_pair(d, tc::desc64(a_lo + 128, a_hi), tc::desc64(b_lo + 128, b_hi), idesc, 1u);
-                            tc::mma_f16_ss_pair(d, tc::desc64(a_lo + 256, a_hi), tc::desc64(b_lo + 256, b_hi), idesc, 1u);
-                            tc::mma_f16_ss_pair(d, tc::desc64(a_lo + 384, a_hi), tc::desc64(b_lo + 384, b_hi), idesc, 1u);
-                        } else {
-                            for (int kk = 0; kk < steps_last; ++kk)
-                                tc::mma_f16_ss_pair(d, tc::desc64(a_lo + 128 * kk, a_hi), tc::desc64(b_lo + 128 * kk, b_hi), idesc,
-                                                    (kb > 0 || kk > 0) ? 1u : 0u);
-                        }
-                        tc::mma_commit_pair(bar_done + 8 * bar);   // this CTA's barrier; the forwarding warp tells the other CTA
-                        if (VS_PAIR_REMOTE_COMMIT) tc::mma_commit_pair(tc::map_to_cta(bar_done, 1) + 8 * bar);
+                    if (kb + 1 < k_blocks || steps_last == kBlockK / 16) {
+                        tc::mma_f16_ss_pair(d, tc::desc64(a_lo, a_hi), tc::desc64(b_lo, b_hi), idesc, kb > 0 ? 1u : 0u);
+                        tc::mma_f16_ss_pair(d, tc::desc64(a_lo + 128, a_hi), tc::desc64(b_lo + 128, b_hi), idesc, 1u);
+                        tc::mma_f16_ss_pair(d, tc::desc64(a_lo + 256, a_hi), tc::desc64(b_lo + 256, b_hi), idesc, 1u);
+                        tc::mma_f16_ss_pair(d, tc::desc64(a_lo + 384, a_hi), tc::desc64(b_lo + 384, b_hi), idesc, 1u);
+                    } else {
+                        for (int kk = 0; kk < steps_last; ++kk)
+                            tc::mma_f16_ss_pair(d, tc::desc64(a_lo + 128 * kk, a_hi), tc::desc64(b_lo + 128 * kk, b_hi), idesc,
+                                                (kb > 0 || kk > 0) ? 1u : 0u);
                     }
-                    if (VS_PAIR_WARP_ISSUE) __syncwarp();
+                    tc::mma_commit_pair(bar_done + 8 * bar);   // this CTA's barrier; the forwarding warp tells the other CTA
                     if (++a_slot == (uint32_t)kAStages) a_slot = 0;
                     if (++b_slot == (uint32_t)kBStages) b_slot = 0;
                     if (++bar == (uint32_t)kBarStages) { bar = 0; parity ^= 1u; }
-                    VS_PROF_ADD(5);   // mma: issue + commit
-                    if (j == 0 && issue) VS_TRACE_B(0, 5, i * k_blocks + kb);
                 }
-                if (ok_run && issue) tc::mma_commit_pair(bar_acc_full + 8 * buf);
-                if (ok_run && issue && VS_PAIR_REMOTE_COMMIT) tc::mma_commit_pair(tc::map_to_cta(bar_acc_full, 1) + 8 * buf);
+                if (ok_run) tc::mma_commit_pair(bar_acc_full + 8 * buf);
             }
-            if (j == 0 && issue) VS_PROF_FLUSH(3);
-        } else if (lane == 0 && rank != 0 && j == 0) {
+        } else if (lane == 0 && rank != 0) {
             // =========================== second CTA: forward "my B tile has landed" =======================
             const uint32_t full_first = tc::map_to_cta(bar_full, 0);
             bool ok_run = true;
             uint32_t slot = 0, parity = 0;
-            VS_PROF_T0();
             for (uint32_t g = 0; g < total_stages && ok_run; ++g) {
                 ok_run = wait_or_abort<kSleepMma>(bar_full + 8 * slot, parity, abort_flag, abort_addr, peer);
                 if (!ok_run) break;
-                VS_PROF_ADD(12);   // forwarder: wait
-                VS_TRACE_B(1, 12, g);
                 tc::mbar_arrive_remote(full_first + 8 * slot);
                 if (++slot == (uint32_t)kBarStages) { slot = 0; parity ^= 1u; }
-                VS_PROF_ADD(13);   // forwarder: arrive
             }
-            VS_PROF_FLUSH(12);
         }
     } else if (warp == kForwardWarp) {
-        if (lane == 0 && rank == 0 && !VS_PAIR_REMOTE_COMMIT) {
+        if (lane == 0 && rank == 0) {
             // =========================== first CTA: forward "multiplied" and "accumulator complete" =======
             const uint32_t done_there = tc::map_to_cta(bar_done, 1), accf_there = tc::map_to_cta(bar_acc_full, 1);
             bool ok_run = true;
@@ -540,7 +438,6 @@ spmm_pair_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b, 
                 for (int kb = 0; kb < k_blocks && ok_run; ++kb) {
                     ok_run = wait_or_abort<kSleepMma>(bar_done + 8 * slot, parity, abort_flag, abort_addr, peer);
                     if (!ok_run) break;
-                    VS_TRACE_B(0, 8, i * k_blocks + kb);
                     tc::mbar_arrive_remote(done_there + 8 * slot);
                     if (++slot == (uint32_t)kBarStages) { slot = 0; parity ^= 1u; }
                 }
@@ -572,20 +469,18 @@ spmm_pair_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b, 
         tc::mbar_arrive_remote(acc_empty_first + 8);
         Walk walk;
         walk.init(pair, pairs, 0u, my_items, m_tiles, n_tiles, 1);
-        VS_PROF_T0();
         for (uint32_t i = 0; i < my_items && ok_run; ++i, walk.advance(1)) {
             const uint32_t buf = i & 1u;
             ok_run = __all_sync(0xffffffffu, wait_or_abort<kSleepEpilogue>(bar_acc_full + 8 * buf, (i >> 1) & 1u, abort_flag, abort_addr, peer));
             if (!ok_run) break;
-            VS_PROF_ADD(6);   // epilogue: wait for the accumulator
 
             tc::tc_fence_after_sync();
             const int row0 = walk.mt * kTileM + (int)rank * kCtaRows + quarter * 32;
+            const int col0 = walk.nt * tn + half * half_cols;   // accumulator column c of the item is its output column c
 #pragma unroll 1
             for (int c0 = 0; c0 < half_cols; c0 += kStoreCols) {
                 uint32_t r[kStoreCols];
                 tc::tmem_ld_x32(lane_taddr + buf * kMaxTileN + (uint32_t)c0, r);
-                VS_PROF_ADD(7);   // epilogue: tensor-memory load
                 if (row0 < m_rows) {   // warp-uniform
                     if (row0 + lane < m_rows) {
 #pragma unroll
@@ -611,22 +506,16 @@ spmm_pair_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b, 
                     tc::fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) {
-                        // accumulator column -> output column: which issuing thread wrote it, which CTA's half of B it
-                        // multiplied, where inside that thread's slab
-                        const int tcol = half * half_cols + c0, within = tcol % issuer_cols, slab_cols = issuer_cols >> 1;
-                        const int col = walk.nt * tn + (within / slab_cols) * half_cols + (tcol / issuer_cols) * slab_cols + within % slab_cols;
-                        tc::tma_store_3d(&map_out, stg_u32 + box * kBoxBytes, col, row0, walk.b);
+                        tc::tma_store_3d(&map_out, stg_u32 + box * kBoxBytes, col0 + c0, row0, walk.b);
                         tc::bulk_commit_group();
                     }
                     ++box_count;
-                    VS_PROF_ADD(8);   // epilogue: convert, stage, store
                 }
             }
             tc::tc_fence_before_sync();
             tc::mbar_arrive_remote(acc_empty_first + 8 * buf);   // read out: the buffer is free for the pair
 
         }
-        VS_PROF_FLUSH(6);
         if (lane == 0) tc::bulk_wait_group<0>();
         const float probe = (finite_probe[0] + finite_probe[1]) + (finite_probe[2] + finite_probe[3]);
         if (__any_sync(0xffffffffu, probe != 0.0f) && lane == 0) atomicExch(use_dense, 0);
@@ -641,9 +530,6 @@ spmm_pair_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b, 
     }
     tc::cluster_sync();   // neither CTA's shared or tensor memory goes away while the other half of an MMA may use it
     if (warp == kMmaWarp) tc::tmem_dealloc_pair(tmem_base, kTmemCols);
-#ifdef VS_TC_PROFILE
-    if (t == 0 && blockIdx.x == 0) g_prof[15] = (unsigned long long)(clock64() - kernel_t0);
-#endif
 }
 
 }  // namespace pairspmm

@@ -253,16 +253,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) spmm_tc_kernel(const Spm
             uint32_t g = g_stage + (uint32_t)s0;
             int n = 0;
             bool ok_run = true;
-            VS_PROF_T0();
             while (cur.valid() && ok_run) {
                 if (g >= (uint32_t)kStages) ok_run = wait_or_abort<kSleepProducer>(bar_empty + 8 * slot, ((g / kStages) - 1u) & 1u, abort_flag);
                 if (!ok_run) break;
-                VS_PROF_ADD(0);   // producer: wait for the slot
                 // this stage's indices were fetched two of this warp's stages ago: at most the newest cp.async
                 // group may still be pending; the warp barrier publishes the landed indices to all lanes
                 tc::cp_async_wait<1>();
                 __syncwarp();
-                VS_PROF_ADD(1);   // producer: wait for indices
                 const int q = cur.q;
                 const int b = l_b[q];
                 const int n0 = l_n0[q];
@@ -275,11 +272,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) spmm_tc_kernel(const Spm
                 const int *idx = ring + (n % kIdxRing) * kStageNnz + h;
 #pragma unroll
                 for (int i = 0; i < kStageNnz / 2; ++i) {
-#ifdef VS_EXP_NOCOPY
-                    if (false) {
-#else
                     if (i < 8 * n_mma) {   // rows h + 2i of MMA (i >> 3)
-#endif
                         const bool ok = col_ok && (h + 2 * i) < nnz;
                         const __half *src = ok ? rhs_t + (int64_t)idx[2 * i] * p.N : rhs;
                         tc::cp_async_16(a_base + x[i & 3] + (i >> 2) * 1024, src, ok ? 16u : 0u);
@@ -311,10 +304,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) spmm_tc_kernel(const Spm
                 cur.advance(kStages);
                 g += kStages;
                 ++n;
-                VS_PROF_ADD(2);   // producer: issue
             }
             tc::cp_async_wait<0>();
-            VS_PROF_FLUSH(0);
         } else if (warp < kEpiWarp0) {
             // =========================== MMA issuers (even / odd items) ====================================
             // One issuing thread for all stages, in ring order: an mbarrier parity wait is only safe for a
@@ -327,7 +318,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) spmm_tc_kernel(const Spm
                 const uint32_t b_hi = tc::smem_desc_hi(kVStageBytes / 2, (uint32_t)tc::kSwizzleNone);
                 uint32_t g = g_stage, ic = g_item;
                 bool ok_run = true;
-                VS_PROF_T0();
                 for (int q = 0; q < cnt && ok_run; ++q, ++ic) {
                     int rem = l_end[q] - l_j0[q];
                     const uint32_t acc = ic % kAccSlots;
@@ -335,28 +325,17 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) spmm_tc_kernel(const Spm
                         ok_run = wait_or_abort<kSleepMma>(bar_acc_empty + 8 * acc, ((ic / kAccSlots) - 1u) & 1u, abort_flag);
                     const uint32_t d = tmem_base + acc * kAccCols;
                     uint32_t accumulate = 0;
-                    VS_PROF_ADD(3);   // mma: wait for a free accumulator (+ item bookkeeping)
                     do {
                         const uint32_t slot = g % kStages;
                         if (ok_run) ok_run = wait_or_abort<kSleepMma>(bar_full + 8 * slot, (g / kStages) & 1u, abort_flag);
                         if (!ok_run) break;
-                        VS_PROF_ADD(4);   // mma: wait for a full stage
-#ifndef VS_EXP_NOFENCE
                         tc::fence_proxy_async();
-#endif
                         tc::tc_fence_after_sync();
                         const int n_mma = rem >= kStageNnz ? kMmaPerStage : max(1, (rem + 15) >> 4);
                         const uint32_t a_lo = a_lo0 + slot * (kAStageBytes >> 4);
                         const uint32_t b_lo = b_lo0 + slot * (kVStageBytes >> 4);
-#ifdef VS_EXP_NOMMA
-                        if (false)
-#endif
                         tc::mma_f16_ss(d, tc::desc64(a_lo, a_hi), tc::desc64(b_lo, b_hi), kIdesc, accumulate);
-#ifdef VS_EXP_NOMMA
-                        if (false) {
-#else
                         {
-#endif
                         if (n_mma > 1) tc::mma_f16_ss(d, tc::desc64(a_lo + 128, a_hi), tc::desc64(b_lo + 16, b_hi), kIdesc, 1u);
                         if (kMmaPerStage > 2 && n_mma > 2) tc::mma_f16_ss(d, tc::desc64(a_lo + 256, a_hi), tc::desc64(b_lo + 32, b_hi), kIdesc, 1u);
                         if (kMmaPerStage > 3 && n_mma > 3) tc::mma_f16_ss(d, tc::desc64(a_lo + 384, a_hi), tc::desc64(b_lo + 48, b_hi), kIdesc, 1u);
@@ -365,11 +344,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) spmm_tc_kernel(const Spm
                         accumulate = 1;
                         rem -= kStageNnz;
                         ++g;
-                        VS_PROF_ADD(5);   // mma: issue
                     } while (rem > 0);
                     if (ok_run) tc::mma_commit(bar_acc_full + 8 * acc);
                 }
-                VS_PROF_FLUSH(3);
             }
         } else {
             // =========================== epilogue (even / odd items) ========================================
@@ -377,14 +354,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) spmm_tc_kernel(const Spm
             const int ew = warp - kEpiWarp0;              // 0..3
             uint8_t *stg = sm + Smem::kStaging + ew * kStagingBytes;
             bool ok_run = true;
-            VS_PROF_T0();
             for (int q = 0; q < cnt && ok_run; ++q) {
                 const uint32_t ic = g_item + (uint32_t)q;
                 const uint32_t acc = ic % kAccSlots;
                 // warp-uniform outcome: tcgen05.ld below needs all 32 lanes
                 ok_run = __all_sync(0xffffffffu, wait_or_abort<kSleepEpilogue>(bar_acc_full + 8 * acc, (ic / kAccSlots) & 1u, abort_flag));
                 if (!ok_run) break;
-                VS_PROF_ADD(6);   // epilogue: wait for the accumulator
                 tc::tc_fence_after_sync();
                 uint32_t r[8];
                 tc::tmem_ld_x8(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kAccCols, r);
@@ -412,9 +387,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) spmm_tc_kernel(const Spm
                         }
                     }
                 }
-                VS_PROF_ADD(7);   // epilogue: load, transpose, store
             }
-            VS_PROF_FLUSH(6);
         }
 
         // ---- phase end: everybody is done with the lists; advance the global counters identically ------------

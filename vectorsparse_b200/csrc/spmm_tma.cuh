@@ -269,7 +269,6 @@ spmm_tma_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map, int
             uint32_t g = g_stage + (uint32_t)s0;
             int n = 0;
             bool ok_run = true;
-            VS_PROF_T0();
             while (pq[0] < cnt && ok_run) {
                 const uint32_t slot = g % kStages;
                 if (g >= (uint32_t)kStages)
@@ -296,7 +295,6 @@ spmm_tma_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map, int
                     if (kBulkValues && nnz > 0) tc::bulk_copy_g2s(v_base, vals + (int64_t)j * V, (uint32_t)nnz * 16u, bar);
                 }
                 __syncwarp();                                  // indices in shared memory, byte count armed
-                VS_PROF_ADD(0);   // producer: waits + stage set-up
                 if (grp < 4 * n_mma && (half == 0 || two_halves)) {
                     const int4 c = *reinterpret_cast<const int4 *>(my_ring + 4 * grp);
                     const int row0 = b * rows_per_batch;
@@ -306,7 +304,6 @@ spmm_tma_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map, int
                                     e + 0 < nnz ? row0 + c.x : total_rows, e + 1 < nnz ? row0 + c.y : total_rows,
                                     e + 2 < nnz ? row0 + c.z : total_rows, e + 3 < nnz ? row0 + c.w : total_rows);
                 }
-                VS_PROF_ADD(1);   // producer: gather issue
                 if constexpr (kBulkValues) {
                     // value slots between the row's end and the end of the last MMA must read as zeros
 #pragma unroll
@@ -341,10 +338,8 @@ spmm_tma_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map, int
                 it.advance(kProducerWarps);
                 g += kProducerWarps;
                 ++n;
-                VS_PROF_ADD(2);   // producer: values, look-ahead
             }
             tc::cp_async_wait<0>();
-            VS_PROF_FLUSH(0);
         } else if (warp >= kMmaWarp) {
             // =========================== MMA issuers =======================================================
             // Two issuing threads share the work by item parity (a tcgen05.mma costs its issuing thread ~64
@@ -367,7 +362,6 @@ spmm_tma_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map, int
                 uint32_t item_parity = g_item & 1u;
                 bool ok_run = true;
                 int len = l_end[0] - l_j0[0];
-                VS_PROF_T0();
                 for (int q = 0; q < cnt && ok_run; ++q, item_parity ^= 1u) {
                     int rem = len;
                     if (q + 1 < cnt) len = l_end[q + 1] - l_j0[q + 1];   // next item's length: off the critical path
@@ -384,7 +378,6 @@ spmm_tma_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map, int
                     if (acc_wait) ok_run = wait_or_abort<kSleepMma>(bar_acc_empty + 8 * acc, acc_parity, abort_flag);
                     const uint32_t d = tmem_base + acc * kAccCols;
                     uint32_t accumulate = 0;
-                    VS_PROF_ADD(3);   // mma: wait for a free accumulator (+ item bookkeeping)
                     do {
                         if (ok_run && g >= (uint32_t)kStages) {   // bounded wait for the other issuer (see above)
                             const uint32_t need = g - kStages;
@@ -396,7 +389,6 @@ spmm_tma_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map, int
                         if (ok_run) ok_run = wait_or_abort<kSleepMma>(bar_full + 8 * slot, full_parity, abort_flag);
                         if (!ok_run) break;
                         mma_done[mine] = g + 1;
-                        VS_PROF_ADD(4);   // mma: wait for a full stage
                         tc::fence_proxy_async();   // the value vectors were written by cp.async (generic proxy)
                         tc::tc_fence_after_sync();
                         const int n_mma = rem >= kStageNnz ? kMmaPerStage : max(1, (rem + 15) >> 4);
@@ -410,27 +402,23 @@ spmm_tma_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map, int
                         rem -= kStageNnz;
                         ++g;
                         if (++slot == (uint32_t)kStages) { slot = 0; full_parity ^= 1u; }
-                        VS_PROF_ADD(5);   // mma: issue
                     } while (rem > 0);
                     if (ok_run) tc::mma_commit(bar_acc_full + 8 * acc);
                     if (++acc == (uint32_t)kAccSlots) { acc = 0; acc_parity ^= 1u; acc_wait = true; }
                 }
                 mma_done[mine] = g_stage + stages_here;   // nothing of this phase is left for this thread to wait on
-                VS_PROF_FLUSH(3);
             }
         } else if (warp < kEpiWarps) {
             // =========================== epilogue ==========================================================
             const int quarter = warp;                     // warps 0..3: TMEM lanes 32*warp .. +31
             uint8_t *stg = sm + Smem::kStaging + warp * kStagingBytes;
             bool ok_run = true;
-            VS_PROF_T0();
             for (int q = 0; q < cnt && ok_run; ++q) {
                 const uint32_t ic = g_item + (uint32_t)q;
                 const uint32_t acc = ic % kAccSlots;
                 // warp-uniform outcome: tcgen05.ld below needs all 32 lanes
                 ok_run = __all_sync(0xffffffffu, wait_or_abort<kSleepEpilogue>(bar_acc_full + 8 * acc, (ic / kAccSlots) & 1u, abort_flag));
                 if (!ok_run) break;
-                VS_PROF_ADD(6);   // epilogue: wait for the accumulator
                 tc::tc_fence_after_sync();
                 uint32_t r[8];
                 tc::tmem_ld_x8(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kAccCols, r);
@@ -458,9 +446,7 @@ spmm_tma_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map, int
                         }
                     }
                 }
-                VS_PROF_ADD(7);   // epilogue: load, transpose, store
             }
-            VS_PROF_FLUSH(6);
         }
 
         // ---- phase end: everybody is done with the lists; advance the global counters identically ------------

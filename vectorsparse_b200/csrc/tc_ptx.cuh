@@ -9,25 +9,6 @@
 
 namespace vs {
 
-#ifdef VS_TC_PROFILE
-// Instrumented build only: clock cycles spent per role and wait site, kept in registers and summed over CTAs
-// (lane 0 of each warp) when the role finishes a phase.
-__device__ unsigned long long g_prof[16];
-#define VS_PROF_T0() long long prof_t0 = clock64(); long long prof_acc[3] = {0, 0, 0}
-#define VS_PROF_ADD(slot) do { long long prof_t1 = clock64(); prof_acc[(slot) % 3] += prof_t1 - prof_t0; prof_t0 = prof_t1; } while (0)
-#define VS_PROF_FLUSH(first) do { if (lane == 0) { for (int pi = 0; pi < 3; ++pi) atomicAdd(&g_prof[(first) + pi], (unsigned long long)prof_acc[((first) + pi) % 3]); } } while (0)
-// Time line of one CTA (block 0): clock64 at event `ev` of stage / item `idx`.
-__device__ long long g_trace[16][2048];
-#define VS_TRACE(ev, idx) do { if (blockIdx.x == 0 && (idx) < 2048u) g_trace[ev][idx] = clock64(); } while (0)
-#define VS_TRACE_B(blk, ev, idx) do { if (blockIdx.x == (blk) && (idx) < 2048u) g_trace[ev][idx] = clock64(); } while (0)
-#else
-#define VS_TRACE(ev, idx) do { } while (0)
-#define VS_TRACE_B(blk, ev, idx) do { } while (0)
-#define VS_PROF_T0() do { } while (0)
-#define VS_PROF_ADD(slot) do { } while (0)
-#define VS_PROF_FLUSH(first) do { } while (0)
-#endif
-
 namespace tc {
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -49,17 +30,6 @@ __device__ __forceinline__ void fence_mbar_init() {
 constexpr uint32_t kSuspendNs = VS_SUSPEND_NS;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
-#ifdef VS_EXP_TESTWAIT
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-#else
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
@@ -69,7 +39,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok)
         : "r"(bar), "r"(parity), "r"(kSuspendNs)
         : "memory");
-#endif
     return ok != 0;
 }
 // Polls at most kMaxPolls times (a few seconds at worst).  Returns false if the phase never completed.

@@ -1281,24 +1281,7 @@ VS_EXPORT int vs_selftest_gather4(const void *matrix, int rows, int cols, const 
     return (int)cudaGetLastError();
 }
 
-#ifdef VS_TC_PROFILE
-// Instrumented build only: reads (and clears) the per-role cycle counters of the tensor-core SpMM.
-VS_EXPORT int vs_debug_prof(unsigned long long *out16) {
-    VS_CUDA_TRY(cudaDeviceSynchronize());
-    VS_CUDA_TRY(cudaMemcpyFromSymbol(out16, vs::g_prof, sizeof(unsigned long long) * 16));
-    unsigned long long zero[16] = {0};
-    VS_CUDA_TRY(cudaMemcpyToSymbol(vs::g_prof, zero, sizeof(zero)));
-    return VS_OK;
-}
-#endif
 
-#ifdef VS_TC_PROFILE
-VS_EXPORT int vs_debug_trace(long long *out_16x2048) {
-    VS_CUDA_TRY(cudaDeviceSynchronize());
-    VS_CUDA_TRY(cudaMemcpyFromSymbol(out_16x2048, vs::g_trace, sizeof(long long) * 16 * 2048));
-    return VS_OK;
-}
-#endif
 
 namespace {
 // Whether the 16 contraction elements x `rows` fp16 operand a shared-memory descriptor names lies inside an image
