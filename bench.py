@@ -70,7 +70,7 @@ SHARDED = ("spmm_f32_v4_s80_n8192", "spmm_f32_v1_s80_n8192", "attention_cfg5")
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from an ncu capture of this
 # command (profiles/ holds the summary it comes from); None until one has been taken for the workload.
 NCU_TRAFFIC_BYTES = {
-    "spmm_v8_s90": 335.4e6,    # profiles/spmm_dense_kernel__spmm_v8_s90.md
+    "spmm_v8_s90": 335.4e6,    # profiles/spmm_pair_kernel__spmm_v8_s90.md
     "sddmm_v8_s90": 380.5e6,   # profiles/sddmm_dense_kernel__sddmm_v8_s90.md
 }
 
@@ -126,6 +126,29 @@ def measured_peaks():
         with open(path) as f:
             return float(json.load(f)["hbm_gbs"]), "measured"
     return 6650.0, "fallback"
+
+
+def measured_tensor_peaks():
+    """(burst, sustained) dense 16-bit GEMM TFLOP/s of the library GEMM on this pool, and where they come from."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    return 1590.0, 1400.0, "fallback"
+
+
+def tensor_pipe_view(w, avg_launch_s):
+    """The densifying SpMM kernels multiply whole 128- or 256-row tiles of A, zeros included, so the tensor pipe
+    executes 2*M*K*N flops per instance whatever the sparsity.  That dense-equivalent rate against the measured
+    GEMM peak is the second ceiling of these kernels (the first is HBM, `roofline`): at 90 % sparsity and K = 512
+    it is the higher of the two floors."""
+    dense_flops = 2.0 * w["M"] * w["K"] * w["N"] * w["inst"]
+    burst, sustained, kind = measured_tensor_peaks()
+    tfl = dense_flops / avg_launch_s / 1e12
+    return {"dense_equivalent_tflops": tfl, "peak_burst": burst, "peak_sustained": sustained, "peak_source": f"of {kind}",
+            "frac_of_burst": tfl / burst, "frac_of_sustained": tfl / sustained,
+            "floor_ms_at_burst": dense_flops / (burst * 1e12) * 1e3}
 
 
 class ClockSampler:
@@ -419,6 +442,8 @@ def run_ours(args):
             roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                         "peak_source": f"of {peak_kind}", "frac_of_nominal_8tbs": achieved / 8000.0,
                         "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "algorithmic_bytes_per_launch": alg_bytes}
+            if w["op"] in ("spmm", "spmm_t") and path != VS_PATH_CUDA_CORE:
+                roofline["tensor_pipe"] = tensor_pipe_view(w, avg_launch_s)
         line = {
             "metric": metric_name(w),
             "value": flops * args.steps * world / (total_ms * 1e-3) / 1e12,
