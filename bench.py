@@ -104,7 +104,7 @@ def kernels_per_step(w, a=None):
         return ["sddmm_cc_kernel"]
     from vectorsparse_b200 import _lib
     dense = a is not None and _lib.lib().vs_sddmm_formulation(a.m_vec, w["N"], w["K"], a.nnz_vec, w["V"]) == 1
-    return ["sddmm_plan_kernel", "sddmm_dense_kernel"] if dense else ["sddmm_tma_kernel"]
+    return ["sddmm_plan_kernel", "sddmm_pair_kernel"] if dense else ["sddmm_tma_kernel"]
 
 
 def config_of(name, w, a):

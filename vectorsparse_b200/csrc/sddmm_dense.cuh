@@ -10,7 +10,7 @@
 // Nothing outside the mask is ever stored, so non-finite products elsewhere in the tile cannot leak.
 //
 // Plan.  A small kernel buckets each vector-row's mask entries by 32-column chunk: `chunk_offsets`
-// [vector-rows][chunks + 1] and `chunk_entries` (entry index j, column within the chunk), in any order inside
+// [vector-rows][chunks + 1] and `chunk_entries` (entry index j, column), in any order inside
 // a chunk.  It depends on the structure only and is shared by every matrix of a batch.
 //
 // Organisation: one persistent CTA per SM, work items (batch, 256-row tile of lhs, 128-row tile of rhs).
@@ -70,7 +70,7 @@ static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 
 // ---- plan -------------------------------------------------------------------------------------------------
 // One CTA per vector-row.  chunk_offsets[i * (chunks + 1) + c] .. [.. + c + 1] delimit, inside chunk_entries, the
-// mask entries of vector-row i whose column lies in [32 c, 32 c + 32); an entry is (j, column - 32 c).  Columns
+// mask entries of vector-row i whose column lies in [32 c, 32 c + 32); an entry is (j, column).  Columns
 // outside [0, n) are dropped: their outputs are not written (the gather kernels write zeros there; the host
 // entry points reject such structures where they can see them).
 __global__ void __launch_bounds__(kPlanThreads)
@@ -106,7 +106,7 @@ sddmm_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__rest
         const int c = __ldg(col_indices + j);
         if ((unsigned)c >= (unsigned)n) continue;
         const int pos = atomicAdd(cursor + c / kChunk, 1);
-        chunk_entries[pos] = make_uint2((uint32_t)j, (uint32_t)(c % kChunk));
+        chunk_entries[pos] = make_uint2((uint32_t)j, (uint32_t)c);
     }
 }
 
@@ -341,7 +341,7 @@ sddmm_dense_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_
 #pragma unroll
                     for (int a = 0; a < kAhead; ++a) {
                         if (off[c] + a < off[c + 1]) {
-                            out[(int64_t)ent[a].x * V] = box_read(ent[a].y);
+                            out[(int64_t)ent[a].x * V] = box_read(ent[a].y % kChunk);
                         }
                     }
                     // denser rows: the remaining entries eight at a time, so that their loads overlap
@@ -352,7 +352,7 @@ sddmm_dense_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_
 #pragma unroll
                         for (int u = 0; u < 8; ++u) {
                             if (e + u < off[c + 1]) {
-                                out[(int64_t)en[u].x * V] = box_read(en[u].y);
+                                out[(int64_t)en[u].x * V] = box_read(en[u].y % kChunk);
                             }
                         }
                     }

@@ -113,6 +113,16 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void *tensor_map
         "l"(tensor_map), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
         : "memory");
 }
+// The same load issued by either CTA of a pair (cta_group::2): the tile lands in the ISSUING CTA's shared memory, the
+// bytes are counted on the mbarrier at `cluster_bar`, which may belong to the other CTA of the pair (map_to_cta).  No
+// multicast: one destination.
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void *tensor_map, uint32_t cluster_bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.cta_group::2"
+        " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+        "l"(tensor_map), "r"(cluster_bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
 // Asks for the same tile to be brought into L2 only.
 __device__ __forceinline__ void tma_prefetch_3d(const void *tensor_map, int x, int y, int z) {
     asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(tensor_map), "r"(x), "r"(y), "r"(z)
@@ -295,6 +305,15 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t cluster_addr) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
 }
 
+// The same arrival on the mbarrier at offset `bar` of BOTH CTAs of the pair, with one instruction (a commit, not a
+// load: nothing is copied anywhere).
+__device__ __forceinline__ void mma_commit_pair_both(uint32_t bar) {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+                 "h"(both)
+                 : "memory");
+}
+
 // ---- TMEM -> registers: each thread of a warp reads N consecutive 32-bit columns of its own lane ------------
 // The load and the wait for it are one asm statement: tcgen05.ld completes asynchronously, and nothing else
 // tells the compiler that the destination registers must not be read before tcgen05.wait::ld.
@@ -329,6 +348,18 @@ __device__ __forceinline__ void tmem_ld_x32_issue(uint32_t taddr, uint32_t (&r)[
 }
 __device__ __forceinline__ void tmem_ld_x32_wait(uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31]) : : "memory");
+}
+// One column: every lane of the warp reads column `taddr.column` of its own lane.  The column is an ordinary
+// (warp-uniform) register, which makes this the way to index an accumulator row dynamically without going through
+// shared memory.  Issued without a wait; tmem_ld_wait8 names up to eight destinations.
+__device__ __forceinline__ void tmem_ld_x1_issue(uint32_t taddr, uint32_t &r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait8(uint32_t (&r)[8]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7])
+                 :
+                 : "memory");
 }
 // 64 columns: two loads in flight, one wait.
 __device__ __forceinline__ void tmem_ld_x64(uint32_t taddr, uint32_t (&r)[64]) {

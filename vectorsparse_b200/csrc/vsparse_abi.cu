@@ -25,6 +25,7 @@
 #include "spmm_tc.cuh"
 #include "spmm_tma.cuh"
 #include "spmm_dense.cuh"
+#include "sddmm_pair.cuh"
 #include "spmm_pair.cuh"
 #include "spmm_t.cuh"
 #include "sddmm_tc.cuh"
@@ -587,6 +588,75 @@ bool sddmm_use_dense(const SddmmParams &p, int V) {
     return dense * 1.25 < gather;
 }
 
+// The dense SDDMM by pairs of CTAs (sddmm_pair.cuh) serves masks of up to pairsddmm::kMaxPlanColumns columns whose
+// outputs can be written with vector stores; VSPARSE_B200_SDDMM_PAIR=0 keeps the single-CTA kernel.
+inline bool sddmm_pair_enabled() {
+    const char *e = std::getenv("VSPARSE_B200_SDDMM_PAIR");
+    return !(e && !std::strcmp(e, "0"));
+}
+// Scratch of the pair kernel's plan: cells, entry order, the twins flag.
+int64_t sddmm_pair_plan_bytes(int m_vec, int n, int nnz_vec, int64_t *cells_out, int64_t *order_out) {
+    const int64_t blocks = (m_vec + pairsddmm::kBlockVecRows - 1) / pairsddmm::kBlockVecRows;
+    const int64_t cells_bytes = (blocks * n * 8 + 15) & ~15ll, order_bytes = ((int64_t)nnz_vec * 4 + 15) & ~15ll;
+    if (cells_out) *cells_out = cells_bytes;
+    if (order_out) *order_out = order_bytes;
+    return cells_bytes + order_bytes + 16;
+}
+// Plan, multiplying kernel and the fix-up for repeated columns; false if this call or this device cannot take them
+// (nothing has been enqueued then).
+template <typename TOut, int V> bool launch_sddmm_pair(const SddmmParams &p, cudaStream_t s, DeviceInfo *d, int *rc_out) {
+    static int resident[kMaxDevices];   // 0 = not asked yet, -1 = the kernels cannot run here
+    auto kernel = pairsddmm::sddmm_pair_kernel<TOut, V>;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return false;
+    if (resident[dev] == 0) {
+        if (set_smem(kernel, pairsddmm::kSmemBytes) != VS_OK ||
+            set_smem(pairsddmm::sddmm_cell_plan_kernel, 8 * pairsddmm::kMaxPlanColumns) != VS_OK) {
+            resident[dev] = -1;
+        } else {
+            const int n = max_resident_pairs(kernel, pairsddmm::kThreads, pairsddmm::kSmemBytes, d);
+            resident[dev] = n > 0 ? n : -1;
+        }
+    }
+    if (resident[dev] < 0) return false;
+    int64_t cells_bytes = 0, order_bytes = 0;
+    const int64_t plan_bytes = sddmm_pair_plan_bytes(p.m_vec, p.n, p.nnz_vec, &cells_bytes, &order_bytes);
+    if (p.n > pairsddmm::kMaxPlanColumns || plan_bytes > kMaxPlanBytes || !aligned16(p.out) ||
+        (p.batch > 1 && (p.stride_out * sizeof(TOut)) % 16 != 0))
+        return false;
+    CUtensorMap map_l, map_r;
+    if (make_tile_map(&map_l, p.lhs, false, (uint64_t)p.m_vec * V, (uint64_t)p.k, (uint64_t)p.batch, (uint64_t)p.stride_lhs, 64,
+                      pairsddmm::kCtaRows) != VS_OK ||
+        make_tile_map(&map_r, p.rhs, false, (uint64_t)p.n, (uint64_t)p.k, (uint64_t)p.batch, (uint64_t)p.stride_rhs, 64,
+                      pairsddmm::kCtaRows) != VS_OK)
+        return false;
+    uint8_t *plan = nullptr;
+    if (stream_scratch(d, s, (size_t)plan_bytes, reinterpret_cast<void **>(&plan)) != VS_OK) return false;
+    uint2 *cells = reinterpret_cast<uint2 *>(plan);
+    int32_t *order = reinterpret_cast<int32_t *>(plan + cells_bytes);
+    int32_t *twins = reinterpret_cast<int32_t *>(plan + cells_bytes + order_bytes);
+    const int blocks = (p.m_vec + pairsddmm::kBlockVecRows - 1) / pairsddmm::kBlockVecRows;
+    pairsddmm::sddmm_cell_plan_kernel<<<blocks, pairsddmm::kPlanThreads, (size_t)8 * p.n, s>>>(p.row_offsets, p.col_indices, p.m_vec, p.n,
+                                                                                              p.nnz_vec, cells, order, twins);
+    int rc = (int)cudaGetLastError();
+    if (rc == VS_OK) {
+        const int m_tiles = (p.m_vec * V + pairsddmm::kTile - 1) / pairsddmm::kTile;
+        const int n_tiles = (p.n + pairsddmm::kTile - 1) / pairsddmm::kTile;
+        const int64_t items = (int64_t)p.batch * n_tiles * m_tiles;
+        const unsigned pairs = (unsigned)(items < resident[dev] ? items : resident[dev]);
+        // rhs of a batch entry fits the resident slots (VSPARSE_B200_SDDMM_RESIDENT=0: stream both operands anyway)
+        const char *res_env = std::getenv("VSPARSE_B200_SDDMM_RESIDENT");
+        const int resident = (n_tiles * (p.k / densesddmm::kBlockK) <= pairsddmm::kMaxResident && !(res_env && !std::strcmp(res_env, "0"))) ? 1 : 0;
+        rc = (int)launch_pairs(kernel, pairs, pairsddmm::kThreads, (size_t)pairsddmm::kSmemBytes, s, true, p, map_l, map_r, cells, order,
+                               blocks, m_tiles, n_tiles, resident, d->status);
+    }
+    if (rc == VS_OK)
+        rc = (int)launch_overlapped(pairsddmm::sddmm_twin_kernel<TOut, V>, (unsigned)((p.nnz_vec + pairsddmm::kPlanThreads - 1) / pairsddmm::kPlanThreads),
+                                    pairsddmm::kPlanThreads, 0, s, p, cells, order, twins);
+    *rc_out = rc;
+    return true;
+}
+
 template <typename TOut, int V> int launch_sddmm_tc(const SddmmParams &p, cudaStream_t s) {
     DeviceInfo *d;
     int rc = device_info(&d);
@@ -600,6 +670,7 @@ template <typename TOut, int V> int launch_sddmm_tc(const SddmmParams &p, cudaSt
                           (p.batch == 1 || ((p.stride_lhs * 2) % 16 == 0 && (p.stride_rhs * 2) % 16 == 0)) &&
                           sddmm_use_dense(p, V);
     if (!dense_ok) return launch_sddmm_gather<TOut, V>(p, s, d);
+    if (sddmm_pair_enabled() && launch_sddmm_pair<TOut, V>(p, s, d, &rc)) return rc;
     CUtensorMap map_l, map_r;
     if (make_tile_map(&map_l, p.lhs, false, (uint64_t)p.m_vec * V, (uint64_t)p.k, (uint64_t)p.batch, (uint64_t)p.stride_lhs, 64,
                       densesddmm::kTileM) != VS_OK ||
