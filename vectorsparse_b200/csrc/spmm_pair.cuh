@@ -18,23 +18,22 @@
 //   warps 8-19   fill: two warps per A slot (six slots), each owning 128 rows x 32 columns (two plan buckets) of the
 //                stage; what a stage needs from global memory is requested right after the previous one was handed over
 //   warp 20      one thread issuing the CTA's B loads, six stages ahead: the ring of B tiles is what hides the latency
-//                of L2 and HBM (an L2 prefetch warp beside it, as the single-CTA kernel has, made this kernel slower)
-//   warp 21      first CTA: the MMA-issuing thread of the pair; second CTA: the thread that forwards "my B tile has
-//                landed" to the first CTA's barrier
-//   warp 22      first CTA: the thread that forwards "stage multiplied" and "accumulator complete" to the second
-//                CTA's barriers (a second commit per stage, addressed to the other CTA, works as well but costs the
-//                issuing thread ~105 cycles per stage: measured 3 % slower)
-// Barriers, one set per stage in flight.  full[s] (first CTA): the fill warps of BOTH CTAs, its loader + the bytes of
-// its B tile, the forwarded "landed" of the second CTA, whose own full[s] only collects its loader + bytes.  done[s]
-// and acc_full[b]: a tcgen05.commit in the first CTA, the forwarded arrival in the second.  acc_empty[b] (first CTA):
-// every epilogue thread of both CTAs.  Every wait is bounded; a wait that runs out raises the abort flag of both
-// CTAs, all roles fall through, a status bit is set, both CTAs meet at the final cluster barrier and tensor memory
-// is freed.
+//                of L2 and HBM (an L2 prefetch warp beside it, as the single-CTA kernel has, made this kernel slower).
+//                They are cta_group::2 loads: the tile lands in the issuing CTA, its bytes are counted on the FIRST
+//                CTA's barrier, which that CTA's loader arms with the bytes of both halves
+//   warp 21      first CTA: the MMA-issuing thread of the pair (idle in the second).  Its commits arrive on the barriers
+//                of both CTAs at once (tcgen05.commit with a CTA mask: an arrival, not a copy), so nothing is forwarded
+// Barriers, one set per stage in flight.  full[s] (first CTA only): the fill warps of BOTH CTAs, the first CTA's loader
+// + the bytes of both CTAs' B tiles.  done[s] and acc_full[b] (both CTAs): a commit of the MMA-issuing thread.
+// acc_empty[b] (first CTA): every epilogue thread of both CTAs.  Every wait is bounded; a wait that runs out raises the
+// abort flag of both CTAs, all roles fall through, a status bit is set, both CTAs meet at the final cluster barrier and
+// tensor memory is freed.
 //
 // What was measured on the way (B200, 148 SMs, ~1.5 GHz under the power cap while this kernel runs): a pair MMA of
 // N = 256 occupies the pipe for ~135 cycles (N = 128: ~71); one thread issues them back to back every ~52 cycles, a
 // commit costs it ~105.  A remote mbarrier arrive with cluster-scope release costs ~1100 cycles, the default form a
-// few tens.  Two issuing threads splitting the columns (N = 128 each) read A twice and were slower; walking the
+// few tens; forwarding "stage multiplied" and "B landed" between the CTAs with a thread each (instead of the commit mask
+// and the cta_group::2 loads) cost 1-2 %.  Two issuing threads splitting the columns (N = 128 each) read A twice and were slower; walking the
 // issue loop with the whole warp was slower; rings of 4 + 8, 5 + 7, 6 + 6 (A + B) stages are within 3 % of each other.
 // With the fill, the B loads and the output stores switched off in turn the kernel gains 20, 15 and 23 us of its
 // 115; with all three off it takes 77 us, which is the tensor pipe's time for the dense work at that clock.
@@ -64,13 +63,12 @@ constexpr int kFillCols = 32;                             // columns of a stage 
 constexpr int kEpiWarps = 8;                              // TMEM lane quarter = warp % 4, half of the columns = warp / 4
 constexpr int kFillWarp0 = kEpiWarps;
 constexpr int kFillPerSlot = kBlockK / kFillCols;         // warps per CTA and stage
-constexpr int kFillWarps = kAStages * kFillPerSlot;       // 16: warp f fills A slot f % kAStages
+constexpr int kFillWarps = kAStages * kFillPerSlot;       // 12: warp f fills A slot f % kAStages
 constexpr int kFillBatches = 2;                           // batches of 32 entries a fill warp keeps in flight
 constexpr int kOverflowBatches = 4;
-constexpr int kLoadWarp = kFillWarp0 + kFillWarps;        // 24
+constexpr int kLoadWarp = kFillWarp0 + kFillWarps;        // 20
 constexpr int kMmaWarp = kLoadWarp + 1;
-constexpr int kForwardWarp = kMmaWarp + 1;
-constexpr int kThreads = (kForwardWarp + 1) * 32;
+constexpr int kThreads = (kMmaWarp + 1) * 32;
 static_assert(kThreads <= 1024, "too many fill warps for one CTA");
 constexpr int kAStageBytes = kCtaRows * kBlockK * 2;      // 16 KiB
 constexpr int kBSlabBytes = kBlockK * 64 * 2;             // 8 KiB: 64 rows of B x 64 columns
@@ -186,10 +184,9 @@ spmm_pair_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b, 
         reinterpret_cast<uint4 *>(sm + Smem::kA)[i] = make_uint4(0, 0, 0, 0);
     if (t == 0) {
         for (int s = 0; s < kBarStages; ++s) {
-            // first CTA: the fill warps of both CTAs, its loader (+ the bytes of its B tile), the second CTA's "B landed";
-            // second CTA: its loader (+ bytes) only, watched by its forwarding thread
-            tc::mbar_init(bar_full + 8 * s, rank == 0 ? 2 * kFillPerSlot + 2 : 1);
-            tc::mbar_init(bar_done + 8 * s, 1);   // first CTA: the commit; second CTA: the forwarded arrival
+            // first CTA only: the fill warps of both CTAs, its loader's arrival + the bytes of BOTH CTAs' B tiles
+            tc::mbar_init(bar_full + 8 * s, 2 * kFillPerSlot + 1);
+            tc::mbar_init(bar_done + 8 * s, 1);   // a commit of the MMA-issuing thread, which arrives in both CTAs
         }
         for (int s = 0; s < 2; ++s) {
             tc::mbar_init(bar_acc_full + 8 * s, 1);
@@ -353,6 +350,7 @@ spmm_pair_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b, 
         // them can arrive after the CTA has gone.
         if (lane == 0) {
             bool ok_run = true;
+            const uint32_t full_first = tc::map_to_cta(bar_full, 0);
             Walk walk;
             walk.init(pair, pairs, 0u, total_stages, m_tiles, n_tiles, k_blocks);
             for (uint32_t g = 0; g < total_stages && ok_run; ++g, walk.advance(1)) {
@@ -362,13 +360,15 @@ spmm_pair_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b, 
                     ok_run = wait_or_abort<kSleepFill>(bar_done + 8 * (prev % kBarStages), (prev / kBarStages) & 1u, abort_flag, abort_addr, peer);
                 }
                 if (!ok_run) break;
-                const uint32_t bar = bar_full + 8 * (g % kBarStages);
+                // cta_group::2 loads: the tile lands here, its bytes are counted on the FIRST CTA's barrier, which that
+                // CTA's loader arms with the bytes of both halves
+                const uint32_t bar = full_first + 8 * (g % kBarStages);
                 const int n0 = walk.nt * tn + (int)rank * half_cols;   // first column of this CTA's half
-                tc::mbar_expect_tx(bar, (uint32_t)slabs * kBSlabBytes);
+                if (rank == 0) tc::mbar_expect_tx(bar_full + 8 * (g % kBarStages), 2u * (uint32_t)slabs * kBSlabBytes);
                 if (slabs == 2) {
-                    tc::tma_load_4d(base + Smem::kB + slot * kBStageBytes, &map_b2, bar, 0, walk.kb * kBlockK, n0 >> 6, walk.b);
+                    tc::tma_load_4d_pair(base + Smem::kB + slot * kBStageBytes, &map_b2, bar, 0, walk.kb * kBlockK, n0 >> 6, walk.b);
                 } else {
-                    tc::tma_load_3d(base + Smem::kB + slot * kBStageBytes, &map_b, bar, n0, walk.kb * kBlockK, walk.b);
+                    tc::tma_load_3d_pair(base + Smem::kB + slot * kBStageBytes, &map_b, bar, n0, walk.kb * kBlockK, walk.b);
                 }
             }
             const uint32_t tail0 = total_stages > (uint32_t)kBarStages ? total_stages - kBarStages : 0u;
@@ -409,42 +409,12 @@ spmm_pair_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b, 
                             tc::mma_f16_ss_pair(d, tc::desc64(a_lo + 128 * kk, a_hi), tc::desc64(b_lo + 128 * kk, b_hi), idesc,
                                                 (kb > 0 || kk > 0) ? 1u : 0u);
                     }
-                    tc::mma_commit_pair(bar_done + 8 * bar);   // this CTA's barrier; the forwarding warp tells the other CTA
+                    tc::mma_commit_pair_both(bar_done + 8 * bar);   // "stage multiplied", in both CTAs at once
                     if (++a_slot == (uint32_t)kAStages) a_slot = 0;
                     if (++b_slot == (uint32_t)kBStages) b_slot = 0;
                     if (++bar == (uint32_t)kBarStages) { bar = 0; parity ^= 1u; }
                 }
-                if (ok_run) tc::mma_commit_pair(bar_acc_full + 8 * buf);
-            }
-        } else if (lane == 0 && rank != 0) {
-            // =========================== second CTA: forward "my B tile has landed" =======================
-            const uint32_t full_first = tc::map_to_cta(bar_full, 0);
-            bool ok_run = true;
-            uint32_t slot = 0, parity = 0;
-            for (uint32_t g = 0; g < total_stages && ok_run; ++g) {
-                ok_run = wait_or_abort<kSleepMma>(bar_full + 8 * slot, parity, abort_flag, abort_addr, peer);
-                if (!ok_run) break;
-                tc::mbar_arrive_remote(full_first + 8 * slot);
-                if (++slot == (uint32_t)kBarStages) { slot = 0; parity ^= 1u; }
-            }
-        }
-    } else if (warp == kForwardWarp) {
-        if (lane == 0 && rank == 0) {
-            // =========================== first CTA: forward "multiplied" and "accumulator complete" =======
-            const uint32_t done_there = tc::map_to_cta(bar_done, 1), accf_there = tc::map_to_cta(bar_acc_full, 1);
-            bool ok_run = true;
-            uint32_t slot = 0, parity = 0;
-            for (uint32_t i = 0; i < my_items && ok_run; ++i) {
-                for (int kb = 0; kb < k_blocks && ok_run; ++kb) {
-                    ok_run = wait_or_abort<kSleepMma>(bar_done + 8 * slot, parity, abort_flag, abort_addr, peer);
-                    if (!ok_run) break;
-                    tc::mbar_arrive_remote(done_there + 8 * slot);
-                    if (++slot == (uint32_t)kBarStages) { slot = 0; parity ^= 1u; }
-                }
-                if (!ok_run) break;
-                const uint32_t buf = i & 1u;
-                ok_run = wait_or_abort<kSleepMma>(bar_acc_full + 8 * buf, (i >> 1) & 1u, abort_flag, abort_addr, peer);
-                if (ok_run) tc::mbar_arrive_remote(accf_there + 8 * buf);
+                if (ok_run) tc::mma_commit_pair_both(bar_acc_full + 8 * buf);
             }
         }
     } else {

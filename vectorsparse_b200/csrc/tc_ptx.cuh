@@ -123,6 +123,13 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void *tenso
         "l"(tensor_map), "r"(cluster_bar), "r"(x), "r"(y), "r"(z)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const void *tensor_map, uint32_t cluster_bar, int x, int y, int z, int w) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.cta_group::2"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
+        "l"(tensor_map), "r"(cluster_bar), "r"(x), "r"(y), "r"(z), "r"(w)
+        : "memory");
+}
 // Asks for the same tile to be brought into L2 only.
 __device__ __forceinline__ void tma_prefetch_3d(const void *tensor_map, int x, int y, int z) {
     asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(tensor_map), "r"(x), "r"(y), "r"(z)
