@@ -796,11 +796,14 @@ def run_reference(args):
             vals.append(base["value"])
     v = float(np.mean(vals))
     base["value"] = v
+    # the time one whole step of this workload (all its instances) takes at the measured rate
+    per_instance = {"attention": 4.0, "attention_bwd": 10.0}.get(w["op"], 2.0) * a.nnz_vec * w["V"] * w["N"]
+    step_ms = per_instance * w["inst"] / (v * 1e12) * 1e3 if v > 0 else None
     line = {
         "impl": "reference",
         "metric": metric_name(w),
         "value": v, "unit": "TFLOP/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": steps,
-        "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
         "config": config_of(args.workload, w, a),
         "run": {"path": "host loop (spmm_benchmark.cpp:66-86)" if w["op"] == "spmm" else

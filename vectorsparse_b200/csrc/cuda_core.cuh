@@ -13,18 +13,22 @@ namespace vs {
 constexpr int kCcThreads = 128;
 
 // ---- SpMM ---------------------------------------------------------------------------------------------------
-// Work item = (vector-row in row_indices order, 16-byte chunk of the dense width).  The thread keeps V x E
-// fp32 accumulators (E = elements per 16 bytes) and walks the row's nonzero vectors four at a time so that
-// four independent gathers of B are in flight.
-template <typename TIn, typename TOut, int V>
+// Work item = (vector-row in row_indices order, kChunks 16-byte chunks of the dense width, 32 chunks apart so that
+// the lanes of a warp still read consecutive chunks).  The thread keeps V x E x kChunks fp32 accumulators (E = elements
+// per 16 bytes) and walks the row's nonzero vectors four at a time so that four independent gathers of B are in
+// flight.  With two or four chunks per thread the warp-uniform loads of an entry (column index, value vector) feed
+// that many times the FMAs; it needs the dense width to be a multiple of 32 kChunks chunks.
+template <typename TIn, typename TOut, int V, int kChunks>
 __global__ void __launch_bounds__(kCcThreads) spmm_cc_kernel(const SpmmParams p) {
     constexpr int E = Chunk<TIn>::kElems;
-    constexpr int U = 4;
-    const int chunks = p.N / E;
+    constexpr int U = kChunks == 1 ? 4 : (kChunks == 2 ? 2 : 1);
+    const int chunks = p.N / (E * kChunks);            // items per vector-row
     const int64_t item = (int64_t)blockIdx.x * kCcThreads + threadIdx.x;
     if (item >= (int64_t)p.m_vec * chunks) return;
     const int order = (int)(item / chunks);
-    const int chunk = (int)(item - (int64_t)order * chunks);
+    const int piece = (int)(item - (int64_t)order * chunks);
+    // kChunks > 1: warp-sized groups of items take chunks 32 kChunks g + lane, + 32 + lane, ...
+    const int chunk = kChunks == 1 ? piece : (piece / 32) * (32 * kChunks) + (piece % 32);
     const int row = __ldg(p.row_indices + order);
     const int b = blockIdx.y;
 
@@ -32,11 +36,13 @@ __global__ void __launch_bounds__(kCcThreads) spmm_cc_kernel(const SpmmParams p)
     const TIn *rhs = static_cast<const TIn *>(p.rhs) + (int64_t)b * p.stride_rhs + (int64_t)chunk * E;
     TOut *out = static_cast<TOut *>(p.out) + (int64_t)b * p.stride_out + (int64_t)chunk * E;
 
-    float acc[V][E];
+    float acc[kChunks][V][E];
 #pragma unroll
-    for (int v = 0; v < V; ++v)
+    for (int q = 0; q < kChunks; ++q)
 #pragma unroll
-        for (int e = 0; e < E; ++e) acc[v][e] = 0.f;
+        for (int v = 0; v < V; ++v)
+#pragma unroll
+            for (int e = 0; e < E; ++e) acc[q][v][e] = 0.f;
 
     int j = __ldg(p.row_offsets + row);
     const int end = __ldg(p.row_offsets + row + 1);
@@ -44,34 +50,43 @@ __global__ void __launch_bounds__(kCcThreads) spmm_cc_kernel(const SpmmParams p)
     for (; j + U <= end; j += U) {
         int col[U];
         float a[U][V];
-        Chunk<TIn> bt[U];
+        Chunk<TIn> bt[U][kChunks];
 #pragma unroll
         for (int u = 0; u < U; ++u) col[u] = __ldg(p.col_indices + j + u);
 #pragma unroll
-        for (int u = 0; u < U; ++u) bt[u].load(rhs + (int64_t)col[u] * p.N);
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int q = 0; q < kChunks; ++q) bt[u][q].load(rhs + (int64_t)col[u] * p.N + q * 32 * E);
 #pragma unroll
         for (int u = 0; u < U; ++u) VecLoad<TIn, V>::load(values + (int64_t)(j + u) * V, a[u]);
 #pragma unroll
         for (int u = 0; u < U; ++u)
 #pragma unroll
-            for (int v = 0; v < V; ++v)
+            for (int q = 0; q < kChunks; ++q)
 #pragma unroll
-                for (int e = 0; e < E; ++e) acc[v][e] = fmaf(a[u][v], bt[u].f[e], acc[v][e]);
+                for (int v = 0; v < V; ++v)
+#pragma unroll
+                    for (int e = 0; e < E; ++e) acc[q][v][e] = fmaf(a[u][v], bt[u][q].f[e], acc[q][v][e]);
     }
     for (; j < end; ++j) {
         const int col = __ldg(p.col_indices + j);
         float a[V];
-        Chunk<TIn> bt;
-        bt.load(rhs + (int64_t)col * p.N);
+        Chunk<TIn> bt[kChunks];
+#pragma unroll
+        for (int q = 0; q < kChunks; ++q) bt[q].load(rhs + (int64_t)col * p.N + q * 32 * E);
         VecLoad<TIn, V>::load(values + (int64_t)j * V, a);
 #pragma unroll
-        for (int v = 0; v < V; ++v)
+        for (int q = 0; q < kChunks; ++q)
 #pragma unroll
-            for (int e = 0; e < E; ++e) acc[v][e] = fmaf(a[v], bt.f[e], acc[v][e]);
+            for (int v = 0; v < V; ++v)
+#pragma unroll
+                for (int e = 0; e < E; ++e) acc[q][v][e] = fmaf(a[v], bt[q].f[e], acc[q][v][e]);
     }
 
 #pragma unroll
-    for (int v = 0; v < V; ++v) store_chunk(out + ((int64_t)row * V + v) * p.N, acc[v]);
+    for (int q = 0; q < kChunks; ++q)
+#pragma unroll
+        for (int v = 0; v < V; ++v) store_chunk(out + ((int64_t)row * V + v) * p.N + q * 32 * E, acc[q][v]);
 }
 
 // ---- SDDMM --------------------------------------------------------------------------------------------------

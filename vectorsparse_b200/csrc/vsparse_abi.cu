@@ -260,11 +260,28 @@ int make_blocked_map(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t 
 // ---- SpMM dispatch ----------------------------------------------------------------------------------------
 template <typename TIn, typename TOut, int V> int launch_spmm_cc(const SpmmParams &p, cudaStream_t s) {
     constexpr int E = Chunk<TIn>::kElems;
-    const int64_t items = (int64_t)p.m_vec * (p.N / E);
+    // several 16-byte chunks per thread where the dense width allows it and the accumulators stay in registers (64 at
+    // most); VSPARSE_B200_SPMM_CC_CHUNKS=1|2|4 caps them
+    const char *e = std::getenv("VSPARSE_B200_SPMM_CC_CHUNKS");
+    const int cap = e ? std::atoi(e) : 4;
+    const int want = (V * E <= 16 && cap >= 4 && p.N % (128 * E) == 0) ? 4 : (V * E <= 32 && cap >= 2 && p.N % (64 * E) == 0) ? 2 : 1;
+    const int64_t items = (int64_t)p.m_vec * (p.N / E) / want;
     const int64_t blocks = (items + kCcThreads - 1) / kCcThreads;
     if (blocks > 0x7fffffffll) return VS_ERR_SHAPE;
     dim3 grid((unsigned)blocks, (unsigned)p.batch, 1);
-    spmm_cc_kernel<TIn, TOut, V><<<grid, kCcThreads, 0, s>>>(p);
+    if constexpr (V * E <= 16) {
+        if (want == 4) {
+            spmm_cc_kernel<TIn, TOut, V, 4><<<grid, kCcThreads, 0, s>>>(p);
+            return (int)cudaGetLastError();
+        }
+    }
+    if constexpr (V * E <= 32) {
+        if (want == 2) {
+            spmm_cc_kernel<TIn, TOut, V, 2><<<grid, kCcThreads, 0, s>>>(p);
+            return (int)cudaGetLastError();
+        }
+    }
+    spmm_cc_kernel<TIn, TOut, V, 1><<<grid, kCcThreads, 0, s>>>(p);
     return (int)cudaGetLastError();
 }
 
