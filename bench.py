@@ -70,8 +70,8 @@ SHARDED = ("spmm_f32_v4_s80_n8192", "spmm_f32_v1_s80_n8192", "attention_cfg5")
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from an ncu capture of this
 # command (profiles/ holds the summary it comes from); None until one has been taken for the workload.
 NCU_TRAFFIC_BYTES = {
-    "spmm_v8_s90": 335.4e6,    # profiles/spmm_pair_kernel__spmm_v8_s90.md
-    "sddmm_v8_s90": 380.5e6,   # profiles/sddmm_dense_kernel__sddmm_v8_s90.md
+    "spmm_v8_s90": 335.7e6,    # profiles/spmm_pair_kernel__spmm_v8_s90.md
+    "sddmm_v8_s90": 400.8e6,   # profiles/sddmm_pair_kernel__sddmm_v8_s90.md
 }
 
 

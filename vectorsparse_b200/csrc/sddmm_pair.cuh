@@ -69,7 +69,7 @@ constexpr int kThreads = (kMmaWarp + 1) * 32;             // 576
 constexpr int kOperandBytes = kCtaRows * kBlockK * 2;     // 16 KiB: 128 rows of either operand, 64 contraction elements
 constexpr int kTmemCols = 2 * kTile;                      // two accumulator buffers
 constexpr int kBlockVecRows = 32;                         // vector-rows per presence mask
-constexpr int kPlanThreads = 256;
+constexpr int kPlanThreads = 512;
 constexpr int kMaxPlanColumns = 8192;                     // mask widths the plan kernel holds in shared memory
 constexpr int kSleepLoad = 32, kSleepMma = 0, kSleepEpilogue = 32;
 #ifndef VS_SDDMM_PREFETCH_ITEMS
@@ -130,7 +130,7 @@ sddmm_cell_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *_
                        uint2 *__restrict__ cells, int32_t *__restrict__ order, int32_t *__restrict__ twins) {
     extern __shared__ uint32_t cell_sh[];   // [n] masks, then [n] positions
     __shared__ int32_t offs[kBlockVecRows + 1];
-    __shared__ int32_t part_sum[kPlanThreads];
+    __shared__ int32_t part_sum[32];
     pdl_launch_dependents();   // the multiplying kernel may set itself up while the plan is made
     uint32_t *mask = cell_sh, *first = cell_sh + n;
     const int t = threadIdx.x, blk = blockIdx.x, vr0 = blk * kBlockVecRows;
@@ -158,19 +158,33 @@ sddmm_cell_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *_
     }
     if (twin) atomicExch(twins, 1);
     __syncthreads();
-    // exclusive scan of popc(mask[c]) over the columns: every thread sums a contiguous run, thread 0 scans the runs
+    // exclusive scan of popc(mask[c]) over the columns: every thread sums a contiguous run, the runs are scanned with
+    // shuffles inside each warp and once more across the warps
     const int per = (n + kPlanThreads - 1) / kPlanThreads;
     const int c_lo = min(t * per, n), c_hi = min(c_lo + per, n);
     int sum = 0;
     for (int c = c_lo; c < c_hi; ++c) sum += __popc(mask[c]);
-    part_sum[t] = sum;
+    const int lane = t & 31, warp = t >> 5;
+    int incl = sum;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += up;
+    }
+    if (lane == 31) part_sum[warp] = incl;
     __syncthreads();
-    if (t == 0) {
-        int run = j0;
-        for (int i = 0; i < kPlanThreads; ++i) { const int x = part_sum[i]; part_sum[i] = run; run += x; }
+    if (warp == 0) {
+        const int w_sum = lane < kPlanThreads / 32 ? part_sum[lane] : 0;
+        int w_incl = w_sum;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, w_incl, d);
+            if (lane >= d) w_incl += up;
+        }
+        if (lane < kPlanThreads / 32) part_sum[lane] = w_incl - w_sum;   // what the warps before this one hold
     }
     __syncthreads();
-    int run = part_sum[t];
+    int run = j0 + part_sum[warp] + incl - sum;
     uint2 *mine = cells + (int64_t)blk * n;
     for (int c = c_lo; c < c_hi; ++c) {
         first[c] = (uint32_t)run;
