@@ -22,15 +22,19 @@
 // the written entry's outputs to its twins (their values are equal by definition).
 //
 // Operand traffic.  With both operands streamed every SM takes 32 KiB from L2 per 540 cycles of tensor work.  When the
-// rhs of one batch entry fits eight of the CTA's twelve 16 KiB operand slots (n / 256 x k / 64 <= 8 tiles per CTA) it
+// rhs of one batch entry fits eight of the CTA's fourteen 16 KiB operand slots (n / 256 x k / 64 <= 8 tiles per CTA) it
 // stays in shared memory instead: a pair then takes a contiguous run of work items (batch entry, row tile, column
 // tile; column tiles fastest), a tile of rhs is loaded when a batch entry first needs it and is reused by every row
 // tile of lhs, and only lhs streams through the remaining slots (0.64 GB instead of 1.07 GB from L2 per call at
-// lhs 2048 x 256, rhs 512 x 256, 256 batch entries).  Otherwise both operands stream through rings of six slots and
+// lhs 2048 x 256, rhs 512 x 256, 256 batch entries).  Otherwise both operands stream through rings of seven slots and
 // the pairs interleave (items pair, pair + pairs, ...), so that neighbours read the same tiles at the same time.
-// Measured on B200 at that shape: both modes take the same time (0.135 ms per call; the single-CTA kernel 0.174),
-// so L2 bandwidth is not what bounds this kernel; asking tiles into L2 two items ahead made it 13 % SLOWER, and
-// so did reading a warp's 64 accumulator columns with one wait instead of two (it spills).
+// Measured on B200 at that shape (ms per call; the single-CTA kernel: 0.174): both modes 0.134-0.139.  With the loads
+// switched off (timing experiment) 0.129 -> 0.094 and the SM clock rises from ~1.5-1.7 to 1.97 GHz: the part runs this
+// kernel at its power cap, and a good part of what the loads "cost" is clock.  Handing the accumulator back early
+// changes nothing.  What did not help: asking tiles into L2 two items ahead, by TMA prefetches from the loader (13 %
+// slower) or by plain prefetch instructions from a warp of its own (no change); rings of 4, 6 or 7 stages (within
+// 2 %); 128-row lhs tiles shared by two column tiles, which halves the bytes per stage but needs twice the MMA
+// instructions (0.154); reading a warp's 64 accumulator columns with one wait instead of two (0.141-0.145, spills).
 //
 // Organisation per CTA (both CTAs of a pair run the same roles on their own halves):
 //   warps 0-15  sampling epilogue: warp (quarter, part) owns accumulator lanes 32 quarter .. (32 mask columns) and
@@ -60,7 +64,7 @@ using pairspmm::wait_or_abort;
 
 constexpr int kTile = 256;                                // mask columns and rows of lhs per work item: 128 + 128 per pair
 constexpr int kCtaRows = 128;
-constexpr int kSlots = 12;                                // operand slots of 16 KiB per CTA
+constexpr int kSlots = 14;                                // operand slots of 16 KiB per CTA
 constexpr int kMaxResident = 8;                           // of them, at most this many hold a resident rhs
 constexpr int kEpiWarps = 16;                             // TMEM lane quarter = warp % 4, 64 tensor-memory columns = warp / 4
 constexpr int kLoadWarp = kEpiWarps;
@@ -72,10 +76,6 @@ constexpr int kBlockVecRows = 32;                         // vector-rows per pre
 constexpr int kPlanThreads = 512;
 constexpr int kMaxPlanColumns = 8192;                     // mask widths the plan kernel holds in shared memory
 constexpr int kSleepLoad = 32, kSleepMma = 0, kSleepEpilogue = 32;
-#ifndef VS_SDDMM_PREFETCH_ITEMS
-#define VS_SDDMM_PREFETCH_ITEMS 0
-#endif
-constexpr int kPrefetchItems = VS_SDDMM_PREFETCH_ITEMS;   // how many work items ahead the loader asks tiles into L2 (0: never)
 
 struct Smem {  // offsets from the 1024-byte aligned base; identical in both CTAs of a pair
     static constexpr int kOperands = 0;                   // kSlots slots: the ring of lhs tiles first, the rhs tiles behind it
@@ -302,16 +302,8 @@ sddmm_pair_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_l
             for (int i = 0; i < kMaxResident; ++i) last_use[i] = 0u;
             uint32_t used = 0;
             uint32_t g = 0;
-            // first touches come from HBM, further away than a short ring hides: the tiles of the item after the next
-            // are asked into L2 while this one is loaded (a resident rhs only with the first row tile of a batch entry)
-            ItemWalk far = walk;
-            for (int q = 0; q < kPrefetchItems; ++q) far.next();
             for (uint32_t i = 0; i < my_items && ok_run; ++i, walk.next()) {
-                const bool far_valid = kPrefetchItems > 0 && i + kPrefetchItems < my_items;
-                const bool far_rhs = far_valid && (!resident || far.mt() == 0);
                 for (int kb = 0; kb < k_blocks && ok_run; ++kb, ++g) {
-                    if (far_valid) tc::tma_prefetch_3d(&map_lhs, kb * kBlockK, far.mt() * kTile + (int)rank * kCtaRows, far.b);
-                    if (far_rhs) tc::tma_prefetch_3d(&map_rhs, kb * kBlockK, far.nt() * kTile + (int)rank * kCtaRows, far.b);
                     const uint32_t slot = g % ring;
                     if (g >= ring)   // the stage that used this ring slot before must have been multiplied
                         ok_run = wait_or_abort<kSleepLoad>(bar_done + 8 * slot, ((g - ring) / ring) & 1u, abort_flag, abort_addr, peer);
@@ -343,7 +335,6 @@ sddmm_pair_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_l
                         tc::tma_load_3d_pair(rhs_slots + rs * kOperandBytes, &map_rhs, bar, kb * kBlockK,
                                              walk.nt() * kTile + (int)rank * kCtaRows, walk.b);
                 }
-                if (kPrefetchItems > 0) far.next();
             }
             // the last "multiplied" signals addressed to this CTA must not arrive after it has gone
             const uint32_t tail0 = total_stages > ring ? total_stages - ring : 0u;
