@@ -130,11 +130,6 @@ __device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const void *tenso
         "l"(tensor_map), "r"(cluster_bar), "r"(x), "r"(y), "r"(z), "r"(w)
         : "memory");
 }
-// Asks for the same tile to be brought into L2 only.
-__device__ __forceinline__ void tma_prefetch_3d(const void *tensor_map, int x, int y, int z) {
-    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(tensor_map), "r"(x), "r"(y), "r"(z)
-                 : "memory");
-}
 // Tile store from this CTA's shared memory through a 3-D tensor map; elements outside the tensor are not
 // written.  Coordinates must not be negative and x * element size must be a multiple of 16 bytes.  Completion
 // is tracked per thread in bulk groups.
@@ -306,8 +301,7 @@ __device__ __forceinline__ void mma_f16_ss_pair(uint32_t d_tmem, uint64_t a_desc
         : "memory");
 }
 // Arrives once on the mbarrier at `cluster_addr` (this CTA's or, through map_to_cta, the other's) when every
-// pair MMA issued so far by this thread has completed.  One barrier per instruction: a pair of these, not a
-// cluster-wide broadcast, tells both CTAs.
+// pair MMA issued so far by this thread has completed: one barrier of one CTA (mma_commit_pair_both reaches both).
 __device__ __forceinline__ void mma_commit_pair(uint32_t cluster_addr) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
 }
@@ -356,28 +350,6 @@ __device__ __forceinline__ void tmem_ld_x32_issue(uint32_t taddr, uint32_t (&r)[
 __device__ __forceinline__ void tmem_ld_x32_wait(uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31]) : : "memory");
 }
-// One column: every lane of the warp reads column `taddr.column` of its own lane.  The column is an ordinary
-// (warp-uniform) register, which makes this the way to index an accumulator row dynamically without going through
-// shared memory.  Issued without a wait; tmem_ld_wait8 names up to eight destinations.
-__device__ __forceinline__ void tmem_ld_x1_issue(uint32_t taddr, uint32_t &r) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait8(uint32_t (&r)[8]) {
-    asm volatile("tcgen05.wait::ld.sync.aligned;"
-                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7])
-                 :
-                 : "memory");
-}
-// 64 columns: two loads in flight, one wait.
-__device__ __forceinline__ void tmem_ld_x64(uint32_t taddr, uint32_t (&r)[64]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%64];\n"
-                 "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%65];\n"
-                 "tcgen05.wait::ld.sync.aligned;"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
-                 : "r"(taddr), "r"(taddr + 32)
-                 : "memory");
-}
-
 // Zeroes 32 consecutive 32-bit columns of each of the warp's TMEM lanes (asynchronous: see tmem_st_wait).
 __device__ __forceinline__ void tmem_st_zero_x32(uint32_t taddr) {
     const uint32_t z = 0;
