@@ -145,3 +145,13 @@ def test_a_column_named_twice_in_a_vector_row(V, monkeypatch):
     want = sddmm_oracle(dup, 64, lhs, rhs)
     for out_t in (torch.float16, torch.float32):
         assert_close(run(dup, 64, lhs, rhs, out_t, True, monkeypatch), want, f"repeated columns V={V}")
+
+
+def test_masks_wider_than_the_plan_holds_fall_back_to_the_single_cta_kernel(monkeypatch):
+    """Mask widths above 8192 columns (the plan kernel keeps a block's cells in shared memory) run the single-CTA
+    kernel: same results as with the pair kernel switched off."""
+    a = problem(cvse.GEN_BETA, 9, 256 // 8, 8448, 8, 0.97)
+    lhs, rhs = operands(a, 128, 4)
+    wide = run(a, 128, lhs, rhs, torch.float16, True, monkeypatch)
+    assert_close(wide, sddmm_oracle(a, 128, lhs, rhs), "mask of 8448 columns")
+    assert np.array_equal(wide, run(a, 128, lhs, rhs, torch.float16, False, monkeypatch))
