@@ -147,6 +147,99 @@ __global__ void __launch_bounds__(kCcThreads) sddmm_cc_kernel(const SddmmParams 
     }
 }
 
+// The same product with the V rows of lhs kept in registers: L lanes (8, 16 or 32) share one VECTOR-ROW, lane g holds
+// the 16-byte chunk g of each of its V lhs rows (contraction lengths of up to L chunks), and the group walks the
+// vector-row's mask entries: per entry one 16-byte load of the rhs row per lane, V x E FMAs and a folding reduction
+// over the L lanes (each step halves the values a lane still carries: 9 shuffles for V = 8, L = 32, where a plain
+// butterfly needs 40), after which lane g holds the sum of real row g >> log2(L / V).  Against the kernel above,
+// which re-reads the V lhs rows for every entry, this moves a ninth of the bytes through L1.
+template <typename TIn, typename TOut, int V, int L>
+__global__ void __launch_bounds__(kCcThreads) sddmm_cc_row_kernel(const SddmmParams p) {
+    constexpr int E = Chunk<TIn>::kElems;
+    static_assert(L >= 8 && L <= 32 && V <= L, "group size");
+    const int g = threadIdx.x & (L - 1);
+    const int64_t order = ((int64_t)blockIdx.x * kCcThreads + threadIdx.x) / L;
+    const bool live = order < p.m_vec;
+    const int row = live ? __ldg(p.row_indices + order) : 0;
+    const int b = blockIdx.y;
+    const int chunks = p.k / E;
+    const bool mine = g < chunks;   // lanes past the contraction length contribute zeros
+
+    const TIn *lhs = static_cast<const TIn *>(p.lhs) + (int64_t)b * p.stride_lhs + (int64_t)row * V * p.k + g * E;
+    const TIn *rhs = static_cast<const TIn *>(p.rhs) + (int64_t)b * p.stride_rhs + g * E;
+    TOut *out = static_cast<TOut *>(p.out) + (int64_t)b * p.stride_out;
+
+    float l[V][E];
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+        if (live && mine) {
+            Chunk<TIn> c;
+            c.load(lhs + (int64_t)v * p.k);
+#pragma unroll
+            for (int e = 0; e < E; ++e) l[v][e] = c.f[e];
+        } else {
+#pragma unroll
+            for (int e = 0; e < E; ++e) l[v][e] = 0.f;
+        }
+    }
+    int j = live ? min(max(__ldg(p.row_offsets + row), 0), p.nnz_vec) : 0;
+    const int end = live ? min(max(__ldg(p.row_offsets + row + 1), j), p.nnz_vec) : 0;
+    // the groups of a warp walk rows of different lengths: the loop runs to the longest, shorter rows idle.  Four
+    // entries per trip, so that four gathers of rhs are in flight; the column indices of a trip are loaded one trip ahead.
+    constexpr int U = 4;
+    int trips = (end - j + U - 1) / U;
+#pragma unroll
+    for (int d = 16; d >= L; d >>= 1) trips = max(trips, __shfl_xor_sync(0xffffffffu, trips, d));
+    int col[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) col[u] = j + u < end ? __ldg(p.col_indices + j + u) : 0;
+    for (int it = 0; it < trips; ++it, j += U) {
+        Chunk<TIn> r[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (j + u < end && mine) {
+                r[u].load(rhs + (int64_t)col[u] * p.k);
+            } else {
+#pragma unroll
+                for (int e = 0; e < E; ++e) r[u].f[e] = 0.f;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) col[u] = j + U + u < end ? __ldg(p.col_indices + j + U + u) : 0;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            float acc[V];
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                acc[v] = 0.f;
+#pragma unroll
+                for (int e = 0; e < E; ++e) acc[v] = fmaf(l[v][e], r[u].f[e], acc[v]);
+            }
+            // folding reduction over the L lanes of the group
+            int n = V;
+#pragma unroll
+            for (int d = L / 2; d >= 1; d >>= 1) {
+                if (n > 1) {
+                    const bool upper = (g & d) != 0;
+#pragma unroll
+                    for (int i = 0; i < V / 2; ++i) {
+                        if (i < n / 2) {
+                            const float send = upper ? acc[i] : acc[i + n / 2];
+                            const float keep = upper ? acc[i + n / 2] : acc[i];
+                            acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, d);
+                        }
+                    }
+                    n >>= 1;
+                } else {
+                    acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], d);
+                }
+            }
+            // lane g now holds the sum of real row g / (L / V) of the vector-row; the first lane of each run stores it
+            if (j + u < end && (g & (L / V - 1)) == 0) store_scalar(out + (int64_t)(j + u) * V + g / (L / V), acc[0]);
+        }
+    }
+}
+
 // ---- masked row softmax -----------------------------------------------------------------------------------
 // One warp per vector-row: lanes stride over the row's entries, each entry carrying the V real rows, so the V
 // softmaxes of a vector-row run side by side on contiguous vector loads.  fp32 arithmetic.  Rows of up to

@@ -527,7 +527,24 @@ template <typename TOut> int spmm_tc_by_v(int V, const SpmmParams &p, cudaStream
 }
 
 // ---- SDDMM dispatch ---------------------------------------------------------------------------------------
+// CUDA-core SDDMM: a group of lanes per vector-row with the lhs rows in registers when the contraction length fits
+// 32 chunks of 16 bytes (k <= 256 in fp16, 128 in fp32), a group of eight lanes per mask entry otherwise.
+// VSPARSE_B200_SDDMM_CC=entry keeps the latter.
+template <typename TIn, typename TOut, int V, int L> int launch_sddmm_cc_row(const SddmmParams &p, cudaStream_t s) {
+    const int64_t blocks = ((int64_t)p.m_vec * L + kCcThreads - 1) / kCcThreads;
+    if (blocks > 0x7fffffffll) return VS_ERR_SHAPE;
+    dim3 grid((unsigned)blocks, (unsigned)p.batch, 1);
+    sddmm_cc_row_kernel<TIn, TOut, V, L><<<grid, kCcThreads, 0, s>>>(p);
+    return (int)cudaGetLastError();
+}
 template <typename TIn, typename TOut, int V> int launch_sddmm_cc(const SddmmParams &p, cudaStream_t s) {
+    const int chunks = p.k / Chunk<TIn>::kElems;
+    const char *e = std::getenv("VSPARSE_B200_SDDMM_CC");
+    if (chunks >= 1 && chunks <= 32 && p.m_vec > 0 && !(e && !std::strcmp(e, "entry"))) {
+        if (chunks > 16) return launch_sddmm_cc_row<TIn, TOut, V, 32>(p, s);
+        if (chunks > 8) return launch_sddmm_cc_row<TIn, TOut, V, 16>(p, s);
+        return launch_sddmm_cc_row<TIn, TOut, V, 8>(p, s);
+    }
     const int64_t blocks = ((int64_t)p.nnz_vec * 8 + kCcThreads - 1) / kCcThreads;
     if (blocks > 0x7fffffffll) return VS_ERR_SHAPE;
     dim3 grid((unsigned)blocks, (unsigned)p.batch, 1);
