@@ -101,10 +101,16 @@ def kernels_per_step(w, a=None):
     if w["op"] == "spmm":
         return ["spmm_cc_kernel"]
     if not tensor:
-        return ["sddmm_cc_kernel"]
+        # a group of lanes per vector-row while the contraction length fits 32 chunks of 16 bytes, per mask entry beyond
+        by_row = w["N"] // 8 <= 32 and os.environ.get("VSPARSE_B200_SDDMM_CC") != "entry"
+        return ["sddmm_cc_row_kernel" if by_row else "sddmm_cc_kernel"]
     from vectorsparse_b200 import _lib
     dense = a is not None and _lib.lib().vs_sddmm_formulation(a.m_vec, w["N"], w["K"], a.nnz_vec, w["V"]) == 1
-    return ["sddmm_plan_kernel", "sddmm_pair_kernel"] if dense else ["sddmm_tma_kernel"]
+    if not dense:
+        return ["sddmm_tma_kernel"]
+    if os.environ.get("VSPARSE_B200_SDDMM_PAIR") == "0":
+        return ["sddmm_plan_kernel", "sddmm_dense_kernel"]
+    return ["sddmm_cell_plan_kernel", "sddmm_pair_kernel", "sddmm_twin_kernel (returns at once unless a vector-row names a column twice)"]
 
 
 def config_of(name, w, a):
