@@ -272,6 +272,14 @@ int vs_set_workspace(void *workspace, int64_t bytes);
  * calling thread is meant: each host thread has its own.  No counterpart in the reference. */
 int vs_release_scratch(void *stream, int every_stream);
 
+/* Times the multiplying kernels of the dense tensor-core paths (the pair kernels of SpMM, the transposed product and
+ * SDDMM) with CUDA events on their own streams.  enable != 0 switches the bracketing on for the calls that follow,
+ * 0 off; either way the call first waits for the kernels bracketed so far and returns the sum of their durations
+ * and their number (either pointer may be NULL), then forgets them.  A bracketed kernel does not overlap its
+ * neighbours in the stream, so a call is slower while this is on: it measures the kernel, not the call.
+ * Diagnostic, no counterpart in the reference. */
+int vs_kernel_timing(int enable, double *total_ms, int *launches);
+
 /* Measures the fp32 fused-multiply-add throughput of the current device (TFLOP/s, 2 flops per FMA) with a
  * register-only kernel: the roofline denominator for the fp32 CUDA-core SpMM, which is bound by FMA issue and not by
  * memory.  Synchronous (times three short launches on the legacy default stream and returns the best); diagnostic,

@@ -120,3 +120,18 @@ def test_transposed_product_by_pairs(V, monkeypatch):
         assert ops.device_status() == 0
         outs.append(out.cpu().numpy())
         assert_close(outs[-1], want, f"transposed, pairs={pair}, V={V}")
+
+
+def test_kernel_timing_brackets_the_multiplying_kernel(monkeypatch):
+    """vs_kernel_timing: one pair of events per multiplying kernel while it is on, none after it is switched off, and
+    the results are the same either way."""
+    a = problem(cvse.GEN_BETA, 8, 1024 // 8, 256, 8, 0.9)
+    vals, B = spmm_inputs(a, 256, np.float16, 5, sigma=0.5)
+    plain = run(a, 256, vals, B, torch.float16, True, monkeypatch)
+    ops.kernel_timing(True)
+    timed = [run(a, 256, vals, B, torch.float16, True, monkeypatch) for _ in range(3)]
+    ms, n = ops.kernel_timing(False)
+    assert n == 3 and 0.0 < ms < 50.0
+    assert all(np.array_equal(t, plain) for t in timed)
+    run(a, 256, vals, B, torch.float16, True, monkeypatch)
+    assert ops.kernel_timing(False) == (0.0, 0)

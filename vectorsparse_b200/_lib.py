@@ -49,6 +49,7 @@ SIGNATURES = {
     "vs_sddmm_host": (_i, [_i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
     "vs_device_status": (_i, [_i, C.POINTER(C.c_uint32)]),
     "vs_measure_fp32_fma": (_i, [C.POINTER(C.c_double)]),
+    "vs_kernel_timing": (_i, [_i, C.POINTER(C.c_double), C.POINTER(C.c_int)]),
     "vs_sddmm_formulation": (_i, [_i, _i, _i, _i, _i]),
     "vs_spmm_workspace_bytes": (_i64, [_i, _i, _i, _i, _i64]),
     "vs_sddmm_workspace_bytes": (_i64, [_i, _i, _i]),

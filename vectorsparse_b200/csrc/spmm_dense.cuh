@@ -174,24 +174,49 @@ dense_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__rest
     for (int i = t; i <= nr; i += kPlanThreads) roff[i] = offset_of(r0 + i);
     __syncthreads();
     const int j0 = roff[0], j1 = roff[nr];
-    for (int j = j0 + t; j < j1; j += kPlanThreads) {
-        const int c = column_of(j);
-        if ((unsigned)c < (unsigned)K) atomicAdd(hist + c / kPlanCols, 1);
+    // four entries per thread and trip, so that their loads are in flight together (a group of the transposed matrix
+    // is thousands of entries for one CTA)
+    for (int jb = j0 + t; jb < j1; jb += 4 * kPlanThreads) {
+        int c[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) c[u] = jb + u * kPlanThreads < j1 ? column_of(jb + u * kPlanThreads) : -1;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if ((unsigned)c[u] < (unsigned)K) atomicAdd(hist + c[u] / kPlanCols, 1);
     }
     __syncthreads();
-    if (t == 0) {
+    if (t < 32) {   // exclusive scan of the histogram by one warp, 32 buckets per trip
         int run = j0;
         int32_t *o = blk_offsets + (int64_t)g * (plan_blocks + 1);
-        for (int c = 0; c < plan_blocks; ++c) {
-            cursor[c] = run;
-            o[c] = run;
-            run += hist[c];
+        for (int c0 = 0; c0 < plan_blocks; c0 += 32) {
+            const int h = c0 + t < plan_blocks ? hist[c0 + t] : 0;
+            int incl = h;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, incl, d);
+                if (t >= d) incl += up;
+            }
+            if (c0 + t < plan_blocks) {
+                cursor[c0 + t] = run + incl - h;
+                o[c0 + t] = run + incl - h;
+            }
+            run += __shfl_sync(0xffffffffu, incl, 31);
         }
-        o[plan_blocks] = run;
+        if (t == 0) o[plan_blocks] = run;
     }
     __syncthreads();
-    for (int j = j0 + t; j < j1; j += kPlanThreads) {
-        const int c = column_of(j);
+    for (int jb = j0 + t; jb < j1; jb += 4 * kPlanThreads) {
+        int cc[4], vv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int jj = jb + u * kPlanThreads;
+            cc[u] = jj < j1 ? column_of(jj) : -1;
+            vv[u] = jj < j1 ? value_of(jj) : 0;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+        const int j = jb + u * kPlanThreads;
+        const int c = cc[u];
         if ((unsigned)c >= (unsigned)K) continue;
         int lo = 0, hi = nr;   // vector-row of j: the last i with roff[i] <= j (empty rows share an offset)
         while (hi - lo > 1) {
@@ -199,7 +224,8 @@ dense_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *__rest
             if (roff[mid] <= j) lo = mid; else hi = mid;
         }
         const int pos = atomicAdd(cursor + c / kPlanCols, 1);
-        blk_entries[pos] = make_uint2((uint32_t)value_of(j), ((uint32_t)lo << 6) | (uint32_t)(c & (kBlockK - 1)));
+        blk_entries[pos] = make_uint2((uint32_t)vv[u], ((uint32_t)lo << 6) | (uint32_t)(c & (kBlockK - 1)));
+        }
     }
 }
 

@@ -18,6 +18,7 @@
 #include <functional>
 #include <unordered_map>
 #include <utility>
+#include <vector>
 
 #include "vsparse_b200.h"
 #include "common.cuh"
@@ -191,6 +192,37 @@ cudaError_t launch_pairs(void (*kernel)(Exp...), unsigned pairs, unsigned block,
     cfg.numAttrs = (overlapped && overlap) ? 2 : 1;
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Act>(args)...);
 }
+
+// Diagnostic: CUDA events around the multiplying kernels of the dense tensor-core paths (vs_kernel_timing).  Off by
+// default; while on, every such kernel is bracketed by two events on its stream, which also keeps it from
+// overlapping the kernels before and behind it (it is timed alone, as a profiler's launch list shows it).
+struct KernelTiming {
+    std::mutex lock;
+    bool on = false;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pairs;
+};
+KernelTiming &kernel_timing() {
+    static KernelTiming t;
+    return t;
+}
+struct TimedLaunch {   // records the opening event on construction, the closing one on destruction
+    cudaStream_t s;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    explicit TimedLaunch(cudaStream_t stream) : s(stream) {
+        KernelTiming &t = kernel_timing();
+        std::lock_guard<std::mutex> g(t.lock);
+        if (!t.on) return;
+        if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) { e0 = e1 = nullptr; (void)cudaGetLastError(); return; }
+        cudaEventRecord(e0, s);
+    }
+    ~TimedLaunch() {
+        if (!e0) return;
+        cudaEventRecord(e1, s);
+        KernelTiming &t = kernel_timing();
+        std::lock_guard<std::mutex> g(t.lock);
+        t.pairs.emplace_back(e0, e1);
+    }
+};
 
 // cuTensorMapEncodeTiled, fetched from the driver at first use (the library does not link libcuda).
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -450,6 +482,7 @@ bool launch_spmm_pair(const SpmmParams &q, cudaStream_t s, DeviceInfo *d, const 
     const int n_tiles = q.N / tn;
     const int64_t items = (int64_t)q.batch * n_tiles * m_tiles;
     const unsigned pairs = (unsigned)(items < resident[dev] ? items : resident[dev]);
+    TimedLaunch timed(s);
     *rc_out = (int)launch_pairs(kernel, pairs, pairspmm::kThreads, (size_t)pairspmm::kSmemBytes, s, true, q, map, map_out, map_b2, tn,
                                 blk_offsets, blk_entries, m_tiles, n_tiles, k_blocks, d->status, flag, checks);
     return true;
@@ -681,6 +714,7 @@ template <typename TOut, int V> bool launch_sddmm_pair(const SddmmParams &p, cud
         // rhs of a batch entry fits the resident slots (VSPARSE_B200_SDDMM_RESIDENT=0: stream both operands anyway)
         const char *res_env = std::getenv("VSPARSE_B200_SDDMM_RESIDENT");
         const int resident = (n_tiles * (p.k / densesddmm::kBlockK) <= pairsddmm::kMaxResident && !(res_env && !std::strcmp(res_env, "0"))) ? 1 : 0;
+        TimedLaunch timed(s);
         rc = (int)launch_pairs(kernel, pairs, pairsddmm::kThreads, (size_t)pairsddmm::kSmemBytes, s, true, p, map_l, map_r, cells, order,
                                blocks, m_tiles, n_tiles, resident, d->status);
     }
@@ -1323,6 +1357,29 @@ VS_EXPORT int vs_sddmm_formulation(int m_vec, int k, int n, int nonzeros_vec, in
     SddmmParams p{};
     p.m_vec = m_vec; p.k = k; p.n = n; p.nnz_vec = nonzeros_vec;
     return sddmm_use_dense(p, vec_length) ? 1 : 0;
+}
+
+VS_EXPORT int vs_kernel_timing(int enable, double *total_ms, int *launches) {
+    KernelTiming &t = kernel_timing();
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> done;
+    {
+        std::lock_guard<std::mutex> g(t.lock);
+        done.swap(t.pairs);
+        t.on = enable != 0;
+    }
+    double ms = 0.0;
+    int n = 0, rc = VS_OK;
+    for (auto &pr : done) {
+        float x = 0.0f;
+        cudaError_t e = cudaEventSynchronize(pr.second);
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&x, pr.first, pr.second);
+        if (e == cudaSuccess) { ms += x; ++n; } else { rc = (int)e; (void)cudaGetLastError(); }
+        cudaEventDestroy(pr.first);
+        cudaEventDestroy(pr.second);
+    }
+    if (total_ms) *total_ms = ms;
+    if (launches) *launches = n;
+    return rc;
 }
 
 VS_EXPORT int vs_measure_fp32_fma(double *tflops) {

@@ -297,6 +297,15 @@ def device_status(clear: bool = True) -> int:
     return int(v.value)
 
 
+def kernel_timing(enable: bool):
+    """Switches the event bracketing of the dense tensor-core multiplying kernels on or off and returns
+    (total milliseconds, launches) of the kernels bracketed since the last call (synchronous)."""
+    import ctypes as C
+    ms, n = C.c_double(0.0), C.c_int(0)
+    _lib.check(_lib.lib().vs_kernel_timing(1 if enable else 0, C.byref(ms), C.byref(n)), "vs_kernel_timing")
+    return float(ms.value), int(n.value)
+
+
 def measure_fp32_fma() -> float:
     """fp32 FMA throughput of the current device in TFLOP/s (a register-only probe kernel; synchronous)."""
     import ctypes as C
