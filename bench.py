@@ -44,6 +44,18 @@ WORKLOADS = {
     "spmm_v8_s50": dict(op="spmm", M=2048, K=512, V=8, s=0.5, N=256, inst=256, kind="beta"),
     "spmm_v8_s90_n128": dict(op="spmm", M=2048, K=512, V=8, s=0.9, N=128, inst=256, kind="beta"),
     "spmm_v8_s90_n64": dict(op="spmm", M=2048, K=512, V=8, s=0.9, N=64, inst=256, kind="beta"),
+    # the sparsity sweep of configs 2 and 3 at V = 8 (0.5 and 0.9 are above and below)
+    "spmm_v8_s70": dict(op="spmm", M=2048, K=512, V=8, s=0.7, N=256, inst=256, kind="beta"),
+    "spmm_v8_s80": dict(op="spmm", M=2048, K=512, V=8, s=0.8, N=256, inst=256, kind="beta"),
+    "spmm_v8_s95": dict(op="spmm", M=2048, K=512, V=8, s=0.95, N=256, inst=256, kind="beta"),
+    "spmm_v8_s98": dict(op="spmm", M=2048, K=512, V=8, s=0.98, N=256, inst=256, kind="beta"),
+    "sddmm_v8_s50": dict(op="sddmm", M=2048, K=512, V=8, s=0.5, N=256, inst=256, kind="beta"),
+    "sddmm_v8_s70": dict(op="sddmm", M=2048, K=512, V=8, s=0.7, N=256, inst=256, kind="beta"),
+    "sddmm_v8_s80": dict(op="sddmm", M=2048, K=512, V=8, s=0.8, N=256, inst=256, kind="beta"),
+    "sddmm_v8_s95": dict(op="sddmm", M=2048, K=512, V=8, s=0.95, N=256, inst=256, kind="beta"),
+    "sddmm_v8_s98": dict(op="sddmm", M=2048, K=512, V=8, s=0.98, N=256, inst=256, kind="beta"),
+    "sddmm_v4_s90": dict(op="sddmm", M=2048, K=512, V=4, s=0.9, N=256, inst=256, kind="beta"),
+    "sddmm_v2_s90": dict(op="sddmm", M=2048, K=512, V=2, s=0.9, N=256, inst=256, kind="beta"),
     "spmm_v4_s90": dict(op="spmm", M=2048, K=512, V=4, s=0.9, N=256, inst=256, kind="beta"),
     "spmm_v2_s90": dict(op="spmm", M=2048, K=512, V=2, s=0.9, N=256, inst=256, kind="beta"),
     "sddmm_v8_s90": dict(op="sddmm", M=2048, K=512, V=8, s=0.9, N=256, inst=256, kind="beta"),
@@ -307,11 +319,18 @@ def run_ours(args):
         k = N
         h_a = torch.from_numpy(cvse.fill_random((inst, M, k), np.float16, cvse.DIST_NORMAL, seed, 1.0)).pin_memory()
         h_b = torch.from_numpy(cvse.fill_random((inst, K, k), np.float16, cvse.DIST_NORMAL, seed + 1, 1.0)).pin_memory()
-        h_out = torch.empty((inst, a.nnz_vec * V), dtype=torch.float16).pin_memory()
-        d_out = torch.empty((inst, a.nnz_vec * V), dtype=torch.float16, device=dev)
+        row = (a.nnz_vec * V + 7) // 8 * 8  # per-instance stride kept 16-byte aligned for every V
+        h_out = torch.empty((inst, row), dtype=torch.float16).pin_memory()
+        d_out = torch.empty((inst, row), dtype=torch.float16, device=dev)
 
         def launch(d_a, d_b, out):
-            ops.sddmm_batched(path, a.m_vec, k, K, a.nnz_vec, ri, ro, ci, d_a, d_b, out, V)
+            # through the C ABI directly: the Python wrapper takes contiguous [B, nnz] outputs only
+            from vectorsparse_b200 import _lib
+            with torch.cuda.device(dev):
+                rc = _lib.lib().vs_sddmm_batched(path, 0, 0, a.m_vec, k, K, a.nnz_vec, ri.data_ptr(), ro.data_ptr(), ci.data_ptr(),
+                                                 d_a.data_ptr(), d_b.data_ptr(), out.data_ptr(), V, inst, M * k, K * k, row,
+                                                 torch.cuda.current_stream().cuda_stream, 1)
+            _lib.check(rc, "vs_sddmm_batched")
     d_a = h_a.to(dev)
     d_b = h_b.to(dev)
 

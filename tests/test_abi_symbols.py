@@ -107,7 +107,8 @@ def test_sddmm_formulation_choice(monkeypatch):
     f = _lib.lib().vs_sddmm_formulation
     monkeypatch.delenv("VSPARSE_B200_SDDMM", raising=False)
     assert f(256, 256, 512, 12685, 8) == 1        # 90 % sparse, k = 256: dense tiles
-    assert f(256, 256, 512, 600, 8) == 0          # 99.5 % sparse: gather
+    assert f(256, 256, 512, 600, 8) == 1          # 99.5 % sparse, narrow mask: the gather kernel's cost per vector-row still exceeds 16 dense tiles
+    assert f(256, 256, 8192, 256 * 82, 8) == 0    # 99 % sparse and 8192 columns wide: 256 dense tiles for 21 K entries: gather
     assert f(512, 64, 4096, 209920, 8) == 0       # attention, head dimension 64: the sampling pass would dominate
     assert f(256, 256, 512, 12685, 1) == 0        # no tensor path at V = 1
     assert f(0, 256, 512, 0, 8) == 0

@@ -13,6 +13,7 @@
 #include <cstdlib>
 #include <algorithm>
 #include <cstring>
+#include <cmath>
 #include <mutex>
 #include <thread>
 #include <functional>
@@ -637,22 +638,22 @@ template <typename TOut, int V> int launch_sddmm_gather(const SddmmParams &p, cu
     return (int)cudaGetLastError();
 }
 
-// Which tensor-core SDDMM runs: dense 256 x 128 tiles of lhs . rhs^T sampled at the mask cost the same whatever
-// the sparsity but at least an epilogue pass per tile; the gather kernel is proportional to the mask entries.
-// The number of entries is an argument here, so the choice is made on the host (cycles per SM, measured):
-// ~7 per mask entry and 64 contraction elements for the gather kernel; per tile, ~800 per 64 contraction
-// elements (operand traffic through L2 included) and not less than ~2500 (the sampling pass) for the dense one.
+// Which tensor-core SDDMM runs: dense tiles of lhs . rhs^T sampled at the mask cost the same whatever the sparsity,
+// the gather kernel a fixed amount per vector-row plus a little per mask entry.  The number of entries is an argument
+// here, so the choice is made on the host, in SM-cycles per product, fitted to measurements on B200 (lhs 2048 x 256,
+// rhs 512 x 256, 90 % and 98 % sparse; 4096 x 4096 masks of 410 entries per row at k = 64): gather ~306 per vector-row
+// and 64 contraction elements + ~4 per entry; dense ~2230 per 256 x 256 tile and 64 contraction elements over the two
+// SMs of a pair, and not less than ~4250 per tile (reading the accumulator out).
 // VSPARSE_B200_SDDMM = "dense" | "gather" (read at every call) forces one.
 bool sddmm_use_dense(const SddmmParams &p, int V) {
     const char *e = std::getenv("VSPARSE_B200_SDDMM");
     if (e && !std::strcmp(e, "dense")) return true;
     if (e && !std::strcmp(e, "gather")) return false;
-    const double density = (double)p.nnz_vec / ((double)p.m_vec * (double)p.n);
-    const double entries_per_tile = (double)(densesddmm::kTileM / V) * densesddmm::kTileN * density;
     const double k_blocks = (double)(p.k / densesddmm::kBlockK);
-    const double gather = entries_per_tile * k_blocks * 7.0;
-    const double dense = std::max(k_blocks * 800.0, 2500.0);
-    return dense * 1.25 < gather;
+    const double tiles = std::ceil((double)p.m_vec * V / 256.0) * std::ceil((double)p.n / 256.0);
+    const double gather = (double)p.m_vec * 306.0 * k_blocks + (double)p.nnz_vec * 4.0;
+    const double dense = tiles * std::max(2230.0 * k_blocks, 4250.0);
+    return dense * 1.1 < gather;
 }
 
 // The dense SDDMM by pairs of CTAs (sddmm_pair.cuh) serves masks of up to pairsddmm::kMaxPlanColumns columns whose
