@@ -380,6 +380,7 @@ sddmm_pair_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_l
         // rows 64 part .. + 63 of the lhs tile = 64 / V vector-rows, read by two 32-column loads of 32 / V vector-rows
         // each.  All of them lie in one block of 32 vector-rows, so the lane needs ONE cell per work item.
         constexpr int kPerLoad = 32 / V;                 // vector-rows per 32-column load
+        constexpr bool kAheadEntries = 2 * kPerLoad <= 16;   // hold the next item's entry indices as well
         constexpr int kElems = 16 / (int)sizeof(TOut);   // outputs per 16-byte store
         const int quarter = warp & 3, part = warp >> 2;
         const uint32_t lane_taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(part * 64);
@@ -408,7 +409,7 @@ sddmm_pair_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_l
         ahead = walk;
         int bit0, n_bit0, f_bit0;
         uint32_t bits, n_bits;
-        int ent[2 * kPerLoad], n_ent[2 * kPerLoad];
+        int ent[2 * kPerLoad], n_ent[kAheadEntries ? 2 * kPerLoad : 1];
         uint2 n_cell, f_cell;
         {
             const uint2 c_cell = cell_of(ahead, my_items > 0, bit0);
@@ -419,10 +420,11 @@ sddmm_pair_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_l
         bool ok_run = true;
         for (uint32_t i = 0; i < my_items && ok_run; ++i, walk.next()) {
             const uint32_t buf = i & 1u;
-            // requested now: the cell of item i + 2 and the entry indices of item i + 1 (its cell was requested an item ago)
+            // requested now: the cell of item i + 2 and the entry indices of item i + 1 (its cell was requested an item ago);
+            // at V = 2 a lane may have 32 entries per item, too many to hold for two items: they are fetched when needed
             ahead.next();
             f_cell = cell_of(ahead, i + 2 < my_items, f_bit0);
-            entries_of(n_cell, n_bit0, n_bits, n_ent);
+            if constexpr (kAheadEntries) entries_of(n_cell, n_bit0, n_bits, n_ent);
 
             ok_run = __all_sync(0xffffffffu, wait_or_abort<kSleepEpilogue>(bar_acc_full + 8 * buf, (i >> 1) & 1u, abort_flag, abort_addr, peer));
             if (!ok_run) break;
@@ -470,9 +472,13 @@ sddmm_pair_kernel(const SddmmParams p, const __grid_constant__ CUtensorMap map_l
             tc::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) tc::mbar_arrive_remote(acc_empty_first + 8 * buf);   // sampled: the buffer is free for the pair
-            bits = n_bits;
+            if constexpr (kAheadEntries) {
+                bits = n_bits;
 #pragma unroll
-            for (int b = 0; b < 2 * kPerLoad; ++b) ent[b] = n_ent[b];
+                for (int b = 0; b < 2 * kPerLoad; ++b) ent[b] = n_ent[b];
+            } else {
+                entries_of(n_cell, n_bit0, bits, ent);
+            }
             n_cell = f_cell; n_bit0 = f_bit0;
         }
     }
