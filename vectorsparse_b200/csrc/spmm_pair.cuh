@@ -64,7 +64,6 @@ constexpr int kEpiWarps = 8;                              // TMEM lane quarter =
 constexpr int kFillWarp0 = kEpiWarps;
 constexpr int kFillPerSlot = kBlockK / kFillCols;         // warps per CTA and stage
 constexpr int kFillWarps = kAStages * kFillPerSlot;       // 12: warp f fills A slot f % kAStages
-constexpr int kFillBatches = 2;                           // batches of 32 entries a fill warp keeps in flight
 constexpr int kOverflowBatches = 4;
 constexpr int kLoadWarp = kFillWarp0 + kFillWarps;        // 20
 constexpr int kMmaWarp = kLoadWarp + 1;
@@ -221,6 +220,8 @@ spmm_pair_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b, 
         // of the stage) into the A slot, after taking out what it dropped there for the stage kAStages earlier: a
         // place in the tile is only ever written by the one warp that owns its bucket.  All of them tell the FIRST
         // CTA's barrier.
+        // batches of 32 entries a fill warp keeps in flight: a bucket holds 8 / V times as many entries at shorter vectors
+        constexpr int kFillBatches = V == 8 ? 2 : 4;
         const int fw = warp - kFillWarp0;
         const uint32_t a_slot = (uint32_t)(fw % kAStages);
         const int quarter_k = fw / kAStages;
