@@ -280,22 +280,20 @@ spmm_pair_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap map_b, 
                 ok_run = wait_or_abort<kSleepFill>(bar_done + 8 * (prev % kBarStages), (prev / kBarStages) & 1u, abort_flag, abort_addr, peer);
             }
             if (!ok_run) break;
-            {   // back to zeros: overwrite exactly the vectors this warp dropped into the slot last time
+            if (p_e1 - (p_e0 - lane) > kStride * kFillBatches) {   // warp-uniform
+                // back to zeros, denser buckets: the positions beyond the ones kept in registers would have to be
+                // loaded again; clearing the warp's whole region (its 32 columns are 4 KiB in each 64-row atom) with
+                // 16 wide stores per lane is cheaper and waits for nothing
+#pragma unroll
+                for (int atom = 0; atom < kCtaRows / 64; ++atom)
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        *reinterpret_cast<uint4 *>(a_part + atom * 8192 + quarter_k * 4096 + (i * 32 + lane) * 16) = make_uint4(0, 0, 0, 0);
+            } else {   // back to zeros: overwrite exactly the vectors this warp dropped into the slot last time
                 typename ValueVec<V>::Raw zero{};
 #pragma unroll
                 for (int u = 0; u < kFillBatches; ++u)
                     if (p_e0 + kStride * u < p_e1) scatter_vector<V, kTransposed>(a_part, p_pos[u], zero);
-                for (int e0 = p_e0 + kStride * kFillBatches; e0 - lane < p_e1; e0 += kStride * kOverflowBatches) {
-                    uint32_t pos[kOverflowBatches];
-#pragma unroll
-                    for (int u = 0; u < kOverflowBatches; ++u) {
-                        const int e = e0 + kStride * u;
-                        pos[u] = e < p_e1 ? __ldg(blk_entries + e).y : 0u;
-                    }
-#pragma unroll
-                    for (int u = 0; u < kOverflowBatches; ++u)
-                        if (e0 + kStride * u < p_e1) scatter_vector<V, kTransposed>(a_part, pos[u], zero);
-                }
             }
             __syncwarp();
 #pragma unroll
