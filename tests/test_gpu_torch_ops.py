@@ -55,3 +55,28 @@ def test_autograd_through_fixed_mask_attention():
         assert_close(tq.grad[h].float().cpu().numpy(), wq, f"dQ, head {h}")
         assert_close(tk.grad[h].float().cpu().numpy(), wk, f"dK, head {h}")
         assert_close(tv.grad[h].float().cpu().numpy(), wv, f"dV, head {h}")
+
+
+@pytest.mark.parametrize("batched", [False, True])
+def test_autograd_through_the_sparse_dense_product(batched):
+    """C = A @ B: the gradient of B is the product with the transposed matrix, the gradient of the values the sampled
+    dense-dense product; both against the fp64 oracle (shared values with a batched B: summed over the batch)."""
+    V, N, K = 8, 128, 192
+    a = problem(cvse.GEN_BETA, 14, 256 // V, K, V, 0.8)
+    mask = torch_ops.AttentionMask(a, DEV)
+    vals = cvse.fill_random((a.nnz_vec * V,), np.float16, cvse.DIST_NORMAL, 1, 0.25)
+    shape = (3, K, N) if batched else (K, N)
+    B = cvse.fill_random(shape, np.float16, cvse.DIST_NORMAL, 2, 0.5)
+    G = cvse.fill_random(shape[:-2] + (a.m, N), np.float16, cvse.DIST_NORMAL, 3, 0.25)
+    tv, tb = dev(vals).requires_grad_(True), dev(B).requires_grad_(True)
+    C = torch_ops.sparse_dense_product(tv, tb, mask)
+    C.backward(dev(G))
+    torch.cuda.synchronize()
+    Bs, Gs = (B, G) if batched else (B[None], G[None])
+    want_gv = np.zeros(a.nnz_vec * V, np.float64)
+    for i in range(Bs.shape[0]):
+        assert_close((C[i] if batched else C).detach().float().cpu().numpy(), spmm_oracle(a, N, vals, Bs[i]), f"forward {i}")
+        want_gb = oracle.spmm_t(a.m_vec, V, N, K, a.row_offsets, a.col_indices, vals.astype(np.float32), Gs[i].astype(np.float32))
+        assert_close((tb.grad[i] if batched else tb.grad).float().cpu().numpy(), want_gb, f"dB {i}")
+        want_gv += oracle.sddmm(a.m_vec, N, V, a.row_offsets, a.col_indices, Gs[i].astype(np.float32), Bs[i].astype(np.float32), acc="f64")
+    assert_close(tv.grad.float().cpu().numpy(), want_gv, "dvalues")

@@ -11,6 +11,11 @@ of fixed-mask sparse attention into torch.autograd, so that the pair can sit ins
 
     mask = AttentionMask(cvse_matrix, device)
     out = fixed_mask_attention(q, k, v, mask, scale)          # [B, n, d] fp16, differentiable in q, k, v
+
+`SparseDenseProduct` does the same for the product itself (a layer with a column-vector-sparse weight):
+
+    c = sparse_dense_product(values, b, mask)                 # [m, N] = A(values) @ b, differentiable in values and b
+    # backward: d b = A^T @ d c (vs_spmm_t), d values = (d c @ b^T) sampled at the structure (vs_sddmm)
 """
 from __future__ import annotations
 
@@ -112,3 +117,36 @@ class FixedMaskAttention(torch.autograd.Function):
 
 def fixed_mask_attention(q, k, v, mask: AttentionMask, scale: float, path: int = VS_PATH_TENSOR):
     return FixedMaskAttention.apply(q, k, v, mask, scale, path)
+
+
+class SparseDenseProduct(torch.autograd.Function):
+    """C = A @ B with A a CVSE matrix (structure in `mask`, values a tensor), fp16, single or batched (values [nnz] or
+    [batch, nnz], B [K, N] or [batch, K, N]).  The backward pass is two of the library's operators: the product with
+    the transposed matrix for B, the sampled dense-dense product for the values; with batched B and shared values the
+    gradients of the values are summed over the batch."""
+
+    @staticmethod
+    def forward(ctx, values, b, mask: AttentionMask, path: int = VS_PATH_TENSOR):
+        values, b = values.contiguous(), b.contiguous()
+        c = torch.ops.vsparse.spmm(path, mask.m_vec, mask.V, mask.row_indices, mask.row_offsets, mask.col_indices, values, b)
+        ctx.save_for_backward(values, b)
+        ctx.mask, ctx.path = mask, path
+        return c
+
+    @staticmethod
+    def backward(ctx, grad_c):
+        values, b = ctx.saved_tensors
+        m = ctx.mask
+        grad_c = grad_c.contiguous()
+        grad_values = grad_b = None
+        if ctx.needs_input_grad[1]:
+            grad_b = torch.empty_like(b)
+            ops.spmm_t(m.m_vec, m.V, b.shape[-1], m.n, m.t_offsets, m.t_rows, m.t_src, values, grad_c, grad_b, m.nnz_vec)
+        if ctx.needs_input_grad[0]:
+            g = torch.ops.vsparse.sddmm(ctx.path, m.m_vec, m.V, m.nnz_vec, m.row_indices, m.row_offsets, m.col_indices, grad_c, b)
+            grad_values = g.sum(0) if (g.dim() == 2 and values.dim() == 1) else g
+        return grad_values, grad_b, None, None
+
+
+def sparse_dense_product(values, b, mask: AttentionMask, path: int = VS_PATH_TENSOR):
+    return SparseDenseProduct.apply(values, b, mask, path)
