@@ -171,7 +171,8 @@ int vs_softmax_cvse(int dtype, int m_vec, int vec_length, const int32_t *row_ind
  *   O_b = softmax(scale * SDDMM(Q_b, K_b)) . V_b, fp16 in and out, head dimension d (d % 64 == 0).
  * q [batch][m][d], kmat / vmat [batch][n][d], out [batch][m][d], all contiguous.
  * `workspace` must hold batch * nonzeros_vec * V fp16 values (the probabilities); the caller owns it.
- * Enqueues three kernels on `stream`. */
+ * One call for the whole batch (the batched form of the pipeline): it enqueues the SDDMM, the masked softmax and
+ * the SpMM on `stream` (up to five kernels with their plan and fallback kernels); they are not fused into one. */
 int vs_attention_cvse(int path, int m_vec, int vec_length, int n, int d, int nonzeros_vec,
                       const int32_t *row_indices, const int32_t *row_offsets, const int32_t *col_indices,
                       const void *q, const void *kmat, const void *vmat, void *out, void *workspace,
