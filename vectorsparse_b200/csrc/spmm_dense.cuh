@@ -69,7 +69,7 @@ constexpr int kAccCols = kHalves * kTileN;               // 256 TMEM columns per
 constexpr int kTmemCols = 2 * kAccCols;                  // 512
 constexpr int kStoreCols = 32;                           // output box of one epilogue warp: 32 rows x 32 columns
 constexpr int kStoreBoxBytes = 32 * 128;                 // staging per epilogue warp: two fp16 boxes or one fp32 box
-constexpr int kPlanThreads = 256;
+constexpr int kPlanThreads = 1024;
 constexpr int kPlanWarps = kPlanThreads / 32;
 constexpr int kMaxCheckCtas = 256;                       // CTAs of the plan kernel that look for repeated columns
 
