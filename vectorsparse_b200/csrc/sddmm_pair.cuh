@@ -73,7 +73,7 @@ constexpr int kThreads = (kMmaWarp + 1) * 32;             // 576
 constexpr int kOperandBytes = kCtaRows * kBlockK * 2;     // 16 KiB: 128 rows of either operand, 64 contraction elements
 constexpr int kTmemCols = 2 * kTile;                      // two accumulator buffers
 constexpr int kBlockVecRows = 32;                         // vector-rows per presence mask
-constexpr int kPlanThreads = 512;
+constexpr int kPlanThreads = 1024;
 constexpr int kMaxPlanColumns = 8192;                     // mask widths the plan kernel holds in shared memory
 constexpr int kSleepLoad = 32, kSleepMma = 0, kSleepEpilogue = 32;
 
@@ -150,11 +150,16 @@ sddmm_cell_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *_
         return lo;
     };
     bool twin = false;
-    for (int j = j0 + t; j < j1; j += kPlanThreads) {
-        const int c = __ldg(col_indices + j);
-        if ((unsigned)c >= (unsigned)n) continue;
-        const uint32_t bit = 1u << row_of(j);
-        twin |= (atomicOr(mask + c, bit) & bit) != 0u;
+    for (int jb = j0 + t; jb < j1; jb += 4 * kPlanThreads) {   // four entries per thread and trip: their loads fly together
+        int c[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) c[u] = jb + u * kPlanThreads < j1 ? __ldg(col_indices + jb + u * kPlanThreads) : -1;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if ((unsigned)c[u] >= (unsigned)n) continue;
+            const uint32_t bit = 1u << row_of(jb + u * kPlanThreads);
+            twin |= (atomicOr(mask + c[u], bit) & bit) != 0u;
+        }
     }
     if (twin) atomicExch(twins, 1);
     __syncthreads();
@@ -192,11 +197,17 @@ sddmm_cell_plan_kernel(const int32_t *__restrict__ row_offsets, const int32_t *_
         run += __popc(mask[c]);
     }
     __syncthreads();
-    for (int j = j0 + t; j < j1; j += kPlanThreads) {
-        const int c = __ldg(col_indices + j);
-        if ((unsigned)c >= (unsigned)n) continue;
-        const uint32_t below = (1u << row_of(j)) - 1u;
-        order[first[c] + __popc(mask[c] & below)] = j;   // twins write the same place: one of them stays
+    for (int jb = j0 + t; jb < j1; jb += 4 * kPlanThreads) {
+        int c[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) c[u] = jb + u * kPlanThreads < j1 ? __ldg(col_indices + jb + u * kPlanThreads) : -1;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if ((unsigned)c[u] >= (unsigned)n) continue;
+            const int j = jb + u * kPlanThreads;
+            const uint32_t below = (1u << row_of(j)) - 1u;
+            order[first[c[u]] + __popc(mask[c[u]] & below)] = j;   // twins write the same place: one of them stays
+        }
     }
 }
 
